@@ -1,0 +1,154 @@
+"""Compiles the CUDA sources of this folder for sm_100a into one shared library and loads it.
+
+The library is built in-tree (``_build/libtitan_b200.so``) by calling nvcc
+directly: one object per source, in parallel, then one link.  A stamp of the
+sources' contents decides whether a build is current, so a fresh checkout
+compiles at its first call and later calls only load.  If the tree cannot be
+written, the build goes to a per-user folder under the system's temporary
+directory.  Progress is printed to stderr, a line per file and one every few
+seconds while nvcc runs.
+
+There is no fallback: without nvcc or with a failing build, ``load`` raises.
+berniehans/titan compiles its kernels at run time too, through NVRTC for
+compute_86 (engine/engine-cuda/src/batched_gemm.rs:324-336).
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from typing import List, Optional
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_NAME = "libtitan_b200.so"
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+              "-Xcompiler", "-fvisibility=default"]
+
+_lib: Optional[ctypes.CDLL] = None
+_lock = threading.Lock()
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def sources() -> List[str]:
+    return sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
+
+
+def _headers() -> List[str]:
+    return sorted(f for f in os.listdir(HERE) if f.endswith((".cuh", ".h")))
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("TITAN_B200_NVCC"),
+                 os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc"),
+                 shutil.which("nvcc")):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise BuildError("nvcc was not found (CUDA_HOME, /usr/local/cuda/bin, PATH); the kernels cannot be built")
+
+
+def _stamp() -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    for f in sources() + _headers():
+        h.update(f.encode())
+        with open(os.path.join(HERE, f), "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()
+
+
+def _writable(d: str) -> bool:
+    try:
+        os.makedirs(d, exist_ok=True)
+        probe = os.path.join(d, f".probe{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.remove(probe)
+        return True
+    except OSError:
+        return False
+
+
+def build_dir() -> str:
+    d = os.environ.get("TITAN_B200_BUILD_DIR") or os.path.join(HERE, "_build")
+    if _writable(d):
+        return d
+    d = os.path.join(tempfile.gettempdir(), f"titan_b200_build_{os.getuid()}")
+    if _writable(d):
+        return d
+    raise BuildError("no writable folder for the build (tried the source tree and the temporary directory)")
+
+
+def _say(msg: str) -> None:
+    print(f"[titan_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def _run(cmd: List[str], what: str) -> None:
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=HERE)
+    if p.returncode != 0:
+        raise BuildError(f"{what} failed:\n{' '.join(cmd)}\n{p.stdout}")
+
+
+def build(force: bool = False, verbose_ptxas: bool = False) -> str:
+    """Build if the library is missing or stale; return its path."""
+    out = build_dir()
+    lib = os.path.join(out, LIB_NAME)
+    stamp_file = os.path.join(out, "stamp.txt")
+    stamp = _stamp()
+    if not force and os.path.isfile(lib) and os.path.isfile(stamp_file) and open(stamp_file).read().strip() == stamp:
+        return lib
+    nvcc = find_nvcc()
+    srcs = sources()
+    _say(f"compiling {len(srcs)} CUDA sources for sm_100a into {out} (first call only)")
+    t0 = time.time()
+    done = threading.Event()
+
+    def heartbeat():
+        while not done.wait(10.0):
+            _say(f"... still compiling ({time.time() - t0:.0f} s)")
+
+    hb = threading.Thread(target=heartbeat, daemon=True)
+    hb.start()
+    extra = ["-Xptxas", "-v"] if verbose_ptxas else []
+
+    def one(src: str) -> str:
+        obj = os.path.join(out, src[:-3] + ".o")
+        _run([nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *extra, "-c", src, "-o", obj], f"compiling {src}")
+        _say(f"compiled {src} ({time.time() - t0:.0f} s)")
+        return obj
+
+    try:
+        with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
+            objs = list(pool.map(one, srcs))
+        tmp = lib + f".{os.getpid()}.tmp"
+        _run([nvcc, *ARCH_FLAGS, "-shared", "-o", tmp, *objs], "linking")
+        os.replace(tmp, lib)
+        with open(stamp_file, "w") as f:
+            f.write(stamp)
+    finally:
+        done.set()
+    _say(f"built {LIB_NAME} in {time.time() - t0:.0f} s")
+    return lib
+
+
+def load() -> ctypes.CDLL:
+    """The loaded library; builds it first if need be.  Raises if that fails."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            path = build()
+            try:
+                _lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise BuildError(f"{path} was built but cannot be loaded: {e}") from None
+        return _lib

@@ -1,0 +1,208 @@
+// Row kernels: embedding gather, RMSNorm, per-head Q/K norm + rotary (+ cache append),
+// cache append of a prompt's keys and values, and the device-side step bookkeeping.
+//
+// Counterparts in berniehans/titan: get_rows_* (engine/engine-cuda/kernels/gemm_quant.cu:2365-2508),
+// norm_rope_swiglu_kernel and fused_qk_norm_rope_kernel (kernels/norm_rope.cu:3-134, 136-300),
+// paged_append_kv_kernel (kernels/paged_kv.cu:13-45), gpu_advance_token_step_kernel
+// (kernels/gemm_quant.cu:2570-2587).  Sums of squares, the norm scale and the rotation
+// angle are float32 with precise sqrtf / sincosf (the reference uses fast-math, norm_rope.cu:101-113).
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ out, int H, int V) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);   // ids are validated on the host; never read outside
+    const T* row = table + (size_t)tok * H;
+    float* o = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ldf(row + i);
+}
+
+extern "C" int tb_embed(const void* table, int dtype, const int* tokens, float* out, int T, int H, int V,
+                        cudaStream_t stream) {
+    TB_REQUIRE(T > 0 && H > 0 && V > 0, "embed: sizes must be positive (T=%d H=%d V=%d)", T, H, V);
+    const int threads = H >= 1024 ? 256 : 128;
+    if (dtype == TB_F32)
+        embed_kernel<float><<<T, threads, 0, stream>>>((const float*)table, tokens, out, H, V);
+    else if (dtype == TB_BF16)
+        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, H, V);
+    else
+        TB_REQUIRE(false, "embed: unknown dtype %d", dtype);
+    TB_CHECK_LAUNCH("embed");
+    return 0;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// y[r] = x[rows ? rows[r] : r] * 1/sqrt(mean(x^2) + eps) * w      (x float32, y in the compute dtype)
+template <typename T>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
+                               const int* __restrict__ rows, int H, float eps) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = xr[i];
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+    T* yr = y + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) stf(yr + i, xr[i] * scale * w[i]);
+}
+
+extern "C" int tb_rmsnorm(const float* x, const float* w, void* y, int dtype, const int* rows, int n_rows,
+                          int H, float eps, cudaStream_t stream) {
+    TB_REQUIRE(n_rows > 0 && H > 0, "rmsnorm: sizes must be positive (rows=%d H=%d)", n_rows, H);
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 64);
+    if (dtype == TB_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, (float*)y, rows, H, eps);
+    else if (dtype == TB_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, rows, H, eps);
+    else
+        TB_REQUIRE(false, "rmsnorm: unknown dtype %d", dtype);
+    TB_CHECK_LAUNCH("rmsnorm");
+    return 0;
+}
+
+// ------------------------------------------------------------------ Q/K head norm + rotary (+ append)
+// One warp per (token, head).  Heads 0..nh-1 are Q, nh..nh+nkv-1 are K, and, when the cache is
+// written here, nh+nkv.. are V (copied unchanged).  Per head: RMSNorm over head_dim with a shared
+// weight (skipped when the weight pointer is null), then the half-split rotation of the first
+// ``rot`` dims: for k < rot/2, angle = pos * inv_freq[k], (y_k, y_{k+rot/2}) rotated
+// (kernels/norm_rope.cu:226-245 and :83-117 in berniehans/titan).
+struct QkArgs {
+    const void* in; int in_stride;          // [T][in_stride]: Q | K | V
+    void* q_out; int q_stride;              // [T][q_stride]
+    void* k_out; int k_stride;              // [T][k_stride] (null: K goes to the cache only)
+    const float* q_w; const float* k_w;     // [hd] or null
+    const float* inv_freq;                  // [rot/2] or null (no rotation)
+    float eps; int rot; int nh; int nkv; int hd;
+    const int* pos_of; const int* seq_of; const int* slot_of_seq;
+    TbKvView cache; int append; int T;
+};
+
+#define QK_MAXE 8   // head_dim <= 32 * QK_MAXE
+
+template <typename TIn, typename TOut>
+__global__ void qk_norm_rope_kernel(QkArgs a) {
+    extern __shared__ float head_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x;
+    const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+    const int n_heads = a.nh + a.nkv + (a.append ? a.nkv : 0);
+    if (head >= n_heads) return;
+    float* y = head_smem + warp * a.hd;
+    const int hd = a.hd;
+    const bool is_q = head < a.nh, is_k = !is_q && head < a.nh + a.nkv;
+    const int col = is_q ? head * hd : (is_k ? a.nh * hd + (head - a.nh) * hd
+                                             : (a.nh + a.nkv) * hd + (head - a.nh - a.nkv) * hd);
+    const TIn* x = (const TIn*)a.in + (size_t)t * a.in_stride + col;
+    float v[QK_MAXE];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < QK_MAXE; ++j) {
+        const int e = lane + 32 * j;
+        v[j] = e < hd ? ldf(x + e) : 0.f;
+        ss += v[j] * v[j];
+    }
+    const int pos = a.pos_of[t];
+    const int slot = a.slot_of_seq[a.seq_of[t]];
+    if (!is_q && !is_k) {   // V: straight copy into the cache
+        TOut* dst = (TOut*)a.cache.storage + kv_half_elems(a.cache) + kv_row_offset(a.cache, slot, pos, head - a.nh - a.nkv);
+#pragma unroll
+        for (int j = 0; j < QK_MAXE; ++j) {
+            const int e = lane + 32 * j;
+            if (e < hd) stf(dst + e, v[j]);
+        }
+        return;
+    }
+    const float* w = is_q ? a.q_w : a.k_w;
+    float scale = 1.f;
+    if (w) {
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)hd + a.eps);
+    }
+#pragma unroll
+    for (int j = 0; j < QK_MAXE; ++j) {
+        const int e = lane + 32 * j;
+        if (e < hd) y[e] = w ? v[j] * scale * w[e] : v[j];
+    }
+    __syncwarp();
+    const int half = a.rot >> 1;
+    TOut* out = is_q ? (TOut*)a.q_out + (size_t)t * a.q_stride + head * hd
+                     : (a.k_out ? (TOut*)a.k_out + (size_t)t * a.k_stride + (head - a.nh) * hd : nullptr);
+    TOut* cdst = (is_k && a.append)
+                     ? (TOut*)a.cache.storage + kv_row_offset(a.cache, slot, pos, head - a.nh) : nullptr;
+#pragma unroll
+    for (int j = 0; j < QK_MAXE; ++j) {
+        const int e = lane + 32 * j;
+        if (e >= hd) continue;
+        float r = y[e];
+        if (a.inv_freq && e < a.rot) {
+            const bool first = e < half;
+            const int k = first ? e : e - half;
+            float s, c;
+            sincosf((float)pos * a.inv_freq[k], &s, &c);
+            r = first ? y[e] * c - y[e + half] * s : y[e - half] * s + y[e] * c;
+        }
+        if (out) stf(out + e, r);
+        if (cdst) stf(cdst + e, r);
+    }
+}
+
+extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, cudaStream_t stream) {
+    QkArgs a = *args;
+    TB_REQUIRE(a.T > 0 && a.nh > 0 && a.nkv >= 0, "qk_norm_rope: sizes must be positive");
+    TB_REQUIRE(a.hd > 0 && a.hd <= 32 * QK_MAXE, "qk_norm_rope: head_dim %d is not in 1..%d", a.hd, 32 * QK_MAXE);
+    TB_REQUIRE(a.rot >= 0 && a.rot <= a.hd && a.rot % 2 == 0, "qk_norm_rope: rotary_dim %d must be even and <= head_dim %d", a.rot, a.hd);
+    TB_REQUIRE(!a.append || (a.cache.storage && a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv),
+               "qk_norm_rope: the cache view does not match the heads");
+    const int warps = 4;
+    const int n_heads = a.nh + a.nkv + (a.append ? a.nkv : 0);
+    dim3 grid(a.T, (n_heads + warps - 1) / warps);
+    const size_t smem = (size_t)warps * a.hd * sizeof(float);
+    if (in_dtype == TB_F32 && out_dtype == TB_F32)
+        qk_norm_rope_kernel<float, float><<<grid, warps * 32, smem, stream>>>(a);
+    else if (in_dtype == TB_BF16 && out_dtype == TB_BF16)
+        qk_norm_rope_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, warps * 32, smem, stream>>>(a);
+    else if (in_dtype == TB_F32 && out_dtype == TB_BF16)
+        qk_norm_rope_kernel<float, __nv_bfloat16><<<grid, warps * 32, smem, stream>>>(a);
+    else
+        TB_REQUIRE(false, "qk_norm_rope: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+    TB_CHECK_LAUNCH("qk_norm_rope");
+    return 0;
+}
+
+// ------------------------------------------------------------------ append a prompt's K and V
+// Copies rows of the step's own K | V (``kv`` [T][stride], K heads then V heads) into the cache.
+// In a ring, a token whose row a later token of the same step also maps to is skipped.
+template <typename T>
+__global__ void kv_append_kernel(const T* __restrict__ kv, int stride, TbKvView c, const int* pos_of,
+                                 const int* seq_of, const int* slot_of_seq, const int* kv_len) {
+    const int t = blockIdx.x, h2 = blockIdx.y;            // h2 < 2 * kv_heads
+    const int seq = seq_of[t], pos = pos_of[t];
+    if (c.ring_rows && pos < kv_len[seq] - c.ring_rows) return;
+    const int is_v = h2 >= c.kv_heads, head = is_v ? h2 - c.kv_heads : h2;
+    const T* src = kv + (size_t)t * stride + (size_t)h2 * c.head_dim;
+    T* dst = (T*)c.storage + (is_v ? kv_half_elems(c) : 0) + kv_row_offset(c, slot_of_seq[seq], pos, head);
+    for (int e = threadIdx.x; e < c.head_dim; e += blockDim.x) dst[e] = src[e];
+}
+
+extern "C" int tb_kv_append(const void* kv, int stride, int dtype, const TbKvView* cache, const TbBatch* b,
+                            cudaStream_t stream) {
+    TbKvView c = *cache;
+    TB_REQUIRE(b->T > 0 && c.storage, "kv_append: nothing to append or no cache");
+    dim3 grid(b->T, 2 * c.kv_heads);
+    const int threads = c.head_dim >= 64 ? 64 : 32;
+    if (dtype == TB_F32)
+        kv_append_kernel<float><<<grid, threads, 0, stream>>>((const float*)kv, stride, c, b->pos_of, b->seq_of, b->slot_of_seq, b->kv_len);
+    else if (dtype == TB_BF16)
+        kv_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)kv, stride, c, b->pos_of, b->seq_of, b->slot_of_seq, b->kv_len);
+    else
+        TB_REQUIRE(false, "kv_append: unknown dtype %d", dtype);
+    TB_CHECK_LAUNCH("kv_append");
+    return 0;
+}

@@ -1,0 +1,206 @@
+"""The engine: a model on the GPU, its cache, the step function and the generation backend.
+
+``Engine.step`` is the one step function.  It takes a batch of sequences, each
+with the tokens it brings now (a whole prompt, or one token), runs exactly those
+tokens as one packed batch from the cache that earlier steps left, and returns
+float32 logits at the wanted places.  berniehans/titan's counterpart is
+``ForwardDriver::prefill_chunked`` / ``decode`` for one sequence
+(engine/engine-core/src/forward_driver.rs:939-1242, 3035-3070).
+
+Nothing is committed if a step is refused: validation and page reservation
+happen before the first kernel (the reference's InvalidSize guards,
+forward_driver.rs:947-953, 3037-3043).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import kernels as K
+from ..cache import PAGE_SIZE, CacheError, CacheFull, SequenceCache
+from ..config import load_config
+from ..sampling import DeviceSampler, SamplerParams
+from ..weights import DictWeights, FolderWeights, RandomWeights
+from .batch import StepContext, StepEntry, StepLayout
+from .generate import GenerationRequest, GenerationResult, generate, round_up
+from .model import DecoderModel
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+class StepError(ValueError):
+    """A step that the engine refuses; the cache is as it was."""
+
+
+@dataclass
+class EngineOptions:
+    dtype: object = "bfloat16"
+    max_tokens: int = 8192            # tokens the cache holds over all live sequences (pages of 64)
+    max_context: Optional[int] = None  # longest sequence; default: what the cache and the model allow
+    max_slots: Optional[int] = None
+    max_batch: int = 64               # sequences per generation batch
+    gemm: str = "fast"                # "plain": CUDA-core matrix products even in bfloat16
+    attn_chunk: int = 256             # keys per split of decode attention
+    device: str = "cuda:0"
+
+
+class Engine:
+    def __init__(self, config, source_factory, options: EngineOptions):
+        if not torch.cuda.is_available():
+            raise RuntimeError("titan_b200 runs on a CUDA device (sm_100a); none is visible and there is no CPU path")
+        self.options = options
+        self.device = torch.device(options.device)
+        torch.cuda.set_device(self.device)
+        K.lib()                                   # build / load the kernels now, loudly
+        self.dtype = _DTYPES[options.dtype]
+        self.config = config
+        self.spec = config.to_model_spec()
+        self.model = DecoderModel(self.spec)
+        self.model.load(source_factory(self.model.declared_weights(), self.dtype, self.device))
+        num_pages = -(-options.max_tokens // PAGE_SIZE)
+        max_context = min(options.max_context or num_pages * PAGE_SIZE, num_pages * PAGE_SIZE)
+        max_slots = options.max_slots or max(1, min(num_pages, (16 << 20) // max(1, -(-max_context // PAGE_SIZE))))
+        self.cache = SequenceCache(self.model.cache_needs(), options.max_tokens, max_slots, max_context,
+                                   self.dtype, self.device)
+        self.sampler = DeviceSampler(self.cache.state, max_slots, self.spec.vocab_size, self.device)
+        self.scratch: Dict[str, torch.Tensor] = {}
+        self.step_options = {"gemm": options.gemm, "attn_chunk": options.attn_chunk}
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    # -- construction ------------------------------------------------------- #
+    @classmethod
+    def from_pretrained(cls, model_dir: str, dtype="bfloat16", **kw) -> "Engine":
+        config = load_config(model_dir)
+        ignorable = ["lm_head.weight"] if config.to_model_spec().lm_head is None else []
+        return cls(config, lambda declared, dt, dev: FolderWeights(model_dir, declared, dt, dev, ignorable),
+                   EngineOptions(dtype=dtype, **kw))
+
+    @classmethod
+    def from_random(cls, config, seed: int, dtype="bfloat16", **kw) -> "Engine":
+        """Random weights made on the device (N(0, 0.02) matrices, 1 + N(0, 0.1) norm weights)."""
+        return cls(config, lambda declared, dt, dev: RandomWeights(seed, dt, dev, store_dtype=torch.bfloat16),
+                   EngineOptions(dtype=dtype, **kw))
+
+    @classmethod
+    def from_tensors(cls, config, tensors: Dict[str, torch.Tensor], dtype="bfloat16", **kw) -> "Engine":
+        return cls(config, lambda declared, dt, dev: DictWeights(tensors, declared, dt, dev), EngineOptions(dtype=dtype, **kw))
+
+    # -- properties the generation loop reads -------------------------------- #
+    @property
+    def vocab_size(self) -> int:
+        return self.spec.vocab_size
+
+    @property
+    def max_context(self) -> int:
+        return self.cache.max_context
+
+    @property
+    def max_batch(self) -> int:
+        return min(self.options.max_batch, self.cache.max_slots)
+
+    # -- slots --------------------------------------------------------------- #
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    # -- the step function ---------------------------------------------------- #
+    def _context(self, layout: StepLayout) -> StepContext:
+        return StepContext(layout, K.current_stream(), self.dtype, self.device, self.step_options, self.scratch)
+
+    def _check_entries(self, entries: Sequence[StepEntry]) -> List[int]:
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        seen = set()
+        starts = []
+        V = self.spec.vocab_size
+        for e in entries:
+            if not self.cache.is_live(e.slot):
+                raise StepError(f"slot {e.slot} is not live")
+            if e.slot in seen:
+                raise StepError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"slot {e.slot} brings no token")
+            for t in e.tokens:
+                if not 0 <= int(t) < V:
+                    raise StepError(f"token id {t} lies outside the vocabulary of {V}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"logits wanted at place {w} of {n} tokens")
+            starts.append(self.cache.length[e.slot])
+        return starts
+
+    def forward(self, entries: Sequence[StepEntry]) -> Tuple[torch.Tensor, StepLayout, StepContext]:
+        """Run the tokens through the blocks; returns the residual stream [T, H]."""
+        starts = self._check_entries(entries)
+        try:
+            self.cache.reserve({e.slot: s + len(e.tokens) for e, s in zip(entries, starts)})
+        except CacheFull as err:
+            raise StepError(str(err)) from None
+        layout = StepLayout(entries, starts, self.device)
+        self.h2d_bytes += layout.h2d_bytes
+        ctx = self._context(layout)
+        self.sampler.observe(layout, ctx.stream)
+        x = self.model.forward_hidden(ctx, self.cache)
+        for e, s in zip(entries, starts):
+            self.cache.commit(e.slot, s + len(e.tokens))
+        return x, layout, ctx
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Logits float32 [wanted, vocab] on the device, in the order of the entries and of
+        their ``want`` lists; None if nothing is wanted."""
+        x, layout, ctx = self.forward(entries)
+        if layout.W == 0:
+            return None
+        return self.model.logits(x, ctx, layout.want)
+
+    # -- backend of the generation loop ---------------------------------------- #
+    def room_for(self, token_counts: Sequence[int]) -> bool:
+        held = self.cache.tokens_held()
+        want = sum(round_up(n, self.cache.page_size) for n in token_counts)
+        return (held + want <= self.cache.num_pages * self.cache.page_size
+                and self.cache.slots.free_count >= len(token_counts))
+
+    def start(self, prompts, params, sequence_ids):
+        slots = [self.cache.alloc_slot() for _ in prompts]
+        try:
+            self.sampler.configure(slots, params, sequence_ids)
+            entries = [StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)]
+            return slots, self._step_and_sample(entries)
+        except Exception:
+            for s in slots:
+                self.cache.free_slot(s)
+            raise
+
+    def advance(self, slots, tokens):
+        return self._step_and_sample([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)])
+
+    def finish(self, slot) -> None:
+        self.cache.free_slot(slot)
+
+    def _step_and_sample(self, entries) -> List[int]:
+        x, layout, ctx = self.forward(entries)
+        logits = self.model.logits(x, ctx, layout.want)
+        tokens = self.sampler.sample(logits, layout.slot_of_seq, ctx.stream)
+        host = tokens.cpu()
+        self.d2h_bytes += host.numel() * 4
+        return host.tolist()
+
+    # -- the call a user makes --------------------------------------------------- #
+    def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 512,
+                 params: Optional[SamplerParams] = None, stop_tokens: Optional[Sequence[int]] = None,
+                 include_stop: bool = False) -> List[GenerationResult]:
+        """Token ids in, token ids out.  ``stop_tokens`` defaults to the configuration's
+        end-of-sequence ids (the reference uses literal Qwen ids, engine-server/src/server.rs:259)."""
+        params = params or SamplerParams()
+        stops = tuple(self.spec.stop_token_ids) if stop_tokens is None else tuple(int(t) for t in stop_tokens)
+        reqs = [GenerationRequest(list(p), max_tokens, params, stops, include_stop) for p in prompts]
+        return generate(self, reqs)

@@ -1,0 +1,166 @@
+"""Python face of the hand-written CUDA library: argument structs and checked calls.
+
+Every function here launches kernels of ``titan_b200/csrc`` on the given CUDA
+stream and raises ``KernelError`` with the launcher's message when it refuses
+its arguments.  Nothing here computes on the host and nothing falls back to a
+library: if the extension cannot be built or loaded, the first call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, byref, c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+EPI_STORE, EPI_F32, EPI_ADD, EPI_SWIGLU = 0, 1, 2, 3
+F32, BF16 = 0, 1
+
+launch_count = 0          # launcher calls since import (a launcher starts one or two kernels)
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class KvView(Structure):
+    _fields_ = [("storage", c_void_p), ("table", c_void_p), ("table_width", c_int), ("ring_rows", c_int),
+                ("page_size", c_int), ("num_pages", c_int), ("kv_heads", c_int), ("head_dim", c_int)]
+
+
+class Batch(Structure):
+    _fields_ = [("tokens", c_void_p), ("seq_of", c_void_p), ("pos_of", c_void_p), ("slot_of_seq", c_void_p),
+                ("q_start", c_void_p), ("start_pos", c_void_p), ("kv_len", c_void_p),
+                ("T", c_int), ("B", c_int), ("max_new", c_int), ("max_kv_len", c_int)]
+
+
+class QkArgs(Structure):
+    _fields_ = [("inp", c_void_p), ("in_stride", c_int), ("q_out", c_void_p), ("q_stride", c_int),
+                ("k_out", c_void_p), ("k_stride", c_int), ("q_w", c_void_p), ("k_w", c_void_p),
+                ("inv_freq", c_void_p), ("eps", c_float), ("rot", c_int), ("nh", c_int), ("nkv", c_int),
+                ("hd", c_int), ("pos_of", c_void_p), ("seq_of", c_void_p), ("slot_of_seq", c_void_p),
+                ("cache", KvView), ("append", c_int), ("T", c_int)]
+
+
+class AttnArgs(Structure):
+    _fields_ = [("q", c_void_p), ("q_stride", c_int), ("kv_new", c_void_p), ("kv_stride", c_int),
+                ("out", c_void_p), ("out_stride", c_int), ("cache", KvView), ("batch", Batch),
+                ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("window", c_int), ("scale", c_float),
+                ("chunk", c_int), ("n_splits", c_int), ("scratch", c_void_p)]
+
+
+class SampleArgs(Structure):
+    _fields_ = [("logits", c_void_p), ("ld", c_int), ("V", c_int), ("B", c_int), ("slot_of_row", c_void_p),
+                ("temperature", c_void_p), ("top_k", c_void_p), ("top_p", c_void_p), ("penalty", c_void_p),
+                ("seed", c_void_p), ("sequence_id", c_void_p), ("sample_step", c_void_p),
+                ("last_token", c_void_p), ("seen", c_void_p), ("seen_words", c_int), ("out", c_void_p)]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded extension (built on first use)."""
+    global _lib
+    if _lib is None:
+        l = _build.load()
+        l.tb_last_error.restype = ctypes.c_char_p
+        l.tb_uniform24.restype = ctypes.c_uint
+        l.tb_uniform24.argtypes = [c_longlong, c_longlong, c_longlong]
+        l.tb_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        l.tb_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
+        l.tb_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        l.tb_qk_norm_rope.argtypes = [POINTER(QkArgs), c_int, c_int, c_void_p]
+        l.tb_kv_append.argtypes = [c_void_p, c_int, c_int, POINTER(KvView), POINTER(Batch), c_void_p]
+        l.tb_attn_prefill.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
+        l.tb_attn_decode.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
+        l.tb_sample.argtypes = [POINTER(SampleArgs), c_void_p]
+        l.tb_mark_seen.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+        _lib = l
+    return _lib
+
+
+def _check(rc: int) -> None:
+    global launch_count
+    launch_count += 1
+    if rc:
+        raise KernelError(lib().tb_last_error().decode())
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"the kernels take float32 and bfloat16, not {dt}")
+
+
+def current_stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the kernels run on CUDA tensors only; there is no CPU path")
+
+
+# --------------------------------------------------------------------------- #
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, stream: int) -> None:
+    _need_cuda(table, tokens, out)
+    _check(lib().tb_embed(table.data_ptr(), dtype_code(table.dtype), tokens.data_ptr(), out.data_ptr(),
+                          tokens.numel(), table.shape[1], table.shape[0], stream))
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, eps: float, stream: int,
+            rows: Optional[torch.Tensor] = None) -> None:
+    _need_cuda(x, w, y, rows)
+    n = y.shape[0]
+    _check(lib().tb_rmsnorm(x.data_ptr(), w.data_ptr(), y.data_ptr(), dtype_code(y.dtype), _ptr(rows), n,
+                            x.shape[-1], eps, stream))
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, stream: int) -> None:
+    """out (epilogue ``epi``) = x[M,K] . w[N,K]^T; x and out may be row-strided views."""
+    _need_cuda(x, w, out)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or not w.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"gemm: shapes do not fit: x {tuple(x.shape)} w {tuple(w.shape)}")
+    _check(lib().tb_gemm_simt(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(w.dtype), M, N, K,
+                              x.stride(0), out.stride(0), epi, stream))
+
+
+def qk_norm_rope(args: QkArgs, in_dtype: torch.dtype, out_dtype: torch.dtype, stream: int) -> None:
+    _check(lib().tb_qk_norm_rope(byref(args), dtype_code(in_dtype), dtype_code(out_dtype), stream))
+
+
+def kv_append(kv: torch.Tensor, cache: KvView, batch: Batch, stream: int) -> None:
+    _check(lib().tb_kv_append(kv.data_ptr(), kv.stride(0), dtype_code(kv.dtype), byref(cache), byref(batch), stream))
+
+
+def attn_prefill(args: AttnArgs, dtype: torch.dtype, stream: int) -> None:
+    _check(lib().tb_attn_prefill(byref(args), dtype_code(dtype), stream))
+
+
+def attn_decode(args: AttnArgs, dtype: torch.dtype, stream: int) -> None:
+    _check(lib().tb_attn_decode(byref(args), dtype_code(dtype), stream))
+
+
+def sample(args: SampleArgs, stream: int) -> None:
+    _check(lib().tb_sample(byref(args), stream))
+
+
+def mark_seen(tokens, seq_of, slot_of_seq, seen: torch.Tensor, T: int, stream: int) -> None:
+    _check(lib().tb_mark_seen(tokens.data_ptr(), seq_of.data_ptr(), slot_of_seq.data_ptr(), seen.data_ptr(),
+                              seen.shape[1], T, stream))
+
+
+def uniform24(seed: int, sequence: int, step: int) -> int:
+    return int(lib().tb_uniform24(seed, sequence, step))

@@ -1,0 +1,146 @@
+"""Causal grouped-query attention as a mixer.
+
+x -> [Q | K | V] = x . Wqkv^T -> per-head RMSNorm on Q and K (optional) ->
+position encoding on Q and K -> keys and values into the cache -> softmax(q.k *
+scale) v over the keys the query may see (all earlier ones, or the last
+``window``) -> . Wo^T, added into the residual stream.
+
+berniehans/titan: engine/engine-core/src/forward_cpu.rs:300-366 and 440-507;
+driver steps forward_driver.rs:1010-1133 (prompt) and 2168-2259 (one token).
+Q, K and V are three launches there; here their weights are concatenated at
+bind time into one [Q + 2 KV, H] matrix.
+
+A step of single tokens writes K and V into the cache inside the norm/rotary
+kernel and attends over the cache.  A step with longer runs of tokens keeps the
+step's own K and V beside the cache, attends over both, and appends afterwards,
+which is what makes a ring of ``window`` rows safe.
+
+With ``cache_from`` the mixer owns no keys: it projects queries only and reads
+the named layer's cache.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from .. import kernels as K
+from ..cache.groups import CacheNeed, KVGroup
+from ..weights.loader import WeightSpec
+from . import linear
+from .base import MIXERS, NORMS, POSITIONS, Mixer
+
+
+class AttentionMixer(Mixer):
+    def __init__(self, spec):
+        s = spec
+        if s.num_heads <= 0 or s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
+            raise ValueError(f"{s.num_heads} query heads are not a multiple of {s.num_kv_heads} kv heads")
+        if s.head_dim % 16 or not 16 <= s.head_dim <= 256:
+            raise ValueError(f"head_dim {s.head_dim} is not supported: multiples of 16 from 16 to 256")
+        if s.window is not None and s.window <= 0:
+            raise ValueError("an attention window must be positive")
+        if s.cache_from is not None and s.window is not None:
+            raise ValueError("a mixer that reads another layer's cache cannot have a window")
+        self.spec = s
+        self.Q, self.KV = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        self.shared = s.cache_from is not None
+        self.position = POSITIONS.build(s.position)
+        self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(s.head_dim)
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self._views = {}
+
+    # -- declaration ------------------------------------------------------ #
+    def cache_need(self) -> Optional[CacheNeed]:
+        if self.shared:
+            return None
+        return CacheNeed("kv", self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+
+    def weight_specs(self, prefix: str) -> List[WeightSpec]:
+        s, p = self.spec, prefix + self.spec.prefix
+        specs = [WeightSpec(p + "q_proj.weight", (self.Q, s.hidden_size)),
+                 WeightSpec(p + "o_proj.weight", (s.hidden_size, self.Q))]
+        if not self.shared:
+            specs += [WeightSpec(p + "k_proj.weight", (self.KV, s.hidden_size)),
+                      WeightSpec(p + "v_proj.weight", (self.KV, s.hidden_size))]
+        if s.qk_norm is not None:
+            for which in ("q",) if self.shared else ("q", "k"):
+                specs.append(WeightSpec(p + s.qk_norm.weight.format(which), (s.head_dim,), "vector", ("one_plus_normal", 0.1)))
+        return specs
+
+    def bind(self, get) -> None:
+        s, p = self.spec, self.spec.prefix
+        parts = [get(p + "q_proj.weight")]
+        if not self.shared:
+            parts += [get(p + "k_proj.weight"), get(p + "v_proj.weight")]
+        self.w_qkv = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0]
+        self.w_o = get(p + "o_proj.weight")
+        if s.qk_norm is not None:
+            self.q_norm = get(p + s.qk_norm.weight.format("q"))
+            self.k_norm = None if self.shared else get(p + s.qk_norm.weight.format("k"))
+
+    # -- one step --------------------------------------------------------- #
+    def _view(self, cache) -> K.KvView:
+        group, index = cache
+        key = (id(group), index)
+        if key not in self._views:
+            assert isinstance(group, KVGroup)
+            self._views[key] = K.KvView(group.layer_storage(index).data_ptr(), group.table.data_ptr(), group.table_width,
+                                        group.ring_rows, group.page_size, group.num_pages, group.need.num_kv_heads,
+                                        group.need.head_dim)
+        return self._views[key]
+
+    def forward(self, h: torch.Tensor, ctx, cache, out: torch.Tensor) -> None:
+        s, lay = self.spec, ctx.layout
+        T, Q, KV, hd = lay.T, self.Q, self.KV, s.head_dim
+        width = Q if self.shared else Q + 2 * KV
+        qkv = ctx.empty((T, width))
+        linear.matmul(h, self.w_qkv, qkv, linear.EPI_STORE, ctx)
+        view = self._view(cache)
+        decode = lay.all_single
+        tables = self.position.tables(ctx.device)
+        inv_freq = tables.get("inv_freq")
+        esz = qkv.element_size()
+        qa = K.QkArgs()
+        qa.inp, qa.in_stride = qkv.data_ptr(), width
+        qa.q_out, qa.q_stride = qkv.data_ptr(), width
+        qa.k_out, qa.k_stride = (None, 0) if self.shared else (qkv.data_ptr() + Q * esz, width)
+        qa.q_w = None if self.q_norm is None else self.q_norm.data_ptr()
+        qa.k_w = None if self.k_norm is None else self.k_norm.data_ptr()
+        qa.inv_freq = None if inv_freq is None else inv_freq.data_ptr()
+        qa.eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
+        qa.rot, qa.nh, qa.nkv, qa.hd = self.position.rotary_dim, s.num_heads, (0 if self.shared else s.num_kv_heads), hd
+        qa.pos_of, qa.seq_of, qa.slot_of_seq = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr()
+        qa.cache, qa.append, qa.T = view, int(decode and not self.shared), T
+        K.qk_norm_rope(qa, qkv.dtype, qkv.dtype, ctx.stream)
+
+        attn = ctx.empty((T, Q))
+        aa = K.AttnArgs()
+        aa.q, aa.q_stride = qkv.data_ptr(), width
+        aa.out, aa.out_stride = attn.data_ptr(), Q
+        aa.cache, aa.batch = view, lay.c_struct()
+        aa.nh, aa.nkv, aa.hd = s.num_heads, view.kv_heads, hd
+        aa.window, aa.scale = s.window or 0, self.scale
+        if decode:
+            chunk = int(ctx.options.get("attn_chunk", 256))
+            splits = int(ctx.options.get("attn_splits", 0)) or max(1, -(-lay.max_kv_len // chunk))
+            need = lay.B * s.num_heads * splits * (hd + 2)
+            scratch = ctx.scratch.get("attn_partials")
+            if scratch is None or scratch.numel() < need:
+                scratch = ctx.scratch["attn_partials"] = torch.empty(need, dtype=torch.float32, device=ctx.device)
+            aa.kv_new, aa.kv_stride = None, 0
+            aa.chunk, aa.n_splits, aa.scratch = chunk, splits, scratch.data_ptr()
+            K.attn_decode(aa, qkv.dtype, ctx.stream)
+        else:
+            if self.shared:
+                aa.kv_new, aa.kv_stride = None, 0
+            else:
+                aa.kv_new, aa.kv_stride = qkv.data_ptr() + Q * esz, width
+            K.attn_prefill(aa, qkv.dtype, ctx.stream)
+            if not self.shared:
+                K.kv_append(qkv[:, Q:], view, lay.c_struct(), ctx.stream)
+        linear.matmul(attn, self.w_o, out, linear.EPI_ADD, ctx)
+
+
+MIXERS.register("attention", AttentionMixer)

@@ -1,0 +1,44 @@
+"""Arrangements of a block's parts around the residual stream.
+
+``pre_norm``:  x += mixer(norm1(x));  x += feed_forward(norm2(x))
+(berniehans/titan: engine/engine-core/src/forward_cpu.rs:281-386).  The
+residual stream ``x`` is float32 and is updated in place: mixer and
+feed-forward add into it in the epilogue of their last matrix product.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..weights.loader import WeightSpec
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Part
+
+
+class PreNormBlock(Part):
+    def __init__(self, spec):
+        self.spec = spec
+        self.mixer_norm = NORMS.build(spec.mixer_norm)
+        self.mixer = MIXERS.build(spec.mixer)
+        self.feed_forward_norm = NORMS.build(spec.feed_forward_norm)
+        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward)
+
+    def parts(self):
+        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+
+    def weight_specs(self, prefix: str = "") -> List[WeightSpec]:
+        out: List[WeightSpec] = []
+        for part in self.parts():
+            out += part.weight_specs(self.spec.prefix)
+        return out
+
+    def bind(self, get) -> None:
+        for part in self.parts():
+            part.bind(lambda name: get(self.spec.prefix + name))
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> None:
+        self.mixer.forward(self.mixer_norm.forward(x, ctx), ctx, cache, x)
+        self.feed_forward.forward(self.feed_forward_norm.forward(x, ctx), ctx, x)
+
+
+BLOCKS.register("pre_norm", PreNormBlock)
