@@ -1,0 +1,242 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of titan_b200 on one B200, Qwen3-8B layer sizes, random bfloat16 weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 with every sequence near the
+benchmark context length (device time, CUDA events around K decode steps); ``e2e`` is the same steps
+through the Python entry point with host tokens in and out; ``prefill`` is one 2,048-token prompt;
+``roofline`` divides the bytes a decode step has to read (every weight once, the live cache) by its
+time; ``points`` holds decode at batch 1 and 64.  The step reads far more than the 126 MB L2, so no
+flush is needed between iterations (``config.l2``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=4096,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288,
+                vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                max_position_embeddings=40960, hidden_act="silu")
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["source"] = "measured"
+        return p
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs (read-only queries)."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.proc, self.index = None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def fill_cache_random(engine, slots, length):
+    """Benchmark set-up: give every slot ``length`` tokens of random keys and values without running
+    the prompts (the timed steps only read them)."""
+    engine.cache.reserve({s: length for s in slots})
+    for s in slots:
+        engine.cache.commit(s, length)
+    for g in engine.cache.groups:
+        if hasattr(g, "pool"):
+            g.storage.normal_(0.0, 1.0)
+
+
+def decode_flops_and_bytes(engine, batch, kv_len):
+    spec = engine.spec
+    per_token_kv = 0
+    for g in engine.cache.groups:
+        if hasattr(g, "pool"):
+            per_token_kv += len(g.layers) * 2 * g.need.num_kv_heads * g.need.head_dim * g.storage.element_size()
+    return engine.model.weight_bytes() + batch * kv_len * per_token_kv
+
+
+def prefill_flops(cfg, layers, T):
+    H, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    Q, KV = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+    linear = 2 * T * (H * (Q + 2 * KV) + Q * H + 3 * H * F) * layers
+    attn = 4 * Q * (T * (T + 1) / 2) * layers        # QK^T and PV over the causal half
+    return linear + attn + 2 * H * V                 # LM head on the last row
+
+
+def time_decode(engine, torch, K, batch, kv_start, steps, warmup, e2e: bool):
+    """K timed decode steps at ``batch`` sequences that hold ``kv_start`` tokens at the start.
+    Returns (ms per step by CUDA events, ms per step by wall clock incl. host copies, launcher calls)."""
+    from titan_b200 import SamplerParams
+    slots = [engine.alloc_slot() for _ in range(batch)]
+    try:
+        fill_cache_random(engine, slots, kv_start)
+        engine.sampler.configure(slots, [SamplerParams.greedy()] * batch, list(range(batch)))
+        tokens = [(7 * i + 1) % engine.vocab_size for i in range(batch)]
+        for _ in range(warmup):
+            tokens = engine.advance(slots, tokens)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = K.launch_count
+        t0 = time.perf_counter()
+        start.record()
+        for _ in range(steps):
+            tokens = engine.advance(slots, tokens)       # host token ids in, sampled host token ids out
+        stop.record()
+        torch.cuda.synchronize()
+        wall_ms = (time.perf_counter() - t0) * 1e3 / steps
+        dev_ms = start.elapsed_time(stop) / steps
+        return dev_ms, wall_ms, K.launch_count - launches0
+    finally:
+        for s in slots:
+            engine.free_slot(s)
+
+
+def time_prefill(engine, torch, T, warmup, reps):
+    from titan_b200 import StepEntry
+    prompt = [(13 * i + 5) % engine.vocab_size for i in range(T)]
+    times = []
+    for r in range(warmup + reps):
+        s = engine.alloc_slot()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.step([StepEntry(s, prompt, [T - 1])])
+        stop.record()
+        torch.cuda.synchronize()
+        engine.free_slot(s)
+        if r >= warmup:
+            times.append(start.elapsed_time(stop))
+    return statistics.median(times)
+
+
+def run_ours(args):
+    import torch
+
+    from titan_b200 import Engine, kernels as K
+    from titan_b200.config import config_from_dict
+    pk = peaks()
+    cfg = dict(QWEN3_8B)
+    cfg["num_hidden_layers"] = args.layers
+    context, B = args.context, args.batch
+    big = max(B, 64 if not args.skip_points else B)
+    engine = Engine.from_random(config_from_dict(cfg), seed=2, dtype="bfloat16", max_tokens=big * context,
+                                max_context=context, max_slots=big, max_batch=big)
+    kv_start = context - (args.steps + args.warmup) - 1
+    clocks = ClockSampler()
+    clocks.start()
+    dev_ms, wall_ms, launches = time_decode(engine, torch, K, B, kv_start, args.steps, args.warmup, True)
+    clock_rec = clocks.stop()
+    value = B * 1e3 / dev_ms
+    e2e = B * 1e3 / wall_ms
+    kv_mid = kv_start + args.warmup + args.steps // 2
+    step_bytes = decode_flops_and_bytes(engine, B, kv_mid)
+    achieved = step_bytes / (dev_ms * 1e-3) / 1e9
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            ms, _, _ = time_decode(engine, torch, K, b, kv_start, max(4, args.steps // 2), args.warmup, False)
+            points[f"decode_b{b}"] = round(b * 1e3 / ms, 1)
+    T = args.prefill_tokens
+    pre_ms = time_prefill(engine, torch, T, 1, 3)
+    flops = prefill_flops(cfg, args.layers, T)
+    err = K.gemm_tc_error() if hasattr(K, "gemm_tc_error") else 0
+    line = {
+        "metric": "decode tok/s (Qwen3-8B layer sizes, bf16, batch 8)", "value": round(value, 1), "unit": "tok/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights (seed 2), token ids from a fixed pattern, cache of random keys and values",
+        "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_of_model": 36, "hidden": 4096, "heads": 32,
+                   "kv_heads": 8, "head_dim": 128, "intermediate": 12288, "vocab": 151936, "global_batch": B,
+                   "seq_len": context, "kv_len_at_first_timed_step": kv_start + args.warmup, "prefill_tokens": T,
+                   "parallelism": "single_gpu", "l2": "inputs_larger_than_l2", "cache_fill": "random",
+                   "peaks": pk["source"]},
+        "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": engine.h2d_bytes // max(1, engine_steps(engine)),
+                "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": launches,
+        "prefill": {"value": round(T * 1e3 / pre_ms, 1), "tokens": T, "ms": round(pre_ms, 3),
+                    "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points, "clocks": clock_rec, "kernel_error": err,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def engine_steps(engine):
+    return getattr(engine, "steps_run", 0) or 1
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=36, help="fewer than 36 only where time needs it; both numbers are reported")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "berniehans/titan is a Rust workspace (cargo is not installed) "
+                          "that needs GGUF Q4_K weights and NVRTC for compute_86; it cannot be installed or run offline here"}))
+        return 0
+    if args.gpus != 1:
+        print("titan_b200 is a single-GPU library: bench.py runs at --gpus 1 only")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

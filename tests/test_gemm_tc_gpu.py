@@ -1,0 +1,80 @@
+"""The tcgen05 matrix product against float64, at sizes that fill tiles exactly and at sizes that do
+not (ragged M, N and K; vocabulary-like N; strided views), in both operand orders and all epilogues."""
+import pytest
+import torch
+
+from helpers import rel_l2
+from plain import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from titan_b200 import kernels
+    kernels.lib()
+    return kernels
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+SHAPES = [(1, 128, 64), (5, 384, 256), (16, 200, 72), (17, 1000, 520), (40, 130, 4096), (64, 509, 96), (100, 256, 128),
+          (128, 256, 64), (200, 300, 1032), (333, 1000, 200), (256, 128, 512)]
+
+
+@pytest.mark.parametrize("M,N,Kd", SHAPES)
+def test_all_epilogues(K, M, N, Kd):
+    g = torch.Generator().manual_seed(M + N + Kd)
+    x = torch.randn(M, Kd, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, Kd, generator=g) * 0.1).to(torch.bfloat16)
+    want = P.linear(x.float(), w.float())
+    xd, wd = x.cuda(), w.cuda()
+    n8 = -(-N // 8) * 8
+    out = torch.zeros(M, n8, dtype=torch.bfloat16, device="cuda")[:, :N]
+    K.gemm_tc(xd, wd, out, K.EPI_STORE, stream())
+    assert K.gemm_tc_error() == 0
+    assert rel_l2(out.float().cpu(), want) < 4e-3
+    f = torch.zeros(M, n8, device="cuda")[:, :N]
+    K.gemm_tc(xd, wd, f, K.EPI_F32, stream())
+    assert rel_l2(f.cpu(), want) < 1e-5
+    res = torch.randn(M, N, generator=g)
+    acc = torch.zeros(M, n8, device="cuda")[:, :N]
+    acc.copy_(res)
+    K.gemm_tc(xd, wd, acc, K.EPI_ADD, stream())
+    assert rel_l2(acc.cpu(), res + want) < 1e-5
+    if M < 128 and Kd >= 512:
+        acc2 = torch.zeros(M, n8, device="cuda")[:, :N]
+        acc2.copy_(res)
+        K.gemm_tc(xd, wd, acc2, K.EPI_ADD, stream(), splits=1)       # one slice: no atomics
+        assert rel_l2(acc2.cpu(), res + want) < 1e-5
+    if N % 2 == 0:
+        h8 = -(-(N // 2) // 8) * 8
+        act = torch.zeros(M, h8, dtype=torch.bfloat16, device="cuda")[:, :N // 2]
+        K.gemm_tc(xd, wd, act, K.EPI_SWIGLU, stream())
+        assert rel_l2(act.float().cpu(), P.swiglu(want[:, 0::2], want[:, 1::2])) < 6e-3
+    assert K.gemm_tc_error() == 0
+
+
+def test_strided_input_rows(K):
+    g = torch.Generator().manual_seed(1)
+    big = torch.randn(150, 400, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(96, 200, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    for rows in (150, 20):
+        x = big[:rows, 8:208]
+        out = torch.zeros(rows, 96, device="cuda")
+        K.gemm_tc(x, w, out, K.EPI_F32, stream())
+        assert rel_l2(out.cpu(), P.linear(x.float().cpu(), w.float().cpu())) < 1e-5
+    assert K.gemm_tc_error() == 0
+
+
+def test_refuses_misaligned(K):
+    x = torch.zeros(4, 12, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(8, 12, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(4, 8, device="cuda")
+    assert not K.gemm_tc_accepts(x, w, out, K.EPI_F32)
+    with pytest.raises(K.KernelError, match="multiples of 8"):
+        K.gemm_tc(x, w, out, K.EPI_F32, stream())
+    with pytest.raises(K.KernelError, match="bfloat16"):
+        K.gemm_tc(x.float(), w.float(), out, K.EPI_F32, stream())

@@ -1,0 +1,236 @@
+"""Each part alone, built from its spec, against the plain functions; and a toy mixer with state of
+its own, defined here, registered, built and stepped without touching the library's files."""
+import dataclasses
+import math
+
+import pytest
+import torch
+
+from helpers import TOL, random_tokens, rel_l2
+from plain import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def make_ctx(entries, starts, dtype):
+    from titan_b200 import kernels as K
+    from titan_b200.engine.batch import StepContext, StepLayout
+    lay = StepLayout(entries, starts, "cuda")
+    return StepContext(lay, K.current_stream(), dtype, torch.device("cuda"), {}, {})
+
+
+def bind(part, prefix, weights, dtype):
+    from titan_b200.weights import held_dtype
+    specs = {w.name: w for w in part.weight_specs(prefix)}
+    part.bind(lambda rel: weights[prefix + rel].to("cuda", held_dtype(specs[prefix + rel].role, dtype)).contiguous())
+
+
+def rand_for(part, prefix, seed, std=0.1):
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for w in part.weight_specs(prefix):
+        t = torch.randn(w.shape, generator=g) * (0.1 if w.role == "vector" else std) + (1.0 if w.role == "vector" else 0.0)
+        out[w.name] = t.to(torch.bfloat16).float()
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_and_feed_forward_parts(dtype):
+    from titan_b200.config import FeedForwardSpec, NormSpec
+    from titan_b200.engine.batch import StepEntry
+    from titan_b200.parts import FEED_FORWARDS, NORMS
+    H, F, T = 72, 200, 11
+    norm = NORMS.build(NormSpec("rmsnorm", H, 2e-4, "n.weight"))
+    ffn = FEED_FORWARDS.build(FeedForwardSpec("gated_mlp", H, F, prefix="ff."))
+    wn, wf = rand_for(norm, "x.", 1), rand_for(ffn, "x.", 2)
+    bind(norm, "x.", wn, DT[dtype])
+    bind(ffn, "x.", wf, DT[dtype])
+    ctx = make_ctx([StepEntry(0, [0] * T, [])], [0], DT[dtype])
+    x = torch.randn(T, H, generator=torch.Generator().manual_seed(3))
+    h = norm.forward(x.cuda(), ctx)
+    want_h = P.rms_norm(x, wn["x.n.weight"], 2e-4)
+    assert h.dtype == DT[dtype] and rel_l2(h.float().cpu(), want_h) < TOL[dtype]
+    out = x.clone().cuda()
+    ffn.forward(h, ctx, out)
+    w = {"mlp." + k.split("ff.")[1]: v for k, v in wf.items()}
+    want = x + P.mlp_part(w, "", h.float().cpu())
+    assert rel_l2(out.cpu(), want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,qk_norm,rope", [(None, True, True), (24, False, True), (None, True, False)])
+def test_attention_mixer_alone(dtype, window, qk_norm, rope):
+    """The mixer with its own cache: a prompt for two sequences, then single tokens; options that the
+    test models never use (no head norm, no rotation) are built from the spec too."""
+    from titan_b200.cache import SequenceCache
+    from titan_b200.config import MixerSpec, NormSpec, PositionSpec
+    from titan_b200.engine.batch import StepEntry
+    from titan_b200.parts import MIXERS
+    H, nh, nkv, hd = 56, 6, 3, 32
+    spec = MixerSpec("attention", H, nh, nkv, hd, window=window,
+                     qk_norm=NormSpec("rmsnorm", hd, 1e-4, "{}_norm.weight") if qk_norm else None,
+                     position=PositionSpec("rope", hd, 5000.0) if rope else PositionSpec("none"), prefix="att.")
+    mixer = MIXERS.build(spec)
+    w = rand_for(mixer, "", 7, std=0.15)
+    bind(mixer, "", w, DT[dtype])
+    cache = SequenceCache([mixer.cache_need()], 512, 4, 256, DT[dtype], "cuda")
+    lens = [100, 37]
+    g = torch.Generator().manual_seed(9)
+    xs = [torch.randn(n, H, generator=g).to(torch.bfloat16).float() for n in lens]
+
+    def plain(x):
+        T = x.shape[0]
+        pos = torch.arange(T)
+        q = P.linear(x, w["att.q_proj.weight"]).view(T, nh, hd)
+        k = P.linear(x, w["att.k_proj.weight"]).view(T, nkv, hd)
+        v = P.linear(x, w["att.v_proj.weight"]).view(T, nkv, hd)
+        if qk_norm:
+            q, k = P.rms_norm(q, w["att.q_norm.weight"], 1e-4), P.rms_norm(k, w["att.k_norm.weight"], 1e-4)
+        if rope:
+            q, k = P.rope_neox(q, pos, 5000.0), P.rope_neox(k, pos, 5000.0)
+        return P.linear(P.causal_attention(q, k, v, window).reshape(T, nh * hd), w["att.o_proj.weight"])
+    want = [plain(x) for x in xs]
+    slots = [cache.alloc_slot(), cache.alloc_slot()]
+    cut = [80, 30]
+    cache.reserve({s: n for s, n in zip(slots, lens)})
+    ctx = make_ctx([StepEntry(s, [0] * c, []) for s, c in zip(slots, cut)], [0, 0], DT[dtype])
+    h = torch.cat([x[:c] for x, c in zip(xs, cut)]).to(DT[dtype]).cuda()
+    out = torch.zeros(sum(cut), H, device="cuda")
+    mixer.forward(h, ctx, cache.view_for_layer(0), out)
+    got = [[out[:80].cpu()], [out[80:].cpu()]]
+    at = list(cut)
+    while any(a < n for a, n in zip(at, lens)):
+        live = [i for i in range(2) if at[i] < lens[i]]
+        ctx = make_ctx([StepEntry(slots[i], [0], []) for i in live], [at[i] for i in live], DT[dtype])
+        h = torch.stack([xs[i][at[i]] for i in live]).to(DT[dtype]).cuda()
+        out = torch.zeros(len(live), H, device="cuda")
+        mixer.forward(h, ctx, cache.view_for_layer(0), out)
+        for k, i in enumerate(live):
+            got[i].append(out[k:k + 1].cpu())
+            at[i] += 1
+    for i in range(2):
+        assert rel_l2(torch.cat(got[i]), want[i]) < TOL[dtype]
+
+
+# --------------------------------------------------------------------------- #
+# A toy mixer with fixed-size state, a toy architecture around it: all defined here.
+# --------------------------------------------------------------------------- #
+def toy_parts():
+    from titan_b200.cache import CacheNeed
+    from titan_b200.parts import MIXERS, Mixer
+    from titan_b200.weights import WeightSpec
+
+    class DecayMixer(Mixer):
+        """state_t = decay * state_{t-1} + x_t . W^T ; output = state_t (per sequence, fixed size)."""
+
+        def __init__(self, spec):
+            self.spec, self.decay = spec, spec.option("decay", 0.5)
+
+        def cache_need(self):
+            return CacheNeed("state", state_shape=(self.spec.hidden_size,))
+
+        def weight_specs(self, prefix):
+            return [WeightSpec(prefix + self.spec.prefix + "w.weight", (self.spec.hidden_size, self.spec.hidden_size))]
+
+        def bind(self, get):
+            self.w = get(self.spec.prefix + "w.weight")
+
+        def forward(self, h, ctx, cache, out):
+            group, index = cache
+            state = group.layer_storage(index)                      # [slots, H] float32
+            lay = ctx.layout
+            u = h.float() @ self.w.float().t()
+            starts, slots = lay.q_start.tolist(), lay.slot_of_seq.tolist()
+            for b, slot in enumerate(slots):                        # a sequence's tokens in order
+                s = state[slot]
+                for t in range(starts[b], starts[b + 1]):
+                    s = self.decay * s + u[t]
+                    out[t] += s
+                state[slot] = s
+    MIXERS.register("toy_decay", DecayMixer)
+
+
+class ToyConfig:
+    """Layers alternate between the toy mixer and attention; layer 2 runs twice."""
+
+    def __init__(self, d):
+        self.d = d
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d)
+
+    def to_dict(self):
+        return dict(self.d)
+
+    def to_model_spec(self):
+        from titan_b200.config import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec
+        d = self.d
+        H = d["width"]
+        layers = []
+        for i in range(d["depth"]):
+            if i % 2 == 0:
+                mixer = MixerSpec("toy_decay", H, prefix="mix.", extra=(("decay", d["decay"]),))
+            else:
+                mixer = MixerSpec("attention", H, 4, 2, 16, position=PositionSpec("rope", 16, 100.0), prefix="attn.")
+            layers.append(LayerSpec(i, "pre_norm", mixer, FeedForwardSpec("gated_mlp", H, d["ff"], prefix="ff."),
+                                    NormSpec("rmsnorm", H, 1e-5, "n1.weight"), NormSpec("rmsnorm", H, 1e-5, "n2.weight"), f"blocks.{i}."))
+        return ModelSpec("ToyForCausalLM", H, d["vocab"], tuple(layers), tuple(d["order"]),
+                         NormSpec("rmsnorm", H, 1e-5, "final.weight"), embedding="embed.weight", lm_head=None)
+
+
+def toy_plain(d, w, tokens):
+    x = w["embed.weight"][torch.tensor(tokens)]
+    T, pos = len(tokens), torch.arange(len(tokens))
+    for i in d["order"]:
+        p = f"blocks.{i}."
+        h = P.rms_norm(x, w[p + "n1.weight"], 1e-5)
+        if i % 2 == 0:
+            u, s, rows = P.linear(h, w[p + "mix.w.weight"]), torch.zeros(d["width"]), []
+            for t in range(T):
+                s = d["decay"] * s + u[t]
+                rows.append(s)
+            x = x + torch.stack(rows)
+        else:
+            q = P.rope_neox(P.linear(h, w[p + "attn.q_proj.weight"]).view(T, 4, 16), pos, 100.0)
+            k = P.rope_neox(P.linear(h, w[p + "attn.k_proj.weight"]).view(T, 2, 16), pos, 100.0)
+            v = P.linear(h, w[p + "attn.v_proj.weight"]).view(T, 2, 16)
+            x = x + P.linear(P.causal_attention(q, k, v).reshape(T, 64), w[p + "attn.o_proj.weight"])
+        h = P.rms_norm(x, w[p + "n2.weight"], 1e-5)
+        x = x + P.mlp_part({k.replace(p + "ff.", "mlp."): v for k, v in w.items() if k.startswith(p + "ff.")}, "", h)
+    return P.linear(P.rms_norm(x, w["final.weight"], 1e-5), w["embed.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_mixer_with_state_registers_builds_and_steps(dtype):
+    from titan_b200 import Engine, StepEntry, register_architecture
+    from titan_b200.parts import declare_weights
+    toy_parts()
+    register_architecture("ToyForCausalLM", ToyConfig)
+    d = {"architectures": ["ToyForCausalLM"], "width": 48, "depth": 3, "ff": 80, "vocab": 120, "decay": 0.6, "order": [0, 1, 2, 2, 1]}
+    cfg = ToyConfig(d)
+    g = torch.Generator().manual_seed(4)
+    w = {}
+    for s in declare_weights(cfg.to_model_spec()):
+        t = torch.randn(s.shape, generator=g) * (0.1 if s.role == "vector" else 0.12) + (1.0 if s.role == "vector" else 0.0)
+        w[s.name] = t.to(torch.bfloat16)
+    e = Engine.from_tensors(cfg, w, dtype=dtype, max_tokens=512, max_slots=3)
+    assert len(e.cache.groups) == 2 and len(e.model.cache_needs()) == 5      # one cache per run of the order
+    w32 = {k: v.float() for k, v in w.items()}
+    reqs = [random_tokens(50, 120, 1), random_tokens(21, 120, 2)]
+    want = [toy_plain(d, w32, r) for r in reqs]
+    for round_ in range(2):                                                     # slots (and their state) are used again
+        slots = [e.alloc_slot(), e.alloc_slot()]
+        out = e.step([StepEntry(slots[0], reqs[0][:30], list(range(30))), StepEntry(slots[1], reqs[1][:5], list(range(5)))])
+        got = [[out[:30]], [out[30:]]]
+        at = [30, 5]
+        while any(a < len(r) for a, r in zip(at, reqs)):
+            live = [i for i in range(2) if at[i] < len(reqs[i])]
+            out = e.step([StepEntry(slots[i], [reqs[i][at[i]]], [0]) for i in live])
+            for k, i in enumerate(live):
+                got[i].append(out[k:k + 1])
+                at[i] += 1
+        for i in range(2):
+            assert rel_l2(torch.cat(got[i]).cpu(), want[i]) < TOL[dtype]
+            e.free_slot(slots[i])

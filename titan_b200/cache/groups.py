@@ -62,6 +62,8 @@ class KVGroup:
         self.storage = torch.empty((len(layers), 2, num_pages, need.num_kv_heads, page_size, need.head_dim),
                                    dtype=dtype, device=device)
         self.table_host = torch.zeros((max_slots, self.table_width), dtype=torch.int32)
+        if torch.device(device).type == "cuda":
+            self.table_host = self.table_host.pin_memory()     # so that a page's table entry is copied without a sync
         self.table = torch.zeros((max_slots, self.table_width), dtype=torch.int32, device=device)
 
     # -- pages ---------------------------------------------------------- #
@@ -79,7 +81,7 @@ class KVGroup:
         first = len(have)
         have.extend(self.pool.take_many(n))
         self.table_host[slot, first:len(have)] = torch.tensor(have[first:], dtype=torch.int32)
-        self.table[slot, first:len(have)].copy_(self.table_host[slot, first:len(have)], non_blocking=False)
+        self.table[slot, first:len(have)].copy_(self.table_host[slot, first:len(have)], non_blocking=True)
 
     def release(self, slot: int) -> None:
         for p in self.pages_of.pop(slot, []):

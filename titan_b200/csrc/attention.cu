@@ -158,6 +158,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(AttnArgs a)
     const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
     const int hd = a.hd, group = a.nh / a.nkv;
     const int len = a.batch.kv_len[b];
+    if (split * a.chunk >= len) return;             // the merge reads ceil(len / chunk) splits only
     const int pos = len - 1;
     const int slot = a.batch.slot_of_seq[b];
     const int wlo = a.window > 0 ? max(0, pos - a.window + 1) : 0;

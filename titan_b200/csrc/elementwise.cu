@@ -206,3 +206,44 @@ extern "C" int tb_kv_append(const void* kv, int stride, int dtype, const TbKvVie
     TB_CHECK_LAUNCH("kv_append");
     return 0;
 }
+
+// ------------------------------------------------------------------ device-side step bookkeeping
+// A captured decode step must not depend on host values that change from step to step.  Before the
+// blocks run, this kernel derives the step's layout from the per-slot state: the token to feed
+// (the slot's last sampled token, or one the host has put into ``tokens``), its position, and the
+// cache length after the step.  berniehans/titan keeps pos_dev and token_id_dev for the same reason
+// (engine/engine-core/src/forward_driver.rs:2444-2452, kernels/gemm_quant.cu:2570-2587).
+__global__ void decode_prepare_kernel(const int* __restrict__ slot_of_seq, const int* __restrict__ seq_len,
+                                      const int* __restrict__ last_token, int feed_last, int* tokens, int* pos_of,
+                                      int* start_pos, int* kv_len, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    const int slot = slot_of_seq[b], len = seq_len[slot];
+    if (feed_last) tokens[b] = last_token[slot];
+    pos_of[b] = len;
+    start_pos[b] = len;
+    kv_len[b] = len + 1;
+}
+
+extern "C" int tb_decode_prepare(const int* slot_of_seq, const int* seq_len, const int* last_token, int feed_last,
+                                 int* tokens, int* pos_of, int* start_pos, int* kv_len, int B, cudaStream_t stream) {
+    TB_REQUIRE(B > 0, "decode_prepare: no sequences");
+    decode_prepare_kernel<<<(B + 127) / 128, 128, 0, stream>>>(slot_of_seq, seq_len, last_token, feed_last, tokens,
+                                                               pos_of, start_pos, kv_len, B);
+    TB_CHECK_LAUNCH("decode_prepare");
+    return 0;
+}
+
+// seq_len[slot_of_seq[b]] = kv_len[b]: the device copy of the lengths after a step.
+__global__ void commit_lengths_kernel(const int* __restrict__ slot_of_seq, const int* __restrict__ kv_len,
+                                      int* seq_len, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < B) seq_len[slot_of_seq[b]] = kv_len[b];
+}
+
+extern "C" int tb_commit_lengths(const int* slot_of_seq, const int* kv_len, int* seq_len, int B, cudaStream_t stream) {
+    TB_REQUIRE(B > 0, "commit_lengths: no sequences");
+    commit_lengths_kernel<<<(B + 127) / 128, 128, 0, stream>>>(slot_of_seq, kv_len, seq_len, B);
+    TB_CHECK_LAUNCH("commit_lengths");
+    return 0;
+}

@@ -1,0 +1,462 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05) of sm_100a:
+//     out = epilogue(X[M,K] . W[N,K]^T),  float32 accumulation in tensor memory.
+//
+// One CTA computes one 128 x BN tile of D = A . B^T, where A and B are both K-major:
+//   plain mode  A = X (rows = tokens), B = W (rows = outputs):  D[m][n]     (prompts, M >= 128)
+//   swap mode   A = W,                 B = X:                   D[n][m]     (decode: a few tokens)
+// so that in decode the 128-row side of the instruction is filled by weight rows and the batch
+// is the narrow side (BN = 16..128).  Swap mode can also cut K into slices (grid.z), each CTA
+// adding its partial sum into a float32 output with atomics, to put enough CTAs on the machine
+// when N / 128 is small.
+//
+// Data path: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill outside the tensor) into a
+// ring of shared-memory stages -> tcgen05.mma.cta_group::1.kind::f16 issued by one thread, four
+// K=16 steps per 64-wide stage -> accumulator in TMEM -> tcgen05.ld by four epilogue warps.
+// Warp 0 produces, warp 1 allocates TMEM and issues MMAs, warps 2..5 run the epilogue.
+// No cluster launch, no multicast.
+//
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the thread records an error code
+// in a device word (read with tb_gemm_tc_error) and goes on, so the kernel always ends and frees
+// its tensor memory; the result is then invalid and the host says so.
+//
+// berniehans/titan's counterpart is gemm_q4k_batched_kernel (engine/engine-cuda/kernels/
+// gemm_quant.cu:3365-3499), a scalar-FMA warp-per-column kernel with the residual in its
+// epilogue (:3489-3493); it has no tensor-core path.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "gemm.h"
+
+namespace {
+
+constexpr int BM = 128;          // rows of A per tile = M of the instruction
+constexpr int BK = 64;           // bf16 elements per stage row = 128 bytes = one swizzle span
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
+
+__device__ unsigned int g_tc_error = 0;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; on expiry records ``code`` and returns.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, unsigned code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_test(bar, parity)) return;
+        if (i > 64) __nanosleep(32);
+        if ((i & 1023u) == 1023u && *(volatile unsigned int*)&g_tc_error) break;   // another wait has given up already
+    }
+    atomicCAS(&g_tc_error, 0u, code);
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread = lane (row), v[j] = column j.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled:
+// start address >> 4 in bits 0-13, leading byte offset (unused for swizzled K-major) 1 in 16-29,
+// stride byte offset 1024 >> 4 (eight rows) in 32-45, version 1 in 46-47, swizzle mode 2 (128 B) in 61-63.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: D float32 (1 << 4), A and B bfloat16 (1 << 7, 1 << 10), both
+// K-major (bits 15, 16 clear), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&p);
+}
+
+struct TcArgs {
+    void* out;
+    int rows_a;      // valid rows of A (M in plain mode, N in swap mode)
+    int rows_b;      // valid rows of B
+    int K;
+    int ldo;         // row stride of out in elements
+    int k_blocks_per_split;
+    int atomic;      // ADD epilogue through atomics (several K slices)
+};
+
+template <int BN> constexpr int stages_for() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : 6); }
+template <int BN> constexpr int tmem_cols_for() { return BN < 32 ? 32 : BN; }
+template <int BN> constexpr size_t smem_for() {
+    return 1024 /*alignment slack*/ + (size_t)stages_for<BN>() * (BM * BK * 2 + BN * BK * 2) + 256;
+}
+
+// Epilogue of one 32-column chunk held by one thread (row ``r`` of the tile).
+// Plain mode: row = token m, columns = outputs n0 + j.   Swap mode: row = output n, columns = tokens.
+template <int EPI, bool SWAP, int NV>
+__device__ __forceinline__ void epilogue_chunk(const float* v, const TcArgs& a, int row, int col0, int lane) {
+    if (!SWAP) {
+        const int m = row;
+        if (m >= a.rows_a) return;
+        if (EPI == TB_EPI_SWIGLU) {
+            __nv_bfloat16* o = (__nv_bfloat16*)a.out + (size_t)m * a.ldo + col0 / 2;
+#pragma unroll
+            for (int j = 0; j < NV; j += 2)
+                if (col0 + j + 1 < a.rows_b) o[j / 2] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+        } else if (EPI == TB_EPI_STORE) {
+            __nv_bfloat16* o = (__nv_bfloat16*)a.out + (size_t)m * a.ldo + col0;
+            if (col0 + NV <= a.rows_b) {            // whole chunk inside: 16-byte stores (ldo and col0 are multiples of 8)
+#pragma unroll
+                for (int j = 0; j < NV; j += 8) {
+                    uint4 pk;
+                    pk.x = pack_bf16(v[j], v[j + 1]); pk.y = pack_bf16(v[j + 2], v[j + 3]);
+                    pk.z = pack_bf16(v[j + 4], v[j + 5]); pk.w = pack_bf16(v[j + 6], v[j + 7]);
+                    *reinterpret_cast<uint4*>(o + j) = pk;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < NV; ++j)
+                    if (col0 + j < a.rows_b) o[j] = __float2bfloat16_rn(v[j]);
+            }
+        } else {
+            float* o = (float*)a.out + (size_t)m * a.ldo + col0;
+            if (col0 + NV <= a.rows_b && !a.atomic && (a.ldo & 3) == 0) {
+#pragma unroll
+                for (int j = 0; j < NV; j += 4) {
+                    float4 r = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    if (EPI == TB_EPI_ADD) {
+                        const float4 old = *reinterpret_cast<const float4*>(o + j);
+                        r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
+                    }
+                    *reinterpret_cast<float4*>(o + j) = r;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    if (col0 + j >= a.rows_b) continue;
+                    if (EPI == TB_EPI_F32) o[j] = v[j];
+                    else if (a.atomic) atomicAdd(o + j, v[j]);
+                    else o[j] += v[j];
+                }
+            }
+        }
+    } else {
+        const int n = row;
+        const bool n_ok = n < a.rows_a;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int m = col0 + j;
+            if (EPI == TB_EPI_SWIGLU) {
+                const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);      // the odd lane holds the pair's up value
+                if (m < a.rows_b && n_ok && !(lane & 1))
+                    ((__nv_bfloat16*)a.out)[(size_t)m * a.ldo + n / 2] = __float2bfloat16_rn(silu_mul(v[j], up));
+            } else if (m < a.rows_b && n_ok) {
+                if (EPI == TB_EPI_STORE) ((__nv_bfloat16*)a.out)[(size_t)m * a.ldo + n] = __float2bfloat16_rn(v[j]);
+                else if (EPI == TB_EPI_F32) ((float*)a.out)[(size_t)m * a.ldo + n] = v[j];
+                else if (a.atomic) atomicAdd((float*)a.out + (size_t)m * a.ldo + n, v[j]);
+                else ((float*)a.out)[(size_t)m * a.ldo + n] += v[j];
+            }
+        }
+    }
+}
+
+template <int BN, int EPI, bool SWAP>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs a) {
+    constexpr int STAGES = stages_for<BN>();
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr uint32_t TMEM_COLS = tmem_cols_for<BN>();
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // swizzled tiles want 1024-byte alignment
+    uint8_t* smem_a = base;
+    uint8_t* smem_b = base + STAGES * A_BYTES;
+    uint64_t* full = (uint64_t*)(base + STAGES * (A_BYTES + B_BYTES));
+    uint64_t* empty = full + STAGES;
+    uint64_t* accum = empty + STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(accum + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_a = blockIdx.y;                          // tile index along A's rows
+    const int tile_b = blockIdx.x;                          // tile index along B's rows
+    const int kb_total = (a.K + BK - 1) / BK;
+    const int kb0 = blockIdx.z * a.k_blocks_per_split;
+    const int kb1 = min(kb_total, kb0 + a.k_blocks_per_split);
+    const int n_kb = kb1 - kb0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (n_kb > 0) {
+        if (warp == 0) {
+            if (lane == 0) {
+                for (int i = 0; i < n_kb; ++i) {
+                    const int s = i % STAGES, round = i / STAGES;
+                    if (round > 0) mbar_wait(empty + s, (round - 1) & 1, 1);
+                    mbar_expect_tx(full + s, A_BYTES + B_BYTES);
+                    tma_load_2d(smem_a + s * A_BYTES, &map_a, full + s, (kb0 + i) * BK, tile_a * BM);
+                    tma_load_2d(smem_b + s * B_BYTES, &map_b, full + s, (kb0 + i) * BK, tile_b * BN);
+                }
+            }
+        } else if (warp == 1) {
+            if (lane == 0) {
+                constexpr uint32_t idesc = instr_desc(BM, BN);
+                for (int i = 0; i < n_kb; ++i) {
+                    const int s = i % STAGES, round = i / STAGES;
+                    mbar_wait(full + s, round & 1, 2);
+                    tc_fence_after();
+                    const uint64_t da = smem_desc(smem_u32(smem_a + s * A_BYTES));
+                    const uint64_t db = smem_desc(smem_u32(smem_b + s * B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)     // 32 bytes per K step: +2 in the descriptor's address field
+                        tc_mma(tmem, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(empty + s);                     // the stage is free once these MMAs have read it
+                }
+                tc_commit(accum);
+            }
+        } else {
+            mbar_wait(accum, 0, 3);
+            tc_fence_after();
+            const int quarter = warp & 3;                     // a warp reads TMEM lanes 32 * (warp % 4) ..
+            const int row = tile_a * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16);
+            if (BN >= 32) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    float v[32];
+                    tmem_ld32(taddr + c, v);
+                    epilogue_chunk<EPI, SWAP, 32>(v, a, row, tile_b * BN + c, lane);
+                }
+            } else {
+                float v[16];
+                tmem_ld16(taddr, v);
+                epilogue_chunk<EPI, SWAP, 16>(v, a, row, tile_b * BN, lane);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; long long rows, cols, stride; int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && stride == o.stride && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        for (long long v : {k.rows, k.cols, k.stride, (long long)k.box_rows}) h = h * 1000003u ^ (size_t)v;
+        return h;
+    }
+};
+
+// A [rows][cols] bf16 matrix with row stride ``stride`` elements, boxes of box_rows x 64, 128-byte swizzle.
+int make_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long stride, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    const MapKey key{ptr, rows, cols, stride, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    TB_REQUIRE(fn, "gemm_tc: the driver does not export cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)stride * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TB_REQUIRE(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with code %d (rows=%lld cols=%lld stride=%lld)", (int)r, rows, cols, stride);
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+template <int BN, int EPI, bool SWAP>
+int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t stream) {
+    static bool configured = false;
+    constexpr size_t smem = smem_for<BN>();
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        TB_REQUIRE(e == cudaSuccess, "gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    gemm_tc_kernel<BN, EPI, SWAP><<<grid, THREADS, smem, stream>>>(ma, mb, a);
+    return 0;
+}
+
+template <int BN, bool SWAP>
+int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t stream) {
+    switch (epi) {
+        case TB_EPI_STORE: return launch_tc<BN, TB_EPI_STORE, SWAP>(ma, mb, a, grid, stream);
+        case TB_EPI_F32: return launch_tc<BN, TB_EPI_F32, SWAP>(ma, mb, a, grid, stream);
+        case TB_EPI_ADD: return launch_tc<BN, TB_EPI_ADD, SWAP>(ma, mb, a, grid, stream);
+        case TB_EPI_SWIGLU: return launch_tc<BN, TB_EPI_SWIGLU, SWAP>(ma, mb, a, grid, stream);
+    }
+    tb_set_error("gemm_tc: unknown epilogue %d", epi);
+    return 1;
+}
+
+}  // namespace
+
+// Reads and clears the error word of the tensor-core kernels (0: none; 1, 2, 3: a wait of the
+// producer, the MMA issuer or the epilogue ran out).  Synchronises the device.
+extern "C" int tb_gemm_tc_error() {
+    unsigned int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(v)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(zero));
+    return (int)v;
+}
+
+// 0 if tb_gemm_tc can run these sizes, else 1 with the reason in tb_last_error().
+extern "C" int tb_gemm_tc_check(int M, int N, int K, int ldx, int ldo, int epi, const void* X, const void* W, const void* out) {
+    TB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tc: sizes must be positive");
+    TB_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_tc: K=%d and the row stride %d of X must be multiples of 8 (16-byte TMA rows)", K, ldx);
+    TB_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_tc: operands must be 16-byte aligned");
+    TB_REQUIRE(epi != TB_EPI_SWIGLU || N % 2 == 0, "gemm_tc: the SwiGLU epilogue needs an even N");
+    TB_REQUIRE(epi < 0 || ((uintptr_t)out & 15) == 0, "gemm_tc: the output must be 16-byte aligned");
+    const int unit = (epi == TB_EPI_STORE || epi == TB_EPI_SWIGLU) ? 8 : 4;
+    TB_REQUIRE(ldo % unit == 0, "gemm_tc: the row stride %d of the output must be a multiple of %d", ldo, unit);
+    return 0;
+}
+
+// splits: K slices (swap mode, ADD epilogue only); 0 = choose.
+extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N, int K, int ldx, int ldo, int epi,
+                          int splits, cudaStream_t stream) {
+    if (tb_gemm_tc_check(M, N, K, ldx, ldo, epi, X, W, out)) return 1;
+    const bool swap = M < 128;
+    const int kb = (K + BK - 1) / BK;
+    CUtensorMap ma, mb;
+    TcArgs a;
+    a.out = out; a.K = K; a.ldo = ldo; a.k_blocks_per_split = kb; a.atomic = 0;
+    int rc = 0;
+    if (!swap) {
+        const int bn = N >= 256 ? 256 : 128;
+        a.rows_a = M; a.rows_b = N;
+        if (make_map(&ma, X, M, K, ldx, BM) || make_map(&mb, W, N, K, K, bn)) return 1;
+        dim3 grid((N + bn - 1) / bn, (M + BM - 1) / BM, 1);
+        TB_REQUIRE(grid.y <= 65535, "gemm_tc: M=%d is too large for one launch", M);
+        rc = bn == 256 ? launch_epi<256, false>(epi, ma, mb, a, grid, stream) : launch_epi<128, false>(epi, ma, mb, a, grid, stream);
+    } else {
+        const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+        a.rows_a = N; a.rows_b = M;
+        const int tiles = (N + BM - 1) / BM;
+        int s = 1;
+        if (epi == TB_EPI_ADD) {
+            s = splits > 0 ? splits : (2 * 148 + tiles - 1) / tiles;
+            const int max_s = kb / 4 > 0 ? kb / 4 : 1;              // at least four 64-wide blocks per slice
+            s = s < 1 ? 1 : (s > max_s ? max_s : s);
+        }
+        a.k_blocks_per_split = (kb + s - 1) / s;
+        s = (kb + a.k_blocks_per_split - 1) / a.k_blocks_per_split;  // no empty slice
+        a.atomic = s > 1;
+        if (make_map(&ma, W, N, K, K, BM) || make_map(&mb, X, M, K, ldx, bn)) return 1;
+        dim3 grid(1, tiles, s);
+        TB_REQUIRE(tiles <= 65535, "gemm_tc: N=%d is too large for one launch", N);
+        switch (bn) {
+            case 16: rc = launch_epi<16, true>(epi, ma, mb, a, grid, stream); break;
+            case 32: rc = launch_epi<32, true>(epi, ma, mb, a, grid, stream); break;
+            case 64: rc = launch_epi<64, true>(epi, ma, mb, a, grid, stream); break;
+            default: rc = launch_epi<128, true>(epi, ma, mb, a, grid, stream); break;
+        }
+    }
+    if (rc) return rc;
+    TB_CHECK_LAUNCH("gemm_tc");
+    return 0;
+}

@@ -25,6 +25,7 @@ from ..config import load_config
 from ..sampling import DeviceSampler, SamplerParams
 from ..weights import DictWeights, FolderWeights, RandomWeights
 from .batch import StepContext, StepEntry, StepLayout
+from .decode_graph import DecodeGraph
 from .generate import GenerationRequest, GenerationResult, generate, round_up
 from .model import DecoderModel
 
@@ -45,6 +46,7 @@ class EngineOptions:
     max_batch: int = 64               # sequences per generation batch
     gemm: str = "fast"                # "plain": CUDA-core matrix products even in bfloat16
     attn_chunk: int = 256             # keys per split of decode attention
+    decode_graphs: bool = True        # replay single-token steps as CUDA graphs once a batch size has run eagerly
     device: str = "cuda:0"
 
 
@@ -71,6 +73,10 @@ class Engine:
         self.step_options = {"gemm": options.gemm, "attn_chunk": options.attn_chunk}
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self.steps_run = 0
+        self.graph_launches = 0                   # launcher calls replayed through graphs
+        self._graphs: Dict[int, DecodeGraph] = {}
+        self._ran_eagerly = set()
 
     # -- construction ------------------------------------------------------- #
     @classmethod
@@ -147,9 +153,11 @@ class Engine:
             raise StepError(str(err)) from None
         layout = StepLayout(entries, starts, self.device)
         self.h2d_bytes += layout.h2d_bytes
+        self.steps_run += 1
         ctx = self._context(layout)
         self.sampler.observe(layout, ctx.stream)
         x = self.model.forward_hidden(ctx, self.cache)
+        K.commit_lengths(layout.slot_of_seq, layout.kv_len, self.cache.state.seq_len, ctx.stream)
         for e, s in zip(entries, starts):
             self.cache.commit(e.slot, s + len(e.tokens))
         return x, layout, ctx
@@ -181,7 +189,63 @@ class Engine:
             raise
 
     def advance(self, slots, tokens):
-        return self._step_and_sample([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)])
+        """One token for each sequence: host token ids in, sampled host token ids out."""
+        B = len(slots)
+        if not self.options.decode_graphs or B not in self._ran_eagerly:
+            self._ran_eagerly.add(B)              # the first step of a batch size runs eagerly (lazy set-up happens there)
+            return self._step_and_sample([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)])
+        g = self._prepare_graph_step(slots, 1)
+        V = self.spec.vocab_size
+        for i, t in enumerate(tokens):
+            if not 0 <= int(t) < V:
+                raise StepError(f"token id {t} lies outside the vocabulary of {V}")
+            g.host_tokens[i] = int(t)
+        g.tokens.copy_(g.host_tokens, non_blocking=True)
+        self.h2d_bytes += 4 * B
+        self.steps_run += 1
+        self._replay(g, False)
+        for s in slots:
+            self.cache.commit(s, self.cache.length[s] + 1)
+        host = g.out_tokens.cpu()
+        self.d2h_bytes += 4 * B
+        return host.tolist()
+
+    def decode_on_device(self, slots, steps: int) -> torch.Tensor:
+        """``steps`` decode steps without the host in the loop: every step feeds each sequence the
+        token it sampled in the step before (``last_token`` of its slot).  Returns the last step's
+        tokens as a device tensor; nothing is copied back."""
+        g = self._prepare_graph_step(slots, steps)
+        for _ in range(steps):
+            self._replay(g, True)
+        for s in slots:
+            self.cache.commit(s, self.cache.length[s] + steps)
+        self.steps_run += steps
+        return g.out_tokens
+
+    def _prepare_graph_step(self, slots, steps: int) -> "DecodeGraph":
+        seen = set()
+        for s in slots:
+            if not self.cache.is_live(s) or s in seen:
+                raise StepError(f"slot {s} is not live or appears twice")
+            seen.add(s)
+        try:
+            self.cache.reserve({s: self.cache.length[s] + steps for s in slots})
+        except CacheFull as err:
+            raise StepError(str(err)) from None
+        B = len(slots)
+        if B not in self._graphs:
+            self._graphs[B] = DecodeGraph(self, B)
+        g = self._graphs[B]
+        g.set_slots(slots)
+        return g
+
+    def _replay(self, g: "DecodeGraph", feed_last: bool) -> None:
+        before = K.launch_count
+        g.replay(feed_last)
+        captured = K.launch_count - before
+        if captured:                              # this call captured the graph: remember its size
+            g.launches = captured
+        self.graph_launches += g.launches
 
     def finish(self, slot) -> None:
         self.cache.free_slot(slot)

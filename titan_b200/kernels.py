@@ -72,11 +72,15 @@ def lib():
         l.tb_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         l.tb_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
         l.tb_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        l.tb_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        l.tb_gemm_tc_check.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
         l.tb_qk_norm_rope.argtypes = [POINTER(QkArgs), c_int, c_int, c_void_p]
         l.tb_kv_append.argtypes = [c_void_p, c_int, c_int, POINTER(KvView), POINTER(Batch), c_void_p]
         l.tb_attn_prefill.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
         l.tb_attn_decode.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
         l.tb_sample.argtypes = [POINTER(SampleArgs), c_void_p]
+        l.tb_decode_prepare.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        l.tb_commit_lengths.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         l.tb_mark_seen.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
         _lib = l
     return _lib
@@ -137,6 +141,37 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, str
                               x.stride(0), out.stride(0), epi, stream))
 
 
+def gemm_tc_accepts(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int) -> bool:
+    """Whether the tensor-core kernel's alignment rules hold for this product."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous():
+        return False
+    if x.stride(1) != 1 or out.stride(1) != 1 or x.shape[1] != w.shape[1]:
+        return False
+    return lib().tb_gemm_tc_check(x.shape[0], w.shape[0], x.shape[1], x.stride(0), out.stride(0), epi,
+                                  x.data_ptr(), w.data_ptr(), out.data_ptr()) == 0
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, stream: int, splits: int = 0) -> None:
+    """out (epilogue ``epi``) = x[M,K] . w[N,K]^T on the tcgen05 tensor cores (bfloat16 operands)."""
+    _need_cuda(x, w, out)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemm_tc: operands must be bfloat16")
+    want = torch.bfloat16 if epi in (EPI_STORE, EPI_SWIGLU) else torch.float32
+    if out.dtype != want:
+        raise KernelError(f"gemm_tc: this epilogue writes {want}, the output is {out.dtype}")
+    M, K_ = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K_ or not w.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"gemm_tc: shapes do not fit: x {tuple(x.shape)} w {tuple(w.shape)}")
+    _check(lib().tb_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K_, x.stride(0), out.stride(0), epi,
+                            splits, stream))
+
+
+def gemm_tc_error() -> int:
+    """Error word of the tensor-core kernels (0: none); synchronises the device and clears the word."""
+    return int(lib().tb_gemm_tc_error())
+
+
 def qk_norm_rope(args: QkArgs, in_dtype: torch.dtype, out_dtype: torch.dtype, stream: int) -> None:
     _check(lib().tb_qk_norm_rope(byref(args), dtype_code(in_dtype), dtype_code(out_dtype), stream))
 
@@ -160,6 +195,16 @@ def sample(args: SampleArgs, stream: int) -> None:
 def mark_seen(tokens, seq_of, slot_of_seq, seen: torch.Tensor, T: int, stream: int) -> None:
     _check(lib().tb_mark_seen(tokens.data_ptr(), seq_of.data_ptr(), slot_of_seq.data_ptr(), seen.data_ptr(),
                               seen.shape[1], T, stream))
+
+
+def decode_prepare(slot_of_seq, seq_len, last_token, feed_last: bool, tokens, pos_of, start_pos, kv_len, stream: int) -> None:
+    _check(lib().tb_decode_prepare(slot_of_seq.data_ptr(), seq_len.data_ptr(), last_token.data_ptr(), int(feed_last),
+                                   tokens.data_ptr(), pos_of.data_ptr(), start_pos.data_ptr(), kv_len.data_ptr(),
+                                   slot_of_seq.numel(), stream))
+
+
+def commit_lengths(slot_of_seq, kv_len, seq_len, stream: int) -> None:
+    _check(lib().tb_commit_lengths(slot_of_seq.data_ptr(), kv_len.data_ptr(), seq_len.data_ptr(), slot_of_seq.numel(), stream))
 
 
 def uniform24(seed: int, sequence: int, step: int) -> int:
