@@ -355,3 +355,51 @@ def test_sampling_follows_the_distribution(K):
     got = [o[0] for o in b.run(logits, [SamplerParams(1.0, 1.0, 0, 1.0, 123)], [0], steps=6000)]
     freq = torch.bincount(torch.tensor(got), minlength=V).float() / 6000
     assert float((freq - torch.softmax(logits[0], 0)).abs().max()) < 0.02
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window,ring", [(32, 8, 128, 0, 0), (6, 2, 64, 0, 0), (24, 2, 128, 0, 0), (4, 4, 64, 100, 128), (8, 1, 128, 200, 256)])
+def test_attention_decode_on_tensor_cores(K, nh, nkv, hd, window, ring):
+    """The mma kernel against float64 and against the plain kernel: long and short sequences in one
+    batch, lengths that end inside a page, a far key that stands out, chunks of several sizes."""
+    g = torch.Generator().manual_seed(nh + hd)
+    lens = [1, 63, 64, 65, 700, 1500]
+    slots = [3, 0, 5, 1, 2, 4]
+    B, Q = len(lens), nh * hd
+    scale = 1 / math.sqrt(hd)
+    ks = [torch.randn(n, nkv, hd, generator=g).to(torch.bfloat16) for n in lens]
+    vs = [torch.randn(n, nkv, hd, generator=g).to(torch.bfloat16) for n in lens]
+    q = torch.randn(B, nh, hd, generator=g).to(torch.bfloat16)
+    for i, n in enumerate(lens):
+        far = max(0, n - window) if window else min(3, n - 1)
+        ks[i][far] = (ks[i][far].float() * 5).to(torch.bfloat16)
+    cache = Paged(K, slots, lens, nkv, hd, torch.bfloat16, ring_rows=ring)
+    for i, s in enumerate(slots):
+        for p in range(max(0, lens[i] - ring) if ring else 0, lens[i]):
+            cache.put(s, p, ks[i][p], vs[i][p])
+    lay = layout_for(slots, [n - 1 for n in lens], [1] * B)
+    qb = q.reshape(B, Q).cuda()
+    want = torch.stack([reference_attention(q[i].float(), ks[i].float(), vs[i].float(), lens[i] - 1, window, scale) for i in range(B)]).reshape(B, Q)
+    for chunk in (64, 256, 1024):
+        splits = -(-max(lens) // chunk)
+        outs = []
+        for fast in (True, False):
+            out = torch.empty(B, Q, dtype=torch.bfloat16, device="cuda")
+            scratch = torch.full((B * nh * splits * (hd + 2),), float("nan"), device="cuda")
+            d = K.AttnArgs()
+            d.q, d.q_stride, d.out, d.out_stride = qb.data_ptr(), Q, out.data_ptr(), Q
+            d.cache, d.batch = cache.view, lay.c_struct()
+            d.nh, d.nkv, d.hd, d.window, d.scale = nh, nkv, hd, window, scale
+            d.chunk, d.n_splits, d.scratch = chunk, splits, scratch.data_ptr()
+            if fast:
+                assert K.attn_decode_mma_accepts(d, torch.bfloat16)
+                K.attn_decode_mma(d, stream())
+                assert K.attn_mma_error() == 0
+            else:
+                K.attn_decode(d, torch.bfloat16, stream())
+            outs.append(out.float().cpu())
+        assert rel_l2(outs[0], want) < 8e-3, chunk        # P is rounded to bfloat16 before P.V
+        assert rel_l2(outs[0], outs[1]) < 8e-3, chunk
+    d.chunk = 100
+    assert not K.attn_decode_mma_accepts(d, torch.bfloat16)
+    d.chunk, d.hd = 64, 96
+    assert not K.attn_decode_mma_accepts(d, torch.bfloat16)

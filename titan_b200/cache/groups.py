@@ -59,7 +59,9 @@ class KVGroup:
                 self.ring_rows = 0
         self.pool = PagePool(num_pages)
         self.pages_of: Dict[int, List[int]] = {}
-        self.storage = torch.empty((len(layers), 2, num_pages, need.num_kv_heads, page_size, need.head_dim),
+        # zeroed once: rows past a sequence's end are multiplied by a zero weight in the tensor-core
+        # kernels, so they must hold finite numbers (a freed page keeps its old, finite, rows)
+        self.storage = torch.zeros((len(layers), 2, num_pages, need.num_kv_heads, page_size, need.head_dim),
                                    dtype=dtype, device=device)
         self.table_host = torch.zeros((max_slots, self.table_width), dtype=torch.int32)
         if torch.device(device).type == "cuda":

@@ -186,28 +186,39 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(AttnArgs a)
 }
 
 // grid (B, nh), one warp: out = sum_s exp(m_s - m) acc_s / sum_s exp(m_s - m) l_s, splits in order.
+// Lane s holds the weight of split s (32 splits per round), so the loads of the accumulation are
+// independent of one another.
 template <typename T>
 __global__ void attn_merge_kernel(AttnArgs a) {
-    const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, hd = a.hd;
-    const float* part = a.scratch + (size_t)(b * a.nh + h) * a.n_splits * (hd + 2);
+    const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, hd = a.hd, stride = hd + 2;
+    const float* part = a.scratch + (size_t)(b * a.nh + h) * a.n_splits * stride;
     const int used = min(a.n_splits, (a.batch.kv_len[b] + a.chunk - 1) / a.chunk);
     float m = -FLT_MAX;
-    for (int s = 0; s < used; ++s)
-        if (part[s * (hd + 2) + hd + 1] > 0.f) m = fmaxf(m, part[s * (hd + 2) + hd]);
+    for (int s = lane; s < used; s += 32)
+        if (part[s * stride + hd + 1] > 0.f) m = fmaxf(m, part[s * stride + hd]);
+    m = warp_max(m);
     float l = 0.f, acc[ATT_MAXE];
 #pragma unroll
     for (int j = 0; j < ATT_MAXE; ++j) acc[j] = 0.f;
-    for (int s = 0; s < used; ++s) {
-        const float* p = part + s * (hd + 2);
-        if (!(p[hd + 1] > 0.f)) continue;
-        const float w = expf(p[hd] - m);
-        l += w * p[hd + 1];
+    for (int s0 = 0; s0 < used; s0 += 32) {
+        const int s = s0 + lane;
+        float w = 0.f;
+        if (s < used) {
+            const float ls = part[s * stride + hd + 1];
+            if (ls > 0.f) { w = expf(part[s * stride + hd] - m); l += w * ls; }
+        }
+        const int n = min(32, used - s0);
+        for (int k = 0; k < n; ++k) {
+            const float wk = __shfl_sync(0xffffffffu, w, k);
+            const float* p = part + (size_t)(s0 + k) * stride;
 #pragma unroll
-        for (int j = 0; j < ATT_MAXE; ++j) {
-            const int d = lane + 32 * j;
-            if (d < hd) acc[j] = fmaf(w, p[d], acc[j]);
+            for (int j = 0; j < ATT_MAXE; ++j) {
+                const int d = lane + 32 * j;
+                if (d < hd) acc[j] = fmaf(wk, p[d], acc[j]);
+            }
         }
     }
+    l = warp_sum(l);
     const float inv = 1.0f / l;
     T* o = (T*)a.out + (size_t)b * a.out_stride + h * hd;
 #pragma unroll
@@ -237,6 +248,16 @@ extern "C" int tb_attn_prefill(const AttnArgs* args, int dtype, cudaStream_t str
     else if (dtype == TB_BF16) attn_prefill_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, smem, stream>>>(a);
     else TB_REQUIRE(false, "attn_prefill: unknown dtype %d", dtype);
     TB_CHECK_LAUNCH("attn_prefill");
+    return 0;
+}
+
+extern "C" int tb_attn_merge(const AttnArgs* args, int dtype, cudaStream_t stream) {
+    AttnArgs a = *args;
+    dim3 mgrid(a.batch.B, a.nh);
+    if (dtype == TB_F32) attn_merge_kernel<float><<<mgrid, 32, 0, stream>>>(a);
+    else if (dtype == TB_BF16) attn_merge_kernel<__nv_bfloat16><<<mgrid, 32, 0, stream>>>(a);
+    else TB_REQUIRE(false, "attn_merge: unknown dtype %d", dtype);
+    TB_CHECK_LAUNCH("attn_merge");
     return 0;
 }
 

@@ -1,0 +1,525 @@
+// bfloat16 attention on tensor cores for the head sizes serving uses (64 and 128), pages of 64 rows.
+//
+//   tb_attn_decode_mma   one query per sequence over its cached keys.  One CTA per (sequence, kv
+//                        head, chunk of keys): TMA brings whole K and V pages (64 keys) of that head
+//                        into a ring of shared-memory stages; four warps each take 16 keys of the page,
+//                        S = Q K^T and O += P V run as mma.sync.m16n8k16 with the kv head's whole
+//                        group of query heads in the 16 rows of the tile, so every key and value is
+//                        read from HBM once for the group.  Partials go through the same
+//                        (max, sum, unnormalised output) format as the plain kernel and the same merge.
+//
+// The chunk borders are multiples of the page size and depend on the launch (batch size, context
+// limit), not on the other sequences of the batch.
+//
+// Keys and values arrive 128-byte swizzled (tensor map of 64 x 64 boxes), which makes the ldmatrix
+// reads conflict-free.  All waits are bounded (tma.cuh); tb_attn_mma_error() reads the error word.
+//
+// berniehans/titan: flash_decoding_split_kernel, one warp per (head, split), one key per iteration,
+// scalar FMA (engine/engine-cuda/kernels/paged_attention.cu:200-309).
+#include <float.h>
+
+#include "common.cuh"
+#include "tma.cuh"
+
+namespace {
+
+using namespace tbtma;
+
+__device__ unsigned int g_attn_error = 0;
+
+constexpr int PAGE = 64;
+constexpr int DEC_WARPS = 4;                 // compute warps; warp DEC_WARPS produces
+constexpr int DEC_THREADS = (DEC_WARPS + 1) * 32;
+
+struct DecArgs {
+    const __nv_bfloat16* q; int q_stride;    // [B][q_stride]
+    float* scratch;                          // [B][nh][n_splits][hd + 2]
+    const int* table; int table_width; int ring_rows; int num_pages;
+    const int* slot_of_seq; const int* kv_len;
+    int nh; int nkv; int window; float scale_log2;   // scale * log2(e)
+    int chunk; int n_splits;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&p);
+}
+// Byte offset of (row, 16-byte chunk of the row's 128 bytes) in a 64-row, 128-byte-swizzled box.
+__device__ __forceinline__ uint32_t swz(int row, int chunk16) { return (uint32_t)(row * 128 + ((chunk16 ^ (row & 7)) << 4)); }
+
+// HD: head size (64 or 128).  WIDE: the group has more than 8 query heads (rows 8..15 of the tile are live).
+template <int HD, bool WIDE>
+__global__ void __launch_bounds__(DEC_THREADS)
+attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
+    constexpr int STAGES = HD == 128 ? 3 : 4;
+    constexpr int BOXES = HD / 64;                      // 64-column boxes per tile
+    constexpr uint32_t TILE_BYTES = PAGE * HD * 2;      // one K or V page of one head
+    constexpr int KS = HD / 16, NT = HD / 8;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(base + STAGES * 2 * TILE_BYTES);
+    uint64_t* empty = full + STAGES;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
+    const int len = a.kv_len[b];
+    if (split * a.chunk >= len) return;                 // uniform over the CTA; the merge skips these splits
+    const int group = a.nh / a.nkv;
+    const int wlo = a.window > 0 ? max(0, len - a.window) : 0;       // first visible key of position len - 1
+    const int lo = max(wlo, split * a.chunk), hi = min(len, (split + 1) * a.chunk);
+    const int page0 = lo / PAGE, n_pages = lo < hi ? (hi - 1) / PAGE - page0 + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, DEC_WARPS); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == DEC_WARPS) {                            // ---------------- producer
+        if (lane == 0) {
+            const int slot = a.slot_of_seq[b];
+            const int* tab = a.table + (size_t)slot * a.table_width;
+            const int v_rows = a.num_pages * a.nkv * PAGE;          // rows of the K half
+            for (int i = 0; i < n_pages; ++i) {
+                const int s = i % STAGES, round = i / STAGES;
+                if (round > 0) mbar_wait(empty + s, (round - 1) & 1, &g_attn_error, 1);
+                const int pos0 = (page0 + i) * PAGE;
+                const int page = tab[(a.ring_rows ? pos0 % a.ring_rows : pos0) / PAGE];
+                const int row = (page * a.nkv + kh) * PAGE;
+                uint8_t* kd = base + s * 2 * TILE_BYTES;
+                mbar_expect_tx(full + s, 2 * TILE_BYTES);
+#pragma unroll
+                for (int x = 0; x < BOXES; ++x) {
+                    tma_load_2d(kd + x * (PAGE * 128), &kv_map, full + s, x * 64, row);
+                    tma_load_2d(kd + TILE_BYTES + x * (PAGE * 128), &kv_map, full + s, x * 64, v_rows + row);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- compute warps: this warp takes keys 16 * warp .. + 15 of every page
+    const int g = lane >> 2, t = lane & 3;
+    uint32_t qf[KS][4];
+    {
+        const __nv_bfloat16* q0 = a.q + (size_t)b * a.q_stride + (size_t)(kh * group) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int d = ks * 16 + 2 * t;
+            qf[ks][0] = g < group ? *reinterpret_cast<const uint32_t*>(q0 + g * HD + d) : 0u;
+            qf[ks][2] = g < group ? *reinterpret_cast<const uint32_t*>(q0 + g * HD + d + 8) : 0u;
+            qf[ks][1] = (WIDE && g + 8 < group) ? *reinterpret_cast<const uint32_t*>(q0 + (g + 8) * HD + d) : 0u;
+            qf[ks][3] = (WIDE && g + 8 < group) ? *reinterpret_cast<const uint32_t*>(q0 + (g + 8) * HD + d + 8) : 0u;
+        }
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;       // rows g and g + 8
+
+    for (int i = 0; i < n_pages; ++i) {
+        const int s = i % STAGES;
+        mbar_wait(full + s, (i / STAGES) & 1, &g_attn_error, 2);
+        const uint32_t ks_base = smem_u32(base + s * 2 * TILE_BYTES);
+        const uint32_t vs_base = ks_base + TILE_BYTES;
+        // S[16 x 16] = Q . K^T for this warp's 16 keys: two n-tiles of 8 keys
+        float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+            const int mtx = lane >> 3, r = lane & 7;
+            const int key = warp * 16 + (mtx >> 1) * 8 + r;              // matrices 0,1: first 8 keys; 2,3: next 8
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                const int dim0 = ks * 16 + (mtx & 1) * 8;
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(ks_base + (dim0 >> 6) * (PAGE * 128) + swz(key, (dim0 & 63) >> 3), b0, b1, b2, b3);
+                mma_bf16(sc[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+                mma_bf16(sc[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+            }
+        }
+        // mask, scale, running softmax
+        const int pos_base = (page0 + i) * PAGE + warp * 16 + 2 * t;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int pos = pos_base + j * 8 + c;
+                const bool ok = pos >= lo && pos < hi;
+                sc[j][c] = ok ? sc[j][c] * a.scale_log2 : -INFINITY;
+                sc[j][c + 2] = ok ? sc[j][c + 2] * a.scale_log2 : -INFINITY;
+                mx0 = fmaxf(mx0, sc[j][c]);
+                mx1 = fmaxf(mx1, sc[j][c + 2]);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float al0 = exp2f(m0 - n0), al1 = exp2f(m1 - n1);
+        m0 = n0; m1 = n1;
+        float p[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            p[j][0] = exp2f(sc[j][0] - n0); p[j][1] = exp2f(sc[j][1] - n0);
+            p[j][2] = WIDE ? exp2f(sc[j][2] - n1) : 0.f; p[j][3] = WIDE ? exp2f(sc[j][3] - n1) : 0.f;
+        }
+        l0 = l0 * al0 + p[0][0] + p[0][1] + p[1][0] + p[1][1];
+        l1 = l1 * al1 + p[0][2] + p[0][3] + p[1][2] + p[1][3];
+        const uint32_t pa0 = pack2(p[0][0], p[0][1]), pa1 = pack2(p[0][2], p[0][3]);
+        const uint32_t pa2 = pack2(p[1][0], p[1][1]), pa3 = pack2(p[1][2], p[1][3]);
+        // O[16 x HD] = alpha * O + P . V over this warp's 16 keys
+        {
+            const int mtx = lane >> 3, r = lane & 7;
+            const int key = warp * 16 + (mtx & 1) * 8 + r;              // matrices 0,2: keys 0-7; 1,3: keys 8-15
+#pragma unroll
+            for (int n = 0; n < NT; n += 2) {
+                const int dim0 = (n + (mtx >> 1)) * 8;
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_trans(vs_base + (dim0 >> 6) * (PAGE * 128) + swz(key, (dim0 & 63) >> 3), b0, b1, b2, b3);
+                o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1;
+                o[n + 1][0] *= al0; o[n + 1][1] *= al0; o[n + 1][2] *= al1; o[n + 1][3] *= al1;
+                mma_bf16(o[n], pa0, pa1, pa2, pa3, b0, b1);
+                mma_bf16(o[n + 1], pa0, pa1, pa2, pa3, b2, b3);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // ---------------- merge the four warps through shared memory (the stages are drained)
+    asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32));      // compute warps only; the producer has left
+    float* mo = reinterpret_cast<float*>(base);                 // [warp][16][HD]
+    float* mm = mo + DEC_WARPS * 16 * HD;                       // [warp][16] max, then [warp][16] sum
+    float* ml = mm + DEC_WARPS * 16;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        float* r0 = mo + (warp * 16 + g) * HD + n * 8 + 2 * t;
+        r0[0] = o[n][0]; r0[1] = o[n][1];
+        if (WIDE) { r0[8 * HD] = o[n][2]; r0[8 * HD + 1] = o[n][3]; }
+    }
+    if (t == 0) {
+        mm[warp * 16 + g] = m0; ml[warp * 16 + g] = l0;
+        mm[warp * 16 + g + 8] = WIDE ? m1 : -1e30f; ml[warp * 16 + g + 8] = WIDE ? l1 : 0.f;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32));
+    const float ln2 = 0.69314718055994531f;
+    for (int idx = threadIdx.x; idx < group * HD; idx += DEC_WARPS * 32) {
+        const int row = idx / HD, d = idx % HD;
+        float M = -1e30f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, mm[w * 16 + row]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float f = exp2f(mm[w * 16 + row] - M);
+            acc += f * mo[(w * 16 + row) * HD + d];
+            L += f * ml[w * 16 + row];
+        }
+        float* part = a.scratch + ((size_t)(b * a.nh + kh * group + row) * a.n_splits + split) * (HD + 2);
+        part[d] = acc;
+        if (d == 0) { part[HD] = M * ln2; part[HD + 1] = L; }     // the merge works with natural exponents
+    }
+}
+
+
+// ------------------------------------------------------------------ prompts that start at position 0
+// One CTA per (sequence, query head, block of 64 queries), four compute warps of 16 query rows each
+// and a producer warp.  Queries, keys and values are read by TMA straight from the step's own
+// [T][Q | K | V] rows (64 x 64 boxes, 128-byte swizzle); the cache is not touched.  Key tiles of 64
+// run from the window's first key to the diagonal; S and P.V are mma.sync.m16n8k16 as above.
+// Heavy (late) query blocks are scheduled first.
+struct PreArgs {
+    __nv_bfloat16* out; int out_stride;
+    const int* q_start; int B;
+    int nh; int nkv; int window; float scale_log2;
+    int k_col0; int v_col0;                  // first column of the K heads and of the V heads
+};
+
+template <int HD>
+__global__ void __launch_bounds__(DEC_THREADS)
+attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, PreArgs a) {
+    constexpr int STAGES = 2;
+    constexpr int BOXES = HD / 64;
+    constexpr uint32_t TILE_BYTES = 64 * HD * 2;
+    constexpr int KS = HD / 16, NT = HD / 8;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_smem = base + STAGES * 2 * TILE_BYTES;
+    uint64_t* full = (uint64_t*)(q_smem + TILE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* qbar = empty + STAGES;
+
+    // which sequence and which block of it (blocks are numbered from the heaviest)
+    int rem = blockIdx.x, seq = -1, blk = 0, tok0 = 0, n = 0;
+    for (int s = 0; s < a.B; ++s) {
+        const int t0 = a.q_start[s], ns = a.q_start[s + 1] - t0, nb = (ns + 63) >> 6;
+        if (rem < nb) { seq = s; blk = nb - 1 - rem; tok0 = t0; n = ns; break; }
+        rem -= nb;
+    }
+    if (seq < 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y, kh = h / (a.nh / a.nkv);
+    const int r0 = blk * 64;                                         // first query position of the block
+    const int last_key = min(n - 1, r0 + 63);
+    const int first_key = a.window > 0 ? max(0, r0 - a.window + 1) : 0;
+    const int kt0 = first_key >> 6, n_tiles = (last_key >> 6) - kt0 + 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, DEC_WARPS); }
+        mbar_init(qbar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == DEC_WARPS) {
+        if (lane == 0) {
+            mbar_expect_tx(qbar, TILE_BYTES);
+#pragma unroll
+            for (int x = 0; x < BOXES; ++x) tma_load_2d(q_smem + x * 8192, &qkv_map, qbar, h * HD + x * 64, tok0 + r0);
+            for (int i = 0; i < n_tiles; ++i) {
+                const int s = i % STAGES, round = i / STAGES;
+                if (round > 0) mbar_wait(empty + s, (round - 1) & 1, &g_attn_error, 3);
+                uint8_t* kd = base + s * 2 * TILE_BYTES;
+                const int row = tok0 + (kt0 + i) * 64;
+                mbar_expect_tx(full + s, 2 * TILE_BYTES);
+#pragma unroll
+                for (int x = 0; x < BOXES; ++x) {
+                    tma_load_2d(kd + x * 8192, &qkv_map, full + s, a.k_col0 + kh * HD + x * 64, row);
+                    tma_load_2d(kd + TILE_BYTES + x * 8192, &qkv_map, full + s, a.v_col0 + kh * HD + x * 64, row);
+                }
+            }
+        }
+        return;
+    }
+
+    const int g = lane >> 2, t = lane & 3, mtx = lane >> 3, r = lane & 7;
+    uint32_t qf[KS][4];
+    mbar_wait(qbar, 0, &g_attn_error, 4);
+    {
+        const uint32_t qs = smem_u32(q_smem);
+        const int row = warp * 16 + (mtx & 1) * 8 + r;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int dim0 = ks * 16 + (mtx >> 1) * 8;
+            ldsm_x4(qs + (dim0 >> 6) * 8192 + swz(row, (dim0 & 63) >> 3), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+        }
+    }
+    float o[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
+    const int qp0 = r0 + warp * 16 + g, qp1 = qp0 + 8;              // positions of this thread's two rows
+    const int lo0 = a.window > 0 ? qp0 - a.window + 1 : 0, lo1 = a.window > 0 ? qp1 - a.window + 1 : 0;
+
+    for (int i = 0; i < n_tiles; ++i) {
+        const int s = i % STAGES;
+        mbar_wait(full + s, (i / STAGES) & 1, &g_attn_error, 5);
+        const uint32_t ks_base = smem_u32(base + s * 2 * TILE_BYTES), vs_base = ks_base + TILE_BYTES;
+        float sc[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int dim0 = ks * 16 + (mtx & 1) * 8;
+            const uint32_t col = (dim0 >> 6) * 8192, ch = (dim0 & 63) >> 3;
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {
+                const int key = (2 * jp + (mtx >> 1)) * 8 + r;
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(ks_base + col + swz(key, ch), b0, b1, b2, b3);
+                mma_bf16(sc[2 * jp], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+                mma_bf16(sc[2 * jp + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+            }
+        }
+        const int key_base = (kt0 + i) * 64 + 2 * t;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int key = key_base + j * 8 + c;
+                sc[j][c] = (key <= qp0 && key >= lo0) ? sc[j][c] * a.scale_log2 : -INFINITY;
+                sc[j][c + 2] = (key <= qp1 && key >= lo1) ? sc[j][c + 2] * a.scale_log2 : -INFINITY;
+                mx0 = fmaxf(mx0, sc[j][c]);
+                mx1 = fmaxf(mx1, sc[j][c + 2]);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float al0 = exp2f(m0 - n0), al1 = exp2f(m1 - n1);
+        m0 = n0; m1 = n1;
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            sc[j][0] = exp2f(sc[j][0] - n0); sc[j][1] = exp2f(sc[j][1] - n0);
+            sc[j][2] = exp2f(sc[j][2] - n1); sc[j][3] = exp2f(sc[j][3] - n1);
+            s0 += sc[j][0] + sc[j][1]; s1 += sc[j][2] + sc[j][3];
+        }
+        l0 = l0 * al0 + s0; l1 = l1 * al1 + s1;
+#pragma unroll
+        for (int i2 = 0; i2 < NT; ++i2) { o[i2][0] *= al0; o[i2][1] *= al0; o[i2][2] *= al1; o[i2][3] *= al1; }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            const uint32_t pa0 = pack2(sc[2 * kk][0], sc[2 * kk][1]), pa1 = pack2(sc[2 * kk][2], sc[2 * kk][3]);
+            const uint32_t pa2 = pack2(sc[2 * kk + 1][0], sc[2 * kk + 1][1]), pa3 = pack2(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+            const int key = kk * 16 + (mtx & 1) * 8 + r;
+#pragma unroll
+            for (int nn = 0; nn < NT; nn += 2) {
+                const int dim0 = (nn + (mtx >> 1)) * 8;
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_trans(vs_base + (dim0 >> 6) * 8192 + swz(key, (dim0 & 63) >> 3), b0, b1, b2, b3);
+                mma_bf16(o[nn], pa0, pa1, pa2, pa3, b0, b1);
+                mma_bf16(o[nn + 1], pa0, pa1, pa2, pa3, b2, b3);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + s);
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float i0 = 1.0f / l0, i1 = 1.0f / l1;
+    __nv_bfloat16* out0 = a.out + (size_t)(tok0 + qp0) * a.out_stride + h * HD + 2 * t;
+    __nv_bfloat16* out1 = a.out + (size_t)(tok0 + qp1) * a.out_stride + h * HD + 2 * t;
+#pragma unroll
+    for (int nn = 0; nn < NT; ++nn) {
+        if (qp0 < n) *reinterpret_cast<uint32_t*>(out0 + nn * 8) = pack2(o[nn][0] * i0, o[nn][1] * i0);
+        if (qp1 < n) *reinterpret_cast<uint32_t*>(out1 + nn * 8) = pack2(o[nn][2] * i1, o[nn][3] * i1);
+    }
+}
+
+}  // namespace
+
+// Same argument block as the plain kernels (attention.cu).
+struct AttnArgs {
+    const void* q; int q_stride;
+    const void* kv_new; int kv_stride;
+    void* out; int out_stride;
+    TbKvView cache;
+    TbBatch batch;
+    int nh; int nkv; int hd;
+    int window;
+    float scale;
+    int chunk;
+    int n_splits;
+    float* scratch;
+};
+
+extern "C" int tb_attn_merge(const AttnArgs* args, int dtype, cudaStream_t stream);
+
+template <int HD, bool WIDE>
+static int launch_decode(const CUtensorMap& map, const DecArgs& d, dim3 grid, cudaStream_t stream) {
+    constexpr int STAGES = HD == 128 ? 3 : 4;
+    constexpr size_t smem = 1024 + (size_t)STAGES * 2 * PAGE * HD * 2 + 2 * STAGES * sizeof(uint64_t);
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        TB_REQUIRE(e == cudaSuccess, "attn_decode_mma: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    attn_decode_mma_kernel<HD, WIDE><<<grid, DEC_THREADS, smem, stream>>>(map, d);
+    return 0;
+}
+
+// 0 if the tensor-core decode kernel takes this problem, else 1 with the reason in tb_last_error().
+extern "C" int tb_attn_decode_mma_check(const AttnArgs* a, int dtype) {
+    TB_REQUIRE(dtype == TB_BF16, "attn_decode_mma: bfloat16 only");
+    TB_REQUIRE(a->hd == 64 || a->hd == 128, "attn_decode_mma: head_dim %d is not 64 or 128", a->hd);
+    TB_REQUIRE(a->cache.page_size == PAGE, "attn_decode_mma: pages of %d rows, not %d", PAGE, a->cache.page_size);
+    TB_REQUIRE(a->nkv > 0 && a->nh % a->nkv == 0 && a->nh / a->nkv <= 16, "attn_decode_mma: at most 16 query heads per kv head");
+    TB_REQUIRE(a->chunk > 0 && a->chunk % PAGE == 0, "attn_decode_mma: the chunk %d must be a multiple of %d", a->chunk, PAGE);
+    TB_REQUIRE(a->q_stride % 2 == 0 && ((uintptr_t)a->q & 3) == 0, "attn_decode_mma: queries must be 4-byte aligned");
+    return 0;
+}
+
+extern "C" int tb_attn_decode_mma(const AttnArgs* args, cudaStream_t stream) {
+    const AttnArgs& a = *args;
+    if (tb_attn_decode_mma_check(args, TB_BF16)) return 1;
+    TB_REQUIRE(a.batch.B > 0 && a.cache.storage && a.scratch, "attn_decode_mma: needs sequences, a cache and scratch");
+    TB_REQUIRE(a.n_splits > 0 && a.n_splits <= 65535 && a.nkv <= 65535, "attn_decode_mma: bad grid");
+    TB_REQUIRE((long long)a.chunk * a.n_splits >= a.batch.max_kv_len, "attn_decode_mma: %d splits of %d keys do not cover %d keys", a.n_splits, a.chunk, a.batch.max_kv_len);
+    TB_REQUIRE(a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv, "attn_decode_mma: the cache view does not match the heads");
+    CUtensorMap map;
+    const long long rows = 2LL * a.cache.num_pages * a.nkv * PAGE;
+    if (tb_make_map_bf16(&map, a.cache.storage, rows, a.hd, a.hd, PAGE)) return 1;
+    DecArgs d;
+    d.q = (const __nv_bfloat16*)a.q; d.q_stride = a.q_stride; d.scratch = a.scratch;
+    d.table = a.cache.table; d.table_width = a.cache.table_width; d.ring_rows = a.cache.ring_rows; d.num_pages = a.cache.num_pages;
+    d.slot_of_seq = a.batch.slot_of_seq; d.kv_len = a.batch.kv_len;
+    d.nh = a.nh; d.nkv = a.nkv; d.window = a.window; d.scale_log2 = a.scale * 1.4426950408889634f;
+    d.chunk = a.chunk; d.n_splits = a.n_splits;
+    dim3 grid(a.batch.B, a.nkv, a.n_splits);
+    const bool wide = a.nh / a.nkv > 8;
+    int rc;
+    if (a.hd == 128) rc = wide ? launch_decode<128, true>(map, d, grid, stream) : launch_decode<128, false>(map, d, grid, stream);
+    else rc = wide ? launch_decode<64, true>(map, d, grid, stream) : launch_decode<64, false>(map, d, grid, stream);
+    if (rc) return rc;
+    TB_CHECK_LAUNCH("attn_decode_mma");
+    return tb_attn_merge(args, TB_BF16, stream);
+}
+
+// Reads and clears the error word of this file's kernels (0: none).  Synchronises the device.
+extern "C" int tb_attn_mma_error() {
+    unsigned int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(v)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(zero));
+    return (int)v;
+}
+
+template <int HD>
+static int launch_prefill(const CUtensorMap& map, const PreArgs& p, dim3 grid, cudaStream_t stream) {
+    constexpr size_t smem = 1024 + (size_t)(2 * 2 + 1) * 64 * HD * 2 + 8 * sizeof(uint64_t);
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        TB_REQUIRE(e == cudaSuccess, "attn_prefill_mma: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    attn_prefill_mma_kernel<HD><<<grid, DEC_THREADS, smem, stream>>>(map, p);
+    return 0;
+}
+
+// 0 if the tensor-core prompt kernel takes this problem (every sequence of the step starts at
+// position 0, so all keys are among the step's own rows), else 1 with the reason.
+extern "C" int tb_attn_prefill_mma_check(const AttnArgs* a, int dtype, int all_fresh) {
+    TB_REQUIRE(dtype == TB_BF16, "attn_prefill_mma: bfloat16 only");
+    TB_REQUIRE(all_fresh, "attn_prefill_mma: a sequence continues from the cache");
+    TB_REQUIRE(a->hd == 64 || a->hd == 128, "attn_prefill_mma: head_dim %d is not 64 or 128", a->hd);
+    TB_REQUIRE(a->nkv > 0 && a->nh % a->nkv == 0, "attn_prefill_mma: heads");
+    TB_REQUIRE(a->kv_new && a->q_stride == a->kv_stride && a->q_stride % 8 == 0, "attn_prefill_mma: Q, K and V must be columns of one row-major buffer");
+    TB_REQUIRE(((uintptr_t)a->q & 15) == 0, "attn_prefill_mma: the buffer must be 16-byte aligned");
+    const long long off = ((const char*)a->kv_new - (const char*)a->q) / 2;
+    TB_REQUIRE(off == (long long)a->nh * a->hd, "attn_prefill_mma: K must follow Q in the buffer");
+    TB_REQUIRE(a->out_stride % 2 == 0 && ((uintptr_t)a->out & 3) == 0, "attn_prefill_mma: the output must be 4-byte aligned");
+    return 0;
+}
+
+extern "C" int tb_attn_prefill_mma(const AttnArgs* args, int all_fresh, cudaStream_t stream) {
+    const AttnArgs& a = *args;
+    if (tb_attn_prefill_mma_check(args, TB_BF16, all_fresh)) return 1;
+    TB_REQUIRE(a.batch.T > 0 && a.batch.B > 0, "attn_prefill_mma: no tokens");
+    CUtensorMap map;
+    if (tb_make_map_bf16(&map, a.q, a.batch.T, a.q_stride, a.q_stride, 64)) return 1;
+    PreArgs p;
+    p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
+    p.nh = a.nh; p.nkv = a.nkv; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd;
+    const int blocks = (a.batch.T + 63) / 64 + a.batch.B;          // upper bound on sum over sequences of ceil(n / 64)
+    TB_REQUIRE(a.nh <= 65535, "attn_prefill_mma: too many heads");
+    dim3 grid(blocks, a.nh);
+    const int rc = a.hd == 128 ? launch_prefill<128>(map, p, grid, stream) : launch_prefill<64>(map, p, grid, stream);
+    if (rc) return rc;
+    TB_CHECK_LAUNCH("attn_prefill_mma");
+    return 0;
+}

@@ -29,6 +29,7 @@
 
 #include "common.cuh"
 #include "gemm.h"
+#include "tma.cuh"
 
 namespace {
 
@@ -36,41 +37,16 @@ constexpr int BM = 128;          // rows of A per tile = M of the instruction
 constexpr int BK = 64;           // bf16 elements per stage row = 128 bytes = one swizzle span
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr uint32_t WAIT_LIMIT = 1u << 20;
 
 __device__ unsigned int g_tc_error = 0;
 
 // ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait; on expiry records ``code`` and returns.
+using tbtma::smem_u32;
+using tbtma::mbar_init;
+using tbtma::mbar_expect_tx;
+using tbtma::tma_load_2d;
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, unsigned code) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        if (mbar_test(bar, parity)) return;
-        if (i > 64) __nanosleep(32);
-        if ((i & 1023u) == 1023u && *(volatile unsigned int*)&g_tc_error) break;   // another wait has given up already
-    }
-    atomicCAS(&g_tc_error, 0u, code);
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+    tbtma::mbar_wait(bar, parity, &g_tc_error, code);
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
@@ -314,60 +290,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; long long rows, cols, stride; int box_rows;
-    bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && rows == o.rows && cols == o.cols && stride == o.stride && box_rows == o.box_rows;
-    }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        size_t h = (size_t)k.ptr;
-        for (long long v : {k.rows, k.cols, k.stride, (long long)k.box_rows}) h = h * 1000003u ^ (size_t)v;
-        return h;
-    }
-};
-
-// A [rows][cols] bf16 matrix with row stride ``stride`` elements, boxes of box_rows x 64, 128-byte swizzle.
-int make_map(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long stride, int box_rows) {
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    static std::mutex mu;
-    const MapKey key{ptr, rows, cols, stride, box_rows};
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return 0; }
-    EncodeTiledFn fn = encode_fn();
-    TB_REQUIRE(fn, "gemm_tc: the driver does not export cuTensorMapEncodeTiled");
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)stride * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    TB_REQUIRE(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with code %d (rows=%lld cols=%lld stride=%lld)", (int)r, rows, cols, stride);
-    if (cache.size() > 4096) cache.clear();
-    cache.emplace(key, *out);
-    return 0;
-}
-
 template <int BN, int EPI, bool SWAP>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t stream) {
     static bool configured = false;
@@ -429,7 +351,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
     if (!swap) {
         const int bn = N >= 256 ? 256 : 128;
         a.rows_a = M; a.rows_b = N;
-        if (make_map(&ma, X, M, K, ldx, BM) || make_map(&mb, W, N, K, K, bn)) return 1;
+        if (tb_make_map_bf16(&ma, X, M, K, ldx, BM) || tb_make_map_bf16(&mb, W, N, K, K, bn)) return 1;
         dim3 grid((N + bn - 1) / bn, (M + BM - 1) / BM, 1);
         TB_REQUIRE(grid.y <= 65535, "gemm_tc: M=%d is too large for one launch", M);
         rc = bn == 256 ? launch_epi<256, false>(epi, ma, mb, a, grid, stream) : launch_epi<128, false>(epi, ma, mb, a, grid, stream);
@@ -446,7 +368,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         a.k_blocks_per_split = (kb + s - 1) / s;
         s = (kb + a.k_blocks_per_split - 1) / a.k_blocks_per_split;  // no empty slice
         a.atomic = s > 1;
-        if (make_map(&ma, W, N, K, K, BM) || make_map(&mb, X, M, K, ldx, bn)) return 1;
+        if (tb_make_map_bf16(&ma, W, N, K, K, BM) || tb_make_map_bf16(&mb, X, M, K, ldx, bn)) return 1;
         dim3 grid(1, tiles, s);
         TB_REQUIRE(tiles <= 65535, "gemm_tc: N=%d is too large for one launch", N);
         switch (bn) {

@@ -1,0 +1,57 @@
+// Device-side wrappers around mbarrier and TMA (cp.async.bulk.tensor) PTX, shared by the kernels that
+// stage tiles through shared memory, and the host-side tensor-map maker.
+//
+// Every wait is bounded: after ``limit`` polls the waiting thread records ``code`` in ``*error_word``
+// (first error wins) and returns, so a kernel always ends; its result is then invalid and the host,
+// which reads the word, says so.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tbtma {
+
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* error_word, unsigned code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_test(bar, parity)) return;
+        if (i > 64) __nanosleep(32);
+        if ((i & 1023u) == 1023u && *(volatile unsigned int*)error_word) break;   // another wait gave up already
+    }
+    atomicCAS(error_word, 0u, code);
+}
+// One 2-D tile: x = coordinate along the contiguous dimension (x * element size must be a multiple of
+// 16 bytes), y = row.  Rows and columns outside the tensor arrive as zeros.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+}  // namespace tbtma
+
+// A [rows][cols] bfloat16 matrix with row stride ``stride`` elements, cut into boxes of
+// box_rows x 64 elements (128 bytes), 128-byte swizzle, zero fill.  Cached by arguments.  0 on success.
+int tb_make_map_bf16(CUtensorMap* out, const void* ptr, long long rows, long long cols, long long stride, int box_rows);

@@ -33,8 +33,7 @@ class DecodeGraph:
         self.layout = StepLayout.from_device_arrays(
             self.tokens, ar(B), self.pos_of, self.slot_of_seq, ar(B + 1), self.start_pos, self.kv_len, ar(B),
             max_new=1, max_kv_len=engine.max_context, all_single=True, all_fresh=False)
-        chunk = int(engine.step_options["attn_chunk"])
-        self.options = dict(engine.step_options, attn_splits=max(1, -(-engine.max_context // chunk)))
+        self.options = dict(engine.step_options, fixed_splits=True)
         self.scratch: Dict[str, torch.Tensor] = {}
         self.graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
         self.slots: Optional[List[int]] = None

@@ -78,6 +78,8 @@ def lib():
         l.tb_kv_append.argtypes = [c_void_p, c_int, c_int, POINTER(KvView), POINTER(Batch), c_void_p]
         l.tb_attn_prefill.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
         l.tb_attn_decode.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
+        l.tb_attn_decode_mma.argtypes = [POINTER(AttnArgs), c_void_p]
+        l.tb_attn_decode_mma_check.argtypes = [POINTER(AttnArgs), c_int]
         l.tb_sample.argtypes = [POINTER(SampleArgs), c_void_p]
         l.tb_decode_prepare.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         l.tb_commit_lengths.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
@@ -186,6 +188,19 @@ def attn_prefill(args: AttnArgs, dtype: torch.dtype, stream: int) -> None:
 
 def attn_decode(args: AttnArgs, dtype: torch.dtype, stream: int) -> None:
     _check(lib().tb_attn_decode(byref(args), dtype_code(dtype), stream))
+
+
+def attn_decode_mma_accepts(args: AttnArgs, dtype: torch.dtype) -> bool:
+    return dtype == torch.bfloat16 and lib().tb_attn_decode_mma_check(byref(args), BF16) == 0
+
+
+def attn_decode_mma(args: AttnArgs, stream: int) -> None:
+    """Decode attention on tensor cores (bfloat16, head_dim 64 or 128), then the merge of the splits."""
+    _check(lib().tb_attn_decode_mma(byref(args), stream))
+
+
+def attn_mma_error() -> int:
+    return int(lib().tb_attn_mma_error())
 
 
 def sample(args: SampleArgs, stream: int) -> None:

@@ -32,6 +32,22 @@ from . import linear
 from .base import MIXERS, NORMS, POSITIONS, Mixer
 
 
+def decode_split(lay, kv_heads: int, options, fast: bool):
+    """(keys per split, number of splits) of decode attention.  Both depend on the batch size and on the
+    context limit only, so a sequence's result is the same whatever the other sequences hold, and a
+    captured step (whose grid is fixed) and an eager one cut the keys at the same places."""
+    bound = int(options.get("max_context", 0)) or lay.max_kv_len
+    if not fast:
+        chunk = int(options.get("attn_chunk", 256))
+    else:       # enough CTAs to fill the machine a few times over, no more: longer chunks pipeline better
+        want = max(1, -(-4 * int(options.get("sm_count", 148)) // (lay.B * kv_heads)))
+        chunk = max(256, -(-(-(-bound // want)) // 64) * 64)
+    # an eager step launches the splits its longest sequence needs; a captured one, whose grid cannot
+    # change, launches what the context limit needs (the extra CTAs leave at once)
+    cover = bound if options.get("fixed_splits") else lay.max_kv_len
+    return chunk, max(1, -(-cover // chunk))
+
+
 class AttentionMixer(Mixer):
     def __init__(self, spec):
         s = spec
@@ -123,15 +139,18 @@ class AttentionMixer(Mixer):
         aa.nh, aa.nkv, aa.hd = s.num_heads, view.kv_heads, hd
         aa.window, aa.scale = s.window or 0, self.scale
         if decode:
-            chunk = int(ctx.options.get("attn_chunk", 256))
-            splits = int(ctx.options.get("attn_splits", 0)) or max(1, -(-lay.max_kv_len // chunk))
+            fast = ctx.options.get("attention", "fast") != "plain" and qkv.dtype == torch.bfloat16 and hd in (64, 128)
+            chunk, splits = decode_split(lay, view.kv_heads, ctx.options, fast)
             need = lay.B * s.num_heads * splits * (hd + 2)
             scratch = ctx.scratch.get("attn_partials")
             if scratch is None or scratch.numel() < need:
                 scratch = ctx.scratch["attn_partials"] = torch.empty(need, dtype=torch.float32, device=ctx.device)
             aa.kv_new, aa.kv_stride = None, 0
             aa.chunk, aa.n_splits, aa.scratch = chunk, splits, scratch.data_ptr()
-            K.attn_decode(aa, qkv.dtype, ctx.stream)
+            if fast and K.attn_decode_mma_accepts(aa, qkv.dtype):
+                K.attn_decode_mma(aa, ctx.stream)
+            else:
+                K.attn_decode(aa, qkv.dtype, ctx.stream)
         else:
             if self.shared:
                 aa.kv_new, aa.kv_stride = None, 0
