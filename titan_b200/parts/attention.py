@@ -111,17 +111,26 @@ class AttentionMixer(Mixer):
         s, lay = self.spec, ctx.layout
         T, Q, KV, hd = lay.T, self.Q, self.KV, s.head_dim
         width = Q if self.shared else Q + 2 * KV
-        qkv = ctx.empty((T, width))
-        linear.matmul(h, self.w_qkv, qkv, linear.EPI_STORE, ctx)
         view = self._view(cache)
         decode = lay.all_single
         tables = self.position.tables(ctx.device)
         inv_freq = tables.get("inv_freq")
+        # A decode step in bfloat16 sums Q | K | V in float32 (K slices of the product add into a zeroed
+        # buffer), and the norm/rotary kernel rounds once, into the query buffer and the cache.
+        wide_sum = decode and not self.shared and h.dtype == torch.bfloat16 and ctx.options.get("gemm", "fast") != "plain"
+        if wide_sum:
+            qkv = torch.zeros((T, width), dtype=torch.float32, device=ctx.device)
+            linear.matmul(h, self.w_qkv, qkv, linear.EPI_ADD, ctx)
+            q_buf, q_stride = ctx.empty((T, Q)), Q
+        else:
+            qkv = ctx.empty((T, width))
+            linear.matmul(h, self.w_qkv, qkv, linear.EPI_STORE, ctx)
+            q_buf, q_stride = qkv, width
         esz = qkv.element_size()
         qa = K.QkArgs()
         qa.inp, qa.in_stride = qkv.data_ptr(), width
-        qa.q_out, qa.q_stride = qkv.data_ptr(), width
-        qa.k_out, qa.k_stride = (None, 0) if self.shared else (qkv.data_ptr() + Q * esz, width)
+        qa.q_out, qa.q_stride = q_buf.data_ptr(), q_stride
+        qa.k_out, qa.k_stride = (None, 0) if (self.shared or wide_sum) else (qkv.data_ptr() + Q * esz, width)
         qa.q_w = None if self.q_norm is None else self.q_norm.data_ptr()
         qa.k_w = None if self.k_norm is None else self.k_norm.data_ptr()
         qa.inv_freq = None if inv_freq is None else inv_freq.data_ptr()
@@ -129,11 +138,11 @@ class AttentionMixer(Mixer):
         qa.rot, qa.nh, qa.nkv, qa.hd = self.position.rotary_dim, s.num_heads, (0 if self.shared else s.num_kv_heads), hd
         qa.pos_of, qa.seq_of, qa.slot_of_seq = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr()
         qa.cache, qa.append, qa.T = view, int(decode and not self.shared), T
-        K.qk_norm_rope(qa, qkv.dtype, qkv.dtype, ctx.stream)
+        K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
 
         attn = ctx.empty((T, Q))
         aa = K.AttnArgs()
-        aa.q, aa.q_stride = qkv.data_ptr(), width
+        aa.q, aa.q_stride = q_buf.data_ptr(), q_stride
         aa.out, aa.out_stride = attn.data_ptr(), Q
         aa.cache, aa.batch = view, lay.c_struct()
         aa.nh, aa.nkv, aa.hd = s.num_heads, view.kv_heads, hd
@@ -156,7 +165,11 @@ class AttentionMixer(Mixer):
                 aa.kv_new, aa.kv_stride = None, 0
             else:
                 aa.kv_new, aa.kv_stride = qkv.data_ptr() + Q * esz, width
-            K.attn_prefill(aa, qkv.dtype, ctx.stream)
+            fast = ctx.options.get("attention", "fast") != "plain" and not self.shared
+            if fast and K.attn_prefill_mma_accepts(aa, qkv.dtype, lay.all_fresh):
+                K.attn_prefill_mma(aa, lay.all_fresh, ctx.stream)
+            else:
+                K.attn_prefill(aa, qkv.dtype, ctx.stream)
             if not self.shared:
                 K.kv_append(qkv[:, Q:], view, lay.c_struct(), ctx.stream)
         linear.matmul(attn, self.w_o, out, linear.EPI_ADD, ctx)
