@@ -125,7 +125,7 @@ struct TcArgs {
     int atomic;      // ADD epilogue through atomics (several K slices)
 };
 
-template <int BN> constexpr int stages_for() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : 6); }
+template <int BN> constexpr int stages_for() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : 4); }   // small tiles: two or three CTAs per SM
 template <int BN> constexpr int tmem_cols_for() { return BN < 32 ? 32 : BN; }
 template <int BN> constexpr size_t smem_for() {
     return 1024 /*alignment slack*/ + (size_t)stages_for<BN>() * (BM * BK * 2 + BN * BK * 2) + 256;
@@ -140,9 +140,21 @@ __device__ __forceinline__ void epilogue_chunk(const float* v, const TcArgs& a, 
         if (m >= a.rows_a) return;
         if (EPI == TB_EPI_SWIGLU) {
             __nv_bfloat16* o = (__nv_bfloat16*)a.out + (size_t)m * a.ldo + col0 / 2;
+            if (col0 + NV <= a.rows_b && NV == 32) {      // 16 outputs: two 16-byte stores
 #pragma unroll
-            for (int j = 0; j < NV; j += 2)
-                if (col0 + j + 1 < a.rows_b) o[j / 2] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+                for (int j = 0; j < NV; j += 16) {
+                    uint4 pk;
+                    pk.x = pack_bf16(silu_mul(v[j], v[j + 1]), silu_mul(v[j + 2], v[j + 3]));
+                    pk.y = pack_bf16(silu_mul(v[j + 4], v[j + 5]), silu_mul(v[j + 6], v[j + 7]));
+                    pk.z = pack_bf16(silu_mul(v[j + 8], v[j + 9]), silu_mul(v[j + 10], v[j + 11]));
+                    pk.w = pack_bf16(silu_mul(v[j + 12], v[j + 13]), silu_mul(v[j + 14], v[j + 15]));
+                    *reinterpret_cast<uint4*>(o + j / 2) = pk;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < NV; j += 2)
+                    if (col0 + j + 1 < a.rows_b) o[j / 2] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+            }
         } else if (EPI == TB_EPI_STORE) {
             __nv_bfloat16* o = (__nv_bfloat16*)a.out + (size_t)m * a.ldo + col0;
             if (col0 + NV <= a.rows_b) {            // whole chunk inside: 16-byte stores (ldo and col0 are multiples of 8)
@@ -161,13 +173,15 @@ __device__ __forceinline__ void epilogue_chunk(const float* v, const TcArgs& a, 
         } else {
             float* o = (float*)a.out + (size_t)m * a.ldo + col0;
             if (col0 + NV <= a.rows_b && !a.atomic && (a.ldo & 3) == 0) {
+                float4 old[NV / 4];
+                if (EPI == TB_EPI_ADD) {            // all loads first: they are independent of the stores below
+#pragma unroll
+                    for (int j = 0; j < NV; j += 4) old[j / 4] = *reinterpret_cast<const float4*>(o + j);
+                }
 #pragma unroll
                 for (int j = 0; j < NV; j += 4) {
                     float4 r = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    if (EPI == TB_EPI_ADD) {
-                        const float4 old = *reinterpret_cast<const float4*>(o + j);
-                        r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
-                    }
+                    if (EPI == TB_EPI_ADD) { r.x += old[j / 4].x; r.y += old[j / 4].y; r.z += old[j / 4].z; r.w += old[j / 4].w; }
                     *reinterpret_cast<float4*>(o + j) = r;
                 }
             } else {
@@ -361,7 +375,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         const int tiles = (N + BM - 1) / BM;
         int s = 1;
         if (epi == TB_EPI_ADD) {
-            s = splits > 0 ? splits : (2 * 148 + tiles - 1) / tiles;
+            s = splits > 0 ? splits : (224 + tiles / 2) / tiles;        // about one and a half CTAs per SM
             const int max_s = kb / 4 > 0 ? kb / 4 : 1;              // at least four 64-wide blocks per slice
             s = s < 1 ? 1 : (s > max_s ? max_s : s);
         }

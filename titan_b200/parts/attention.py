@@ -148,7 +148,7 @@ class AttentionMixer(Mixer):
         aa.nh, aa.nkv, aa.hd = s.num_heads, view.kv_heads, hd
         aa.window, aa.scale = s.window or 0, self.scale
         if decode:
-            fast = ctx.options.get("attention", "fast") != "plain" and qkv.dtype == torch.bfloat16 and hd in (64, 128)
+            fast = ctx.options.get("attention", "fast") != "plain" and q_buf.dtype == torch.bfloat16 and hd in (64, 128)
             chunk, splits = decode_split(lay, view.kv_heads, ctx.options, fast)
             need = lay.B * s.num_heads * splits * (hd + 2)
             scratch = ctx.scratch.get("attn_partials")
@@ -156,20 +156,20 @@ class AttentionMixer(Mixer):
                 scratch = ctx.scratch["attn_partials"] = torch.empty(need, dtype=torch.float32, device=ctx.device)
             aa.kv_new, aa.kv_stride = None, 0
             aa.chunk, aa.n_splits, aa.scratch = chunk, splits, scratch.data_ptr()
-            if fast and K.attn_decode_mma_accepts(aa, qkv.dtype):
+            if fast and K.attn_decode_mma_accepts(aa, q_buf.dtype):
                 K.attn_decode_mma(aa, ctx.stream)
             else:
-                K.attn_decode(aa, qkv.dtype, ctx.stream)
+                K.attn_decode(aa, q_buf.dtype, ctx.stream)
         else:
             if self.shared:
                 aa.kv_new, aa.kv_stride = None, 0
             else:
                 aa.kv_new, aa.kv_stride = qkv.data_ptr() + Q * esz, width
             fast = ctx.options.get("attention", "fast") != "plain" and not self.shared
-            if fast and K.attn_prefill_mma_accepts(aa, qkv.dtype, lay.all_fresh):
+            if fast and K.attn_prefill_mma_accepts(aa, q_buf.dtype, lay.all_fresh):
                 K.attn_prefill_mma(aa, lay.all_fresh, ctx.stream)
             else:
-                K.attn_prefill(aa, qkv.dtype, ctx.stream)
+                K.attn_prefill(aa, q_buf.dtype, ctx.stream)
             if not self.shared:
                 K.kv_append(qkv[:, Q:], view, lay.c_struct(), ctx.stream)
         linear.matmul(attn, self.w_o, out, linear.EPI_ADD, ctx)
