@@ -122,6 +122,8 @@ __device__ __forceinline__ void load_query(float* qs, const T* q, int hd, int la
 // grid (T, ceil(nh / ATT_WARPS)); warp = one head of one query token.
 template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_prefill_kernel(AttnArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float q_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x, h = blockIdx.y * ATT_WARPS + warp;
@@ -153,6 +155,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_prefill_kernel(AttnArgs a
 // hd unnormalised outputs, then m, then l (l = 0: the split saw no key).
 template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(AttnArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float q_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
@@ -190,6 +194,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(AttnArgs a)
 // independent of one another.
 template <typename T>
 __global__ void attn_merge_kernel(AttnArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, hd = a.hd, stride = hd + 2;
     const float* part = a.scratch + (size_t)(b * a.nh + h) * a.n_splits * stride;
     const int used = min(a.n_splits, (a.batch.kv_len[b] + a.chunk - 1) / a.chunk);
@@ -244,8 +250,8 @@ extern "C" int tb_attn_prefill(const AttnArgs* args, int dtype, cudaStream_t str
     TB_REQUIRE(a.kv_new || a.cache.storage, "attn_prefill: neither new keys nor a cache");
     dim3 grid(a.batch.T, (a.nh + ATT_WARPS - 1) / ATT_WARPS);
     const size_t smem = (size_t)ATT_WARPS * a.hd * sizeof(float);
-    if (dtype == TB_F32) attn_prefill_kernel<float><<<grid, ATT_WARPS * 32, smem, stream>>>(a);
-    else if (dtype == TB_BF16) attn_prefill_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, smem, stream>>>(a);
+    if (dtype == TB_F32) tb_launch(attn_prefill_kernel<float>, grid, ATT_WARPS * 32, smem, stream, a);
+    else if (dtype == TB_BF16) tb_launch(attn_prefill_kernel<__nv_bfloat16>, grid, ATT_WARPS * 32, smem, stream, a);
     else TB_REQUIRE(false, "attn_prefill: unknown dtype %d", dtype);
     TB_CHECK_LAUNCH("attn_prefill");
     return 0;
@@ -254,8 +260,8 @@ extern "C" int tb_attn_prefill(const AttnArgs* args, int dtype, cudaStream_t str
 extern "C" int tb_attn_merge(const AttnArgs* args, int dtype, cudaStream_t stream) {
     AttnArgs a = *args;
     dim3 mgrid(a.batch.B, a.nh);
-    if (dtype == TB_F32) attn_merge_kernel<float><<<mgrid, 32, 0, stream>>>(a);
-    else if (dtype == TB_BF16) attn_merge_kernel<__nv_bfloat16><<<mgrid, 32, 0, stream>>>(a);
+    if (dtype == TB_F32) tb_launch(attn_merge_kernel<float>, mgrid, 32, 0, stream, a);
+    else if (dtype == TB_BF16) tb_launch(attn_merge_kernel<__nv_bfloat16>, mgrid, 32, 0, stream, a);
     else TB_REQUIRE(false, "attn_merge: unknown dtype %d", dtype);
     TB_CHECK_LAUNCH("attn_merge");
     return 0;
@@ -271,11 +277,11 @@ extern "C" int tb_attn_decode(const AttnArgs* args, int dtype, cudaStream_t stre
     dim3 grid(a.batch.B, a.nkv, a.n_splits), mgrid(a.batch.B, a.nh);
     const size_t smem = (size_t)ATT_WARPS * a.hd * sizeof(float);
     if (dtype == TB_F32) {
-        attn_decode_kernel<float><<<grid, ATT_WARPS * 32, smem, stream>>>(a);
-        attn_merge_kernel<float><<<mgrid, 32, 0, stream>>>(a);
+        tb_launch(attn_decode_kernel<float>, grid, ATT_WARPS * 32, smem, stream, a);
+        tb_launch(attn_merge_kernel<float>, mgrid, 32, 0, stream, a);
     } else if (dtype == TB_BF16) {
-        attn_decode_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, smem, stream>>>(a);
-        attn_merge_kernel<__nv_bfloat16><<<mgrid, 32, 0, stream>>>(a);
+        tb_launch(attn_decode_kernel<__nv_bfloat16>, grid, ATT_WARPS * 32, smem, stream, a);
+        tb_launch(attn_merge_kernel<__nv_bfloat16>, mgrid, 32, 0, stream, a);
     } else TB_REQUIRE(false, "attn_decode: unknown dtype %d", dtype);
     TB_CHECK_LAUNCH("attn_decode");
     return 0;

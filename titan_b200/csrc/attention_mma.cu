@@ -74,6 +74,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
+    pdl_launch_dependents();
+    pdl_wait();                                         // lengths, queries and the newest cache row come from earlier kernels
     const int len = a.kv_len[b];
     if (split * a.chunk >= len) return;                 // uniform over the CTA; the merge skips these splits
     const int group = a.nh / a.nkv;
@@ -261,6 +263,8 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, PreArgs a) 
     uint64_t* empty = full + STAGES;
     uint64_t* qbar = empty + STAGES;
 
+    pdl_launch_dependents();
+    pdl_wait();
     // which sequence and which block of it (blocks are numbered from the heaviest)
     int rem = blockIdx.x, seq = -1, blk = 0, tok0 = 0, n = 0;
     for (int s = 0; s < a.B; ++s) {
@@ -428,7 +432,7 @@ static int launch_decode(const CUtensorMap& map, const DecArgs& d, dim3 grid, cu
         TB_REQUIRE(e == cudaSuccess, "attn_decode_mma: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    attn_decode_mma_kernel<HD, WIDE><<<grid, DEC_THREADS, smem, stream>>>(map, d);
+    tb_launch(attn_decode_mma_kernel<HD, WIDE>, grid, DEC_THREADS, smem, stream, map, d);
     return 0;
 }
 
@@ -486,7 +490,7 @@ static int launch_prefill(const CUtensorMap& map, const PreArgs& p, dim3 grid, c
         TB_REQUIRE(e == cudaSuccess, "attn_prefill_mma: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    attn_prefill_mma_kernel<HD><<<grid, DEC_THREADS, smem, stream>>>(map, p);
+    tb_launch(attn_prefill_mma_kernel<HD>, grid, DEC_THREADS, smem, stream, map, p);
     return 0;
 }
 

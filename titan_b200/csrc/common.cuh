@@ -11,6 +11,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <utility>
+
 #define TB_F32 0
 #define TB_BF16 1
 
@@ -111,3 +113,25 @@ __device__ __forceinline__ size_t kv_row_offset(const TbKvView& c, int slot, int
 __device__ __forceinline__ size_t kv_half_elems(const TbKvView& c) {
     return (size_t)c.num_pages * c.kv_heads * c.page_size * c.head_dim;
 }
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// Kernels of a step are launched so that a kernel may start while its predecessor in the stream is
+// still finishing (its blocks are scheduled once every block of the predecessor has called
+// pdl_launch_dependents or exited).  A kernel calls pdl_wait() before it reads or writes anything an
+// earlier kernel wrote; what it does before that (barrier set-up, tensor-memory allocation, loads of
+// weights, which no kernel writes) overlaps the predecessor's tail.  Every kernel launched this way
+// calls pdl_wait() on every path, so completion stays transitive along the stream.
+extern int g_tb_pdl;      // 1: on (default); tb_set_pdl(0) launches everything fully serialised
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t tb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = g_tb_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

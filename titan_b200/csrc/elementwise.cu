@@ -12,6 +12,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int H, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     int tok = tokens[t];
     tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);   // ids are validated on the host; never read outside
@@ -25,9 +27,9 @@ extern "C" int tb_embed(const void* table, int dtype, const int* tokens, float* 
     TB_REQUIRE(T > 0 && H > 0 && V > 0, "embed: sizes must be positive (T=%d H=%d V=%d)", T, H, V);
     const int threads = H >= 1024 ? 256 : 128;
     if (dtype == TB_F32)
-        embed_kernel<float><<<T, threads, 0, stream>>>((const float*)table, tokens, out, H, V);
+        tb_launch(embed_kernel<float>, T, threads, 0, stream, (const float*)table, tokens, out, H, V);
     else if (dtype == TB_BF16)
-        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, H, V);
+        tb_launch(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, H, V);
     else
         TB_REQUIRE(false, "embed: unknown dtype %d", dtype);
     TB_CHECK_LAUNCH("embed");
@@ -39,6 +41,8 @@ extern "C" int tb_embed(const void* table, int dtype, const int* tokens, float* 
 template <typename T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
                                const int* __restrict__ rows, int H, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[33];
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
@@ -58,9 +62,9 @@ extern "C" int tb_rmsnorm(const float* x, const float* w, void* y, int dtype, co
     TB_REQUIRE(n_rows > 0 && H > 0, "rmsnorm: sizes must be positive (rows=%d H=%d)", n_rows, H);
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 64);
     if (dtype == TB_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, (float*)y, rows, H, eps);
+        tb_launch(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, w, (float*)y, rows, H, eps);
     else if (dtype == TB_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, w, (__nv_bfloat16*)y, rows, H, eps);
+        tb_launch(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, w, (__nv_bfloat16*)y, rows, H, eps);
     else
         TB_REQUIRE(false, "rmsnorm: unknown dtype %d", dtype);
     TB_CHECK_LAUNCH("rmsnorm");
@@ -82,12 +86,15 @@ struct QkArgs {
     float eps; int rot; int nh; int nkv; int hd;
     const int* pos_of; const int* seq_of; const int* slot_of_seq;
     TbKvView cache; int append; int T;
+    int zero_in;                            // after reading a head, write zeros over it (an accumulation buffer is left clean)
 };
 
 #define QK_MAXE 8   // head_dim <= 32 * QK_MAXE
 
 template <typename TIn, typename TOut>
 __global__ void qk_norm_rope_kernel(QkArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float head_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x;
@@ -107,6 +114,7 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
         const int e = lane + 32 * j;
         v[j] = e < hd ? ldf(x + e) : 0.f;
         ss += v[j] * v[j];
+        if (a.zero_in && e < hd) const_cast<TIn*>(x)[e] = TIn(0.f);
     }
     const int pos = a.pos_of[t];
     const int slot = a.slot_of_seq[a.seq_of[t]];
@@ -158,6 +166,8 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     TB_REQUIRE(a.T > 0 && a.nh > 0 && a.nkv >= 0, "qk_norm_rope: sizes must be positive");
     TB_REQUIRE(a.hd > 0 && a.hd <= 32 * QK_MAXE, "qk_norm_rope: head_dim %d is not in 1..%d", a.hd, 32 * QK_MAXE);
     TB_REQUIRE(a.rot >= 0 && a.rot <= a.hd && a.rot % 2 == 0, "qk_norm_rope: rotary_dim %d must be even and <= head_dim %d", a.rot, a.hd);
+    TB_REQUIRE(!a.zero_in || (a.append && a.in != a.q_out && a.k_out == nullptr),
+               "qk_norm_rope: zeroing the input needs every head to be read (append) and outputs elsewhere");
     TB_REQUIRE(!a.append || (a.cache.storage && a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv),
                "qk_norm_rope: the cache view does not match the heads");
     const int warps = 4;
@@ -165,11 +175,11 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     dim3 grid(a.T, (n_heads + warps - 1) / warps);
     const size_t smem = (size_t)warps * a.hd * sizeof(float);
     if (in_dtype == TB_F32 && out_dtype == TB_F32)
-        qk_norm_rope_kernel<float, float><<<grid, warps * 32, smem, stream>>>(a);
+        tb_launch(qk_norm_rope_kernel<float, float>, grid, warps * 32, smem, stream, a);
     else if (in_dtype == TB_BF16 && out_dtype == TB_BF16)
-        qk_norm_rope_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, warps * 32, smem, stream>>>(a);
+        tb_launch(qk_norm_rope_kernel<__nv_bfloat16, __nv_bfloat16>, grid, warps * 32, smem, stream, a);
     else if (in_dtype == TB_F32 && out_dtype == TB_BF16)
-        qk_norm_rope_kernel<float, __nv_bfloat16><<<grid, warps * 32, smem, stream>>>(a);
+        tb_launch(qk_norm_rope_kernel<float, __nv_bfloat16>, grid, warps * 32, smem, stream, a);
     else
         TB_REQUIRE(false, "qk_norm_rope: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
     TB_CHECK_LAUNCH("qk_norm_rope");
@@ -182,6 +192,8 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
 template <typename T>
 __global__ void kv_append_kernel(const T* __restrict__ kv, int stride, TbKvView c, const int* pos_of,
                                  const int* seq_of, const int* slot_of_seq, const int* kv_len) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x, h2 = blockIdx.y;            // h2 < 2 * kv_heads
     const int seq = seq_of[t], pos = pos_of[t];
     if (c.ring_rows && pos < kv_len[seq] - c.ring_rows) return;
@@ -198,9 +210,9 @@ extern "C" int tb_kv_append(const void* kv, int stride, int dtype, const TbKvVie
     dim3 grid(b->T, 2 * c.kv_heads);
     const int threads = c.head_dim >= 64 ? 64 : 32;
     if (dtype == TB_F32)
-        kv_append_kernel<float><<<grid, threads, 0, stream>>>((const float*)kv, stride, c, b->pos_of, b->seq_of, b->slot_of_seq, b->kv_len);
+        tb_launch(kv_append_kernel<float>, grid, threads, 0, stream, (const float*)kv, stride, c, b->pos_of, b->seq_of, b->slot_of_seq, b->kv_len);
     else if (dtype == TB_BF16)
-        kv_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)kv, stride, c, b->pos_of, b->seq_of, b->slot_of_seq, b->kv_len);
+        tb_launch(kv_append_kernel<__nv_bfloat16>, grid, threads, 0, stream, (const __nv_bfloat16*)kv, stride, c, b->pos_of, b->seq_of, b->slot_of_seq, b->kv_len);
     else
         TB_REQUIRE(false, "kv_append: unknown dtype %d", dtype);
     TB_CHECK_LAUNCH("kv_append");
@@ -216,6 +228,8 @@ extern "C" int tb_kv_append(const void* kv, int stride, int dtype, const TbKvVie
 __global__ void decode_prepare_kernel(const int* __restrict__ slot_of_seq, const int* __restrict__ seq_len,
                                       const int* __restrict__ last_token, int feed_last, int* tokens, int* pos_of,
                                       int* start_pos, int* kv_len, int B) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
     const int slot = slot_of_seq[b], len = seq_len[slot];
@@ -228,8 +242,8 @@ __global__ void decode_prepare_kernel(const int* __restrict__ slot_of_seq, const
 extern "C" int tb_decode_prepare(const int* slot_of_seq, const int* seq_len, const int* last_token, int feed_last,
                                  int* tokens, int* pos_of, int* start_pos, int* kv_len, int B, cudaStream_t stream) {
     TB_REQUIRE(B > 0, "decode_prepare: no sequences");
-    decode_prepare_kernel<<<(B + 127) / 128, 128, 0, stream>>>(slot_of_seq, seq_len, last_token, feed_last, tokens,
-                                                               pos_of, start_pos, kv_len, B);
+    tb_launch(decode_prepare_kernel, (B + 127) / 128, 128, 0, stream, slot_of_seq, seq_len, last_token, feed_last, tokens,
+              pos_of, start_pos, kv_len, B);
     TB_CHECK_LAUNCH("decode_prepare");
     return 0;
 }
@@ -237,13 +251,15 @@ extern "C" int tb_decode_prepare(const int* slot_of_seq, const int* seq_len, con
 // seq_len[slot_of_seq[b]] = kv_len[b]: the device copy of the lengths after a step.
 __global__ void commit_lengths_kernel(const int* __restrict__ slot_of_seq, const int* __restrict__ kv_len,
                                       int* seq_len, int B) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < B) seq_len[slot_of_seq[b]] = kv_len[b];
 }
 
 extern "C" int tb_commit_lengths(const int* slot_of_seq, const int* kv_len, int* seq_len, int B, cudaStream_t stream) {
     TB_REQUIRE(B > 0, "commit_lengths: no sequences");
-    commit_lengths_kernel<<<(B + 127) / 128, 128, 0, stream>>>(slot_of_seq, kv_len, seq_len, B);
+    tb_launch(commit_lengths_kernel, (B + 127) / 128, 128, 0, stream, slot_of_seq, kv_len, seq_len, B);
     TB_CHECK_LAUNCH("commit_lengths");
     return 0;
 }

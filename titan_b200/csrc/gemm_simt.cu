@@ -22,6 +22,8 @@ template <typename T, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, void* __restrict__ out,
                  int M, int N, int K, int ldx, int ldo) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -91,10 +93,10 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, int ldx
     const T* x = (const T*)X;
     const T* w = (const T*)W;
     switch (epi) {
-        case TB_EPI_STORE: gemm_simt_kernel<T, TB_EPI_STORE><<<grid, 256, 0, stream>>>(x, w, out, M, N, K, ldx, ldo); break;
-        case TB_EPI_F32: gemm_simt_kernel<T, TB_EPI_F32><<<grid, 256, 0, stream>>>(x, w, out, M, N, K, ldx, ldo); break;
-        case TB_EPI_ADD: gemm_simt_kernel<T, TB_EPI_ADD><<<grid, 256, 0, stream>>>(x, w, out, M, N, K, ldx, ldo); break;
-        case TB_EPI_SWIGLU: gemm_simt_kernel<T, TB_EPI_SWIGLU><<<grid, 256, 0, stream>>>(x, w, out, M, N, K, ldx, ldo); break;
+        case TB_EPI_STORE: tb_launch(gemm_simt_kernel<T, TB_EPI_STORE>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo); break;
+        case TB_EPI_F32: tb_launch(gemm_simt_kernel<T, TB_EPI_F32>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo); break;
+        case TB_EPI_ADD: tb_launch(gemm_simt_kernel<T, TB_EPI_ADD>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo); break;
+        case TB_EPI_SWIGLU: tb_launch(gemm_simt_kernel<T, TB_EPI_SWIGLU>, grid, 256, 0, stream, x, w, out, M, N, K, ldx, ldo); break;
         default: tb_set_error("gemm: unknown epilogue %d", epi); return 1;
     }
     return 0;

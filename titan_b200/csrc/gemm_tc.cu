@@ -109,7 +109,9 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+// silu(g) * u with the fast exponential and division: the result is rounded to bfloat16 anyway, and the
+// epilogue warps run one per scheduler, so every instruction here is on the critical path of a tile.
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&p);
@@ -127,8 +129,10 @@ struct TcArgs {
 
 template <int BN> constexpr int stages_for() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : 4); }   // small tiles: two or three CTAs per SM
 template <int BN> constexpr int tmem_cols_for() { return BN < 32 ? 32 : BN; }
-template <int BN> constexpr size_t smem_for() {
-    return 1024 /*alignment slack*/ + (size_t)stages_for<BN>() * (BM * BK * 2 + BN * BK * 2) + 256;
+constexpr int EPI_TILE_FLOATS = 32 * 33;      // one warp's 32 x 32 transposition tile, padded against bank conflicts
+template <int BN, bool SWAP> constexpr size_t smem_for() {
+    return 1024 /*alignment slack*/ + (size_t)stages_for<BN>() * (BM * BK * 2 + BN * BK * 2) + 256 +
+           (SWAP ? 0 : 4 * EPI_TILE_FLOATS * sizeof(float));
 }
 
 // Epilogue of one 32-column chunk held by one thread (row ``r`` of the tile).
@@ -214,6 +218,38 @@ __device__ __forceinline__ void epilogue_chunk(const float* v, const TcArgs& a, 
     }
 }
 
+// Plain mode: one warp's 32 rows x 32 output columns.  ``val`` holds this lane's row; the tile is turned
+// in shared memory so that afterwards a lane holds a column and the warp reads and writes whole rows of
+// the output (128 bytes of float32, 64 of bfloat16), eight rows in flight at a time.
+template <int EPI>
+__device__ __forceinline__ void epilogue_rows(const float* val, float* tile, const TcArgs& a, int row0, int col0,
+                                              int n_cols, int lane) {
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = val[j];
+    __syncwarp();
+    const int col = col0 + lane;
+    if (col >= n_cols) return;
+#pragma unroll
+    for (int r0 = 0; r0 < 32; r0 += 8) {
+        float old[8];
+        if (EPI == TB_EPI_ADD) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+                old[r] = (row0 + r0 + r < a.rows_a) ? ((const float*)a.out)[(size_t)(row0 + r0 + r) * a.ldo + col] : 0.f;
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const int m = row0 + r0 + r;
+            if (m >= a.rows_a) continue;
+            const float v = tile[(r0 + r) * 33 + lane];
+            if (EPI == TB_EPI_STORE || EPI == TB_EPI_SWIGLU) ((__nv_bfloat16*)a.out)[(size_t)m * a.ldo + col] = __float2bfloat16_rn(v);
+            else if (EPI == TB_EPI_F32) ((float*)a.out)[(size_t)m * a.ldo + col] = v;
+            else ((float*)a.out)[(size_t)m * a.ldo + col] = old[r] + v;
+        }
+    }
+}
+
 template <int BN, int EPI, bool SWAP>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs a) {
@@ -228,6 +264,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* empty = full + STAGES;
     uint64_t* accum = empty + STAGES;
     uint32_t* tmem_slot = (uint32_t*)(accum + 1);
+    float* epi_tiles = (float*)(base + STAGES * (A_BYTES + B_BYTES) + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_a = blockIdx.y;                          // tile index along A's rows
@@ -237,6 +274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int kb1 = min(kb_total, kb0 + a.k_blocks_per_split);
     const int n_kb = kb1 - kb0;
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
         mbar_init(accum, 1);
@@ -251,9 +289,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (n_kb > 0) {
         if (warp == 0) {
             if (lane == 0) {
-                for (int i = 0; i < n_kb; ++i) {
+                // The weight operand (A in swap mode, B in plain mode) is written by no kernel, so its
+                // tiles for the first stages are requested before the wait on the previous kernel.
+                const int pre = n_kb < STAGES ? n_kb : STAGES;
+                for (int i = 0; i < pre; ++i) {
+                    mbar_expect_tx(full + i, A_BYTES + B_BYTES);
+                    if (SWAP) tma_load_2d(smem_a + i * A_BYTES, &map_a, full + i, (kb0 + i) * BK, tile_a * BM);
+                    else tma_load_2d(smem_b + i * B_BYTES, &map_b, full + i, (kb0 + i) * BK, tile_b * BN);
+                }
+                pdl_wait();
+                for (int i = 0; i < pre; ++i) {
+                    if (SWAP) tma_load_2d(smem_b + i * B_BYTES, &map_b, full + i, (kb0 + i) * BK, tile_b * BN);
+                    else tma_load_2d(smem_a + i * A_BYTES, &map_a, full + i, (kb0 + i) * BK, tile_a * BM);
+                }
+                for (int i = pre; i < n_kb; ++i) {
                     const int s = i % STAGES, round = i / STAGES;
-                    if (round > 0) mbar_wait(empty + s, (round - 1) & 1, 1);
+                    mbar_wait(empty + s, (round - 1) & 1, 1);
                     mbar_expect_tx(full + s, A_BYTES + B_BYTES);
                     tma_load_2d(smem_a + s * A_BYTES, &map_a, full + s, (kb0 + i) * BK, tile_a * BM);
                     tma_load_2d(smem_b + s * B_BYTES, &map_b, full + s, (kb0 + i) * BK, tile_b * BN);
@@ -261,6 +312,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         } else if (warp == 1) {
             if (lane == 0) {
+                pdl_wait();                                   // polling starts once the previous kernel is through
                 constexpr uint32_t idesc = instr_desc(BM, BN);
                 for (int i = 0; i < n_kb; ++i) {
                     const int s = i % STAGES, round = i / STAGES;
@@ -276,12 +328,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tc_commit(accum);
             }
         } else {
+            pdl_wait();
             mbar_wait(accum, 0, 3);
             tc_fence_after();
             const int quarter = warp & 3;                     // a warp reads TMEM lanes 32 * (warp % 4) ..
             const int row = tile_a * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16);
-            if (BN >= 32) {
+            if (!SWAP && EPI == TB_EPI_ADD) {       // read-modify-write of the residual: whole rows per warp
+                float* tile = epi_tiles + quarter * EPI_TILE_FLOATS;
+                const int row0 = tile_a * BM + quarter * 32;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    float v[32];
+                    tmem_ld32(taddr + c, v);
+                    epilogue_rows<EPI>(v, tile, a, row0, tile_b * BN + c, a.rows_b, lane);
+                }
+            } else if (BN >= 32) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 32) {
                     float v[32];
@@ -295,6 +357,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     }
+    pdl_wait();                                               // on every path (cheap once it has been passed)
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -307,13 +370,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 template <int BN, int EPI, bool SWAP>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t stream) {
     static bool configured = false;
-    constexpr size_t smem = smem_for<BN>();
+    constexpr size_t smem = smem_for<BN, SWAP>();
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         TB_REQUIRE(e == cudaSuccess, "gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    gemm_tc_kernel<BN, EPI, SWAP><<<grid, THREADS, smem, stream>>>(ma, mb, a);
+    tb_launch(gemm_tc_kernel<BN, EPI, SWAP>, grid, THREADS, smem, stream, ma, mb, a);
     return 0;
 }
 

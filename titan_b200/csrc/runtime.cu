@@ -25,3 +25,7 @@ extern "C" int tb_device_arch() {
 }
 
 extern "C" int tb_abi_version() { return 1; }
+
+int g_tb_pdl = 1;
+// Programmatic dependent launch on (1) or off (0) for every kernel launched afterwards.
+extern "C" void tb_set_pdl(int on) { g_tb_pdl = on ? 1 : 0; }

@@ -160,6 +160,8 @@ __device__ int nth_in_order(int V, PFn pred, u64 need, Shared& sh) {
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(SampleArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ Shared sh;
     const int row = blockIdx.x, slot = a.slot_of_row[row], V = a.V, tid = threadIdx.x;
     const float temperature = a.temperature[slot];
@@ -276,7 +278,7 @@ extern "C" int tb_sample(const SampleArgs* args, cudaStream_t stream) {
     SampleArgs a = *args;
     TB_REQUIRE(a.B > 0 && a.V > 0 && a.ld >= a.V, "sample: bad sizes (B=%d V=%d ld=%d)", a.B, a.V, a.ld);
     TB_REQUIRE(!a.seen || a.seen_words * 32 >= a.V, "sample: the seen-bitmap is shorter than the vocabulary");
-    sample_kernel<<<a.B, SAMPLE_THREADS, 0, stream>>>(a);
+    tb_launch(sample_kernel, a.B, SAMPLE_THREADS, 0, stream, a);
     TB_CHECK_LAUNCH("sample");
     return 0;
 }
@@ -284,6 +286,8 @@ extern "C" int tb_sample(const SampleArgs* args, cudaStream_t stream) {
 // Marks the tokens of a step as seen (context of the repetition penalty).
 __global__ void mark_seen_kernel(const int* tokens, const int* seq_of, const int* slot_of_seq, unsigned* seen,
                                  int seen_words, int T) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= T) return;
     const int tok = tokens[t];
@@ -294,7 +298,7 @@ __global__ void mark_seen_kernel(const int* tokens, const int* seq_of, const int
 extern "C" int tb_mark_seen(const int* tokens, const int* seq_of, const int* slot_of_seq, unsigned* seen,
                             int seen_words, int T, cudaStream_t stream) {
     TB_REQUIRE(T > 0 && seen, "mark_seen: nothing to mark");
-    mark_seen_kernel<<<(T + 255) / 256, 256, 0, stream>>>(tokens, seq_of, slot_of_seq, seen, seen_words, T);
+    tb_launch(mark_seen_kernel, (T + 255) / 256, 256, 0, stream, tokens, seq_of, slot_of_seq, seen, seen_words, T);
     TB_CHECK_LAUNCH("mark_seen");
     return 0;
 }

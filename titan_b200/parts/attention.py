@@ -119,7 +119,10 @@ class AttentionMixer(Mixer):
         # buffer), and the norm/rotary kernel rounds once, into the query buffer and the cache.
         wide_sum = decode and not self.shared and h.dtype == torch.bfloat16 and ctx.options.get("gemm", "fast") != "plain"
         if wide_sum:
-            qkv = torch.zeros((T, width), dtype=torch.float32, device=ctx.device)
+            key = f"qkv_sum_{T}x{width}"            # zeroed once; the norm/rotary kernel leaves it zeroed again
+            qkv = ctx.scratch.get(key)
+            if qkv is None:
+                qkv = ctx.scratch[key] = torch.zeros((T, width), dtype=torch.float32, device=ctx.device)
             linear.matmul(h, self.w_qkv, qkv, linear.EPI_ADD, ctx)
             q_buf, q_stride = ctx.empty((T, Q)), Q
         else:
@@ -138,6 +141,7 @@ class AttentionMixer(Mixer):
         qa.rot, qa.nh, qa.nkv, qa.hd = self.position.rotary_dim, s.num_heads, (0 if self.shared else s.num_kv_heads), hd
         qa.pos_of, qa.seq_of, qa.slot_of_seq = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr()
         qa.cache, qa.append, qa.T = view, int(decode and not self.shared), T
+        qa.zero_in = int(wide_sum)
         K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
 
         attn = ctx.empty((T, Q))
