@@ -18,24 +18,12 @@
 // query head h reads kv head h / (nh/nkv), partials merged with exp(m_s - m_max).
 #include <float.h>
 
+#include "attention_args.h"
 #include "common.cuh"
 
 #define ATT_MAXE 8        // head_dim <= 256
 #define ATT_WARPS 4
 
-struct AttnArgs {
-    const void* q; int q_stride;            // [T][q_stride], head h at h*hd
-    const void* kv_new; int kv_stride;      // [T][kv_stride]: K heads then V heads of this step (may be null)
-    void* out; int out_stride;              // [T][out_stride]
-    TbKvView cache;                         // storage may be null when every key is in kv_new
-    TbBatch batch;
-    int nh; int nkv; int hd;
-    int window;                             // 0: all keys
-    float scale;
-    int chunk;                              // decode: keys per split
-    int n_splits;                           // decode: grid.z
-    float* scratch;                         // decode: [B][nh][n_splits][hd + 2]
-};
 
 template <typename T> __device__ __forceinline__ void load8(const T* p, float* o);
 template <> __device__ __forceinline__ void load8<float>(const float* p, float* o) {

@@ -18,6 +18,7 @@
 // scalar FMA (engine/engine-cuda/kernels/paged_attention.cu:200-309).
 #include <float.h>
 
+#include "attention_args.h"
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -405,20 +406,6 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, PreArgs a) 
 
 }  // namespace
 
-// Same argument block as the plain kernels (attention.cu).
-struct AttnArgs {
-    const void* q; int q_stride;
-    const void* kv_new; int kv_stride;
-    void* out; int out_stride;
-    TbKvView cache;
-    TbBatch batch;
-    int nh; int nkv; int hd;
-    int window;
-    float scale;
-    int chunk;
-    int n_splits;
-    float* scratch;
-};
 
 extern "C" int tb_attn_merge(const AttnArgs* args, int dtype, cudaStream_t stream);
 
