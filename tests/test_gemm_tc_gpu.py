@@ -21,7 +21,8 @@ def stream():
 
 
 SHAPES = [(1, 128, 64), (5, 384, 256), (16, 200, 72), (17, 1000, 520), (40, 130, 4096), (64, 509, 96), (100, 256, 128),
-          (128, 256, 64), (200, 300, 1032), (333, 1000, 200), (256, 128, 512)]
+          (128, 256, 64), (200, 300, 1032), (333, 1000, 200), (256, 128, 512),
+          (1100, 5000, 520), (2048, 6144, 256)]      # more tiles than SMs: a CTA walks over two or three tiles
 
 
 @pytest.mark.parametrize("M,N,Kd", SHAPES)

@@ -125,6 +125,8 @@ struct TcArgs {
     int ldo;         // row stride of out in elements
     int k_blocks_per_split;
     int atomic;      // ADD epilogue through atomics (several K slices)
+    int tiles_m;     // persistent kernel: tiles along A's rows and along B's rows
+    int tiles_n;
 };
 
 template <int BN> constexpr int stages_for() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : 4); }   // small tiles: two or three CTAs per SM
@@ -366,6 +368,142 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ---------------------------------------------------------------- prompts: persistent, plain mode
+// One CTA per SM walks over the output tiles (tile t = blockIdx.x + i * gridDim.x; consecutive tiles
+// share a panel of W, so concurrent CTAs read the same weights from L2).  The accumulator is double
+// buffered in tensor memory (2 x BN columns): while the four epilogue warps drain tile i, the MMA
+// thread already accumulates tile i + 1 into the other buffer, and the TMA ring never drains between
+// tiles.  Roles and barriers: producer -> full[s] -> MMA -> empty[s] -> producer;
+// MMA -> acc_full[b] -> epilogue -> acc_empty[b] -> MMA.
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs a) {
+    constexpr int STAGES = stages_for<BN>();
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = base;
+    uint8_t* smem_b = base + STAGES * A_BYTES;
+    uint64_t* full = (uint64_t*)(base + STAGES * (A_BYTES + B_BYTES));
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;          // [2]
+    uint64_t* acc_empty = acc_full + 2;           // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    float* epi_tiles = (float*)(base + STAGES * (A_BYTES + B_BYTES) + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_kb = (a.K + BK - 1) / BK;
+    const int total = a.tiles_m * a.tiles_n;
+    const int my_tiles = total > (int)blockIdx.x ? (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // k-block ``it`` (counted over all of this CTA's tiles) belongs to tile it / n_kb
+            const int total_kb = n_kb * my_tiles;
+            const int pre = total_kb < STAGES ? total_kb : STAGES;
+            auto rows_of = [&](int it, int& row_a, int& row_b, int& k) {
+                const int t = blockIdx.x + (it / n_kb) * gridDim.x;
+                row_a = (t % a.tiles_m) * BM; row_b = (t / a.tiles_m) * BN; k = (it % n_kb) * BK;
+            };
+            int ra, rb, k;
+            for (int it = 0; it < pre; ++it) {                // weights first: no kernel writes them
+                rows_of(it, ra, rb, k);
+                mbar_expect_tx(full + it, A_BYTES + B_BYTES);
+                tma_load_2d(smem_b + it * B_BYTES, &map_b, full + it, k, rb);
+            }
+            pdl_wait();                                       // the activations come from the kernel before
+            for (int it = 0; it < pre; ++it) {
+                rows_of(it, ra, rb, k);
+                tma_load_2d(smem_a + it * A_BYTES, &map_a, full + it, k, ra);
+            }
+            for (int it = pre; it < total_kb; ++it) {
+                const int s = it % STAGES, round = it / STAGES;
+                rows_of(it, ra, rb, k);
+                mbar_wait(empty + s, (round - 1) & 1, 1);
+                mbar_expect_tx(full + s, A_BYTES + B_BYTES);
+                tma_load_2d(smem_a + s * A_BYTES, &map_a, full + s, k, ra);
+                tma_load_2d(smem_b + s * B_BYTES, &map_b, full + s, k, rb);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            pdl_wait();
+            constexpr uint32_t idesc = instr_desc(BM, BN);
+            int it = 0;
+            for (int j = 0; j < my_tiles; ++j) {
+                const int buf = j & 1;
+                if (j >= 2) mbar_wait(acc_empty + buf, ((j >> 1) - 1) & 1, 4);     // the epilogue has drained this buffer
+                tc_fence_after();
+                const uint32_t acc = tmem + buf * BN;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % STAGES, round = it / STAGES;
+                    mbar_wait(full + s, round & 1, 2);
+                    tc_fence_after();
+                    const uint64_t da = smem_desc(smem_u32(smem_a + s * A_BYTES));
+                    const uint64_t db = smem_desc(smem_u32(smem_b + s * B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma(acc, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(empty + s);
+                }
+                tc_commit(acc_full + buf);
+            }
+        }
+    } else {
+        pdl_wait();
+        const int quarter = warp & 3;
+        float* tile = epi_tiles + quarter * EPI_TILE_FLOATS;
+        for (int j = 0; j < my_tiles; ++j) {
+            const int t = blockIdx.x + j * gridDim.x;
+            const int tile_a = t % a.tiles_m, tile_b = t / a.tiles_m;
+            const int buf = j & 1;
+            mbar_wait(acc_full + buf, (j >> 1) & 1, 3);
+            tc_fence_after();
+            const int row = tile_a * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem + buf * BN + ((uint32_t)(quarter * 32) << 16);
+            if (EPI == TB_EPI_ADD) {
+                const int row0 = tile_a * BM + quarter * 32;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    float v[32];
+                    tmem_ld32(taddr + c, v);
+                    epilogue_rows<EPI>(v, tile, a, row0, tile_b * BN + c, a.rows_b, lane);
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    float v[32];
+                    tmem_ld32(taddr + c, v);
+                    epilogue_chunk<EPI, false, 32>(v, a, row, tile_b * BN + c, lane);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tbtma::mbar_arrive(acc_empty + buf);
+        }
+    }
+    pdl_wait();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
 // ---------------------------------------------------------------- host side
 template <int BN, int EPI, bool SWAP>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t stream) {
@@ -378,6 +516,31 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim
     }
     tb_launch(gemm_tc_kernel<BN, EPI, SWAP>, grid, THREADS, smem, stream, ma, mb, a);
     return 0;
+}
+
+template <int BN, int EPI>
+int launch_persistent_epi(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t stream) {
+    static bool configured = false;
+    constexpr size_t smem = smem_for<BN, false>();
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        TB_REQUIRE(e == cudaSuccess, "gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    tb_launch(gemm_tc_persistent_kernel<BN, EPI>, grid, THREADS, smem, stream, ma, mb, a);
+    return 0;
+}
+
+template <int BN>
+int launch_persistent(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t stream) {
+    switch (epi) {
+        case TB_EPI_STORE: return launch_persistent_epi<BN, TB_EPI_STORE>(ma, mb, a, grid, stream);
+        case TB_EPI_F32: return launch_persistent_epi<BN, TB_EPI_F32>(ma, mb, a, grid, stream);
+        case TB_EPI_ADD: return launch_persistent_epi<BN, TB_EPI_ADD>(ma, mb, a, grid, stream);
+        case TB_EPI_SWIGLU: return launch_persistent_epi<BN, TB_EPI_SWIGLU>(ma, mb, a, grid, stream);
+    }
+    tb_set_error("gemm_tc: unknown epilogue %d", epi);
+    return 1;
 }
 
 template <int BN, bool SWAP>
@@ -423,15 +586,23 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
     const int kb = (K + BK - 1) / BK;
     CUtensorMap ma, mb;
     TcArgs a;
-    a.out = out; a.K = K; a.ldo = ldo; a.k_blocks_per_split = kb; a.atomic = 0;
+    a.out = out; a.K = K; a.ldo = ldo; a.k_blocks_per_split = kb; a.atomic = 0; a.tiles_m = a.tiles_n = 0;
     int rc = 0;
     if (!swap) {
         const int bn = N >= 256 ? 256 : 128;
         a.rows_a = M; a.rows_b = N;
+        a.tiles_m = (M + BM - 1) / BM; a.tiles_n = (N + bn - 1) / bn;
         if (tb_make_map_bf16(&ma, X, M, K, ldx, BM) || tb_make_map_bf16(&mb, W, N, K, K, bn)) return 1;
-        dim3 grid((N + bn - 1) / bn, (M + BM - 1) / BM, 1);
-        TB_REQUIRE(grid.y <= 65535, "gemm_tc: M=%d is too large for one launch", M);
-        rc = bn == 256 ? launch_epi<256, false>(epi, ma, mb, a, grid, stream) : launch_epi<128, false>(epi, ma, mb, a, grid, stream);
+        TB_REQUIRE((long long)a.tiles_m * a.tiles_n < (1LL << 30), "gemm_tc: too many tiles");
+        const int total = a.tiles_m * a.tiles_n;
+        static int sm_count = 0;
+        if (!sm_count) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+        }
+        dim3 grid(total < sm_count ? total : sm_count, 1, 1);
+        rc = bn == 256 ? launch_persistent<256>(epi, ma, mb, a, grid, stream) : launch_persistent<128>(epi, ma, mb, a, grid, stream);
     } else {
         const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
         a.rows_a = N; a.rows_b = M;
