@@ -251,7 +251,7 @@ struct PreArgs {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(DEC_THREADS)
+__global__ void __launch_bounds__(DEC_THREADS, 2)
 attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, PreArgs a) {
     constexpr int STAGES = 2;
     constexpr int BOXES = HD / 64;
@@ -416,6 +416,7 @@ static int launch_decode(const CUtensorMap& map, const DecArgs& d, dim3 grid, cu
     static bool configured = false;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // room for several CTAs per SM
         TB_REQUIRE(e == cudaSuccess, "attn_decode_mma: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
@@ -474,6 +475,7 @@ static int launch_prefill(const CUtensorMap& map, const PreArgs& p, dim3 grid, c
     static bool configured = false;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // room for several CTAs per SM
         TB_REQUIRE(e == cudaSuccess, "attn_prefill_mma: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }

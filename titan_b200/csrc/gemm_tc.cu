@@ -232,22 +232,22 @@ __device__ __forceinline__ void epilogue_rows(const float* val, float* tile, con
     __syncwarp();
     const int col = col0 + lane;
     if (col >= n_cols) return;
+    float* o = (float*)a.out + (size_t)row0 * a.ldo + col;
+    if (EPI == TB_EPI_ADD) {
+        // all 32 rows of the residual are requested before the first is needed: one round trip, not four
+        float old[32];
 #pragma unroll
-    for (int r0 = 0; r0 < 32; r0 += 8) {
-        float old[8];
-        if (EPI == TB_EPI_ADD) {
+        for (int r = 0; r < 32; ++r) old[r] = (row0 + r < a.rows_a) ? o[(size_t)r * a.ldo] : 0.f;
 #pragma unroll
-            for (int r = 0; r < 8; ++r)
-                old[r] = (row0 + r0 + r < a.rows_a) ? ((const float*)a.out)[(size_t)(row0 + r0 + r) * a.ldo + col] : 0.f;
-        }
+        for (int r = 0; r < 32; ++r)
+            if (row0 + r < a.rows_a) o[(size_t)r * a.ldo] = old[r] + tile[r * 33 + lane];
+    } else {
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const int m = row0 + r0 + r;
-            if (m >= a.rows_a) continue;
-            const float v = tile[(r0 + r) * 33 + lane];
-            if (EPI == TB_EPI_STORE || EPI == TB_EPI_SWIGLU) ((__nv_bfloat16*)a.out)[(size_t)m * a.ldo + col] = __float2bfloat16_rn(v);
-            else if (EPI == TB_EPI_F32) ((float*)a.out)[(size_t)m * a.ldo + col] = v;
-            else ((float*)a.out)[(size_t)m * a.ldo + col] = old[r] + v;
+        for (int r = 0; r < 32; ++r) {
+            if (row0 + r >= a.rows_a) continue;
+            const float v = tile[r * 33 + lane];
+            if (EPI == TB_EPI_F32) o[(size_t)r * a.ldo] = v;
+            else ((__nv_bfloat16*)a.out)[(size_t)(row0 + r) * a.ldo + col] = __float2bfloat16_rn(v);
         }
     }
 }
@@ -511,6 +511,7 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim
     constexpr size_t smem = smem_for<BN, SWAP>();
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, SWAP>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // room for several CTAs per SM
         TB_REQUIRE(e == cudaSuccess, "gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
@@ -524,6 +525,7 @@ int launch_persistent_epi(const CUtensorMap& ma, const CUtensorMap& mb, const Tc
     constexpr size_t smem = smem_for<BN, false>();
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, EPI>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // room for several CTAs per SM
         TB_REQUIRE(e == cudaSuccess, "gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
