@@ -1,0 +1,73 @@
+"""Sizes beyond the tiny models: a mid-size model against the plain implementation (several tiles of the
+tensor-core kernels per matrix, head_dim 128, prompts over several pages), and one layer of the
+benchmark's sizes in bfloat16 against the same engine in true float32."""
+import pytest
+import torch
+
+from helpers import TOL, random_tokens, random_weights, rel_l2
+from plain import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+
+MID = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=1024,
+           num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=2816, vocab_size=5000,
+           rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
+BIG = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=1, hidden_size=4096,
+           num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936,
+           rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mid_size_model_against_the_plain_implementation(dtype):
+    from titan_b200 import Engine, StepEntry
+    from titan_b200.config import config_from_dict
+    w = random_weights(MID, 11, torch.bfloat16, std=0.03)
+    w32 = {k: v.float() for k, v in w.items()}
+    e = Engine.from_tensors(config_from_dict(MID), w, dtype=dtype, max_tokens=2048)
+    reqs = [random_tokens(n, MID["vocab_size"], 50 + n) for n in (300, 130, 70)]
+    want = [P.forward_logits(MID, w32, r) for r in reqs]
+    slots = [e.alloc_slot() for _ in reqs]
+    cut = [260, 100, 69]
+    out = e.step([StepEntry(s, r[:c], list(range(c))) for s, r, c in zip(slots, reqs, cut)])
+    got, at = [], 0
+    for c in cut:
+        got.append([out[at:at + c]])
+        at += c
+    fed = list(cut)
+    while any(f < len(r) for f, r in zip(fed, reqs)):
+        live = [i for i in range(3) if fed[i] < len(reqs[i])]
+        out = e.step([StepEntry(slots[i], [reqs[i][fed[i]]], [0]) for i in live])
+        for k, i in enumerate(live):
+            got[i].append(out[k:k + 1])
+            fed[i] += 1
+    for i in range(3):
+        assert rel_l2(torch.cat(got[i]).float().cpu(), want[i]) < TOL[dtype], i
+        e.free_slot(slots[i])
+
+
+def test_benchmark_layer_sizes_bfloat16_against_float32():
+    from titan_b200 import Engine, SamplerParams, StepEntry, kernels as K
+    from titan_b200.config import config_from_dict
+    cfg = config_from_dict(BIG)
+    logits = {}
+    tokens = {}
+    prompts = [random_tokens(n, 151936, n) for n in (333, 64, 129)]
+    for dtype in ("float32", "bfloat16"):
+        e = Engine.from_random(cfg, seed=3, dtype=dtype, max_tokens=4096, max_context=1024)
+        slots = [e.alloc_slot() for _ in prompts]
+        first = e.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        rows = [first]
+        feed = [7, 8, 9]
+        for _ in range(3):
+            rows.append(e.step([StepEntry(s, [t], [0]) for s, t in zip(slots, feed)]))
+        for s in slots:
+            e.free_slot(s)
+        logits[dtype] = torch.cat(rows).float().cpu()
+        out = e.generate(prompts, max_tokens=24, params=SamplerParams.greedy(), stop_tokens=[])     # graphs after the first step
+        tokens[dtype] = [r.tokens for r in out]
+        assert K.gemm_tc_error() == 0 and K.attn_mma_error() == 0
+        del e
+        torch.cuda.empty_cache()
+    assert rel_l2(logits["bfloat16"], logits["float32"]) < TOL["bfloat16"]
+    # greedy tokens agree until rounding decides a near-tie: the first token of each sequence at least
+    assert [t[0] for t in tokens["bfloat16"]] == [t[0] for t in tokens["float32"]]

@@ -38,7 +38,21 @@ extern "C" int tb_embed(const void* table, int dtype, const int* tokens, float* 
 
 // ------------------------------------------------------------------ RMSNorm
 // y[r] = x[rows ? rows[r] : r] * 1/sqrt(mean(x^2) + eps) * w      (x float32, y in the compute dtype)
-template <typename T>
+template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&lo);
+    u.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+// VEC: H is a multiple of 4 and a row fits the block's registers (H <= 16 * blockDim): the row is read
+// once, as float4, and kept in registers between the sum of squares and the scaling.
+template <typename T, bool VEC>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
                                const int* __restrict__ rows, int H, float eps) {
     pdl_launch_dependents();
@@ -46,27 +60,53 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     __shared__ float red[33];
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = xr[i];
-        ss += v * v;
-    }
-    ss = block_sum(ss, red);
-    const float scale = 1.0f / sqrtf(ss / (float)H + eps);
     T* yr = y + (size_t)r * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) stf(yr + i, xr[i] * scale * w[i]);
+    if (VEC) {
+        float4 v[4];
+        const int n4 = H >> 2;
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            v[j] = i < n4 ? reinterpret_cast<const float4*>(xr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+        }
+        ss = block_sum(ss, red);
+        const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < n4) {
+                const float4 ww = reinterpret_cast<const float4*>(w)[i];
+                store4<T>(yr + 4 * i, v[j].x * scale * ww.x, v[j].y * scale * ww.y, v[j].z * scale * ww.z, v[j].w * scale * ww.w);
+            }
+        }
+    } else {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = xr[i];
+            ss += v * v;
+        }
+        ss = block_sum(ss, red);
+        const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+        for (int i = threadIdx.x; i < H; i += blockDim.x) stf(yr + i, xr[i] * scale * w[i]);
+    }
+}
+
+template <typename T>
+static void launch_rmsnorm(const float* x, const float* w, T* y, const int* rows, int n_rows, int H, float eps, cudaStream_t stream) {
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 64 : 32));
+    const bool vec = (H % 4 == 0) && H <= 16 * threads && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)y % 16 == 0);
+    if (vec) tb_launch(rmsnorm_kernel<T, true>, n_rows, threads, 0, stream, x, w, y, rows, H, eps);
+    else tb_launch(rmsnorm_kernel<T, false>, n_rows, threads, 0, stream, x, w, y, rows, H, eps);
 }
 
 extern "C" int tb_rmsnorm(const float* x, const float* w, void* y, int dtype, const int* rows, int n_rows,
                           int H, float eps, cudaStream_t stream) {
     TB_REQUIRE(n_rows > 0 && H > 0, "rmsnorm: sizes must be positive (rows=%d H=%d)", n_rows, H);
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 64);
-    if (dtype == TB_F32)
-        tb_launch(rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, w, (float*)y, rows, H, eps);
-    else if (dtype == TB_BF16)
-        tb_launch(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, w, (__nv_bfloat16*)y, rows, H, eps);
-    else
-        TB_REQUIRE(false, "rmsnorm: unknown dtype %d", dtype);
+    if (dtype == TB_F32) launch_rmsnorm<float>(x, w, (float*)y, rows, n_rows, H, eps, stream);
+    else if (dtype == TB_BF16) launch_rmsnorm<__nv_bfloat16>(x, w, (__nv_bfloat16*)y, rows, n_rows, H, eps, stream);
+    else TB_REQUIRE(false, "rmsnorm: unknown dtype %d", dtype);
     TB_CHECK_LAUNCH("rmsnorm");
     return 0;
 }
@@ -96,10 +136,18 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float head_smem[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int t = blockIdx.x;
-    const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+    const int head = blockIdx.y * nwarp + warp;
     const int n_heads = a.nh + a.nkv + (a.append ? a.nkv : 0);
+    // cosine and sine of this token's angles, once per block: [rot/2] each, behind the warps' rows
+    float* cs = head_smem + nwarp * a.hd;
+    float* sn = cs + (a.rot >> 1);
+    if (a.inv_freq) {
+        const float p = (float)a.pos_of[t];
+        for (int k = threadIdx.x; k < (a.rot >> 1); k += blockDim.x) sincosf(p * a.inv_freq[k], &sn[k], &cs[k]);
+    }
+    __syncthreads();
     if (head >= n_heads) return;
     float* y = head_smem + warp * a.hd;
     const int hd = a.hd;
@@ -152,8 +200,7 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
         if (a.inv_freq && e < a.rot) {
             const bool first = e < half;
             const int k = first ? e : e - half;
-            float s, c;
-            sincosf((float)pos * a.inv_freq[k], &s, &c);
+            const float s = sn[k], c = cs[k];
             r = first ? y[e] * c - y[e + half] * s : y[e - half] * s + y[e] * c;
         }
         if (out) stf(out + e, r);
@@ -173,7 +220,7 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     const int warps = 4;
     const int n_heads = a.nh + a.nkv + (a.append ? a.nkv : 0);
     dim3 grid(a.T, (n_heads + warps - 1) / warps);
-    const size_t smem = (size_t)warps * a.hd * sizeof(float);
+    const size_t smem = ((size_t)warps * a.hd + a.rot) * sizeof(float);
     if (in_dtype == TB_F32 && out_dtype == TB_F32)
         tb_launch(qk_norm_rope_kernel<float, float>, grid, warps * 32, smem, stream, a);
     else if (in_dtype == TB_BF16 && out_dtype == TB_BF16)
@@ -200,7 +247,13 @@ __global__ void kv_append_kernel(const T* __restrict__ kv, int stride, TbKvView 
     const int is_v = h2 >= c.kv_heads, head = is_v ? h2 - c.kv_heads : h2;
     const T* src = kv + (size_t)t * stride + (size_t)h2 * c.head_dim;
     T* dst = (T*)c.storage + (is_v ? kv_half_elems(c) : 0) + kv_row_offset(c, slot_of_seq[seq], pos, head);
-    for (int e = threadIdx.x; e < c.head_dim; e += blockDim.x) dst[e] = src[e];
+    constexpr int PER = 16 / sizeof(T);            // elements per 16-byte chunk
+    if (c.head_dim % PER == 0 && ((uintptr_t)src % 16 == 0) && ((uintptr_t)dst % 16 == 0)) {
+        for (int e = threadIdx.x; e < c.head_dim / PER; e += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[e] = reinterpret_cast<const uint4*>(src)[e];
+    } else {
+        for (int e = threadIdx.x; e < c.head_dim; e += blockDim.x) dst[e] = src[e];
+    }
 }
 
 extern "C" int tb_kv_append(const void* kv, int stride, int dtype, const TbKvView* cache, const TbBatch* b,
@@ -208,7 +261,7 @@ extern "C" int tb_kv_append(const void* kv, int stride, int dtype, const TbKvVie
     TbKvView c = *cache;
     TB_REQUIRE(b->T > 0 && c.storage, "kv_append: nothing to append or no cache");
     dim3 grid(b->T, 2 * c.kv_heads);
-    const int threads = c.head_dim >= 64 ? 64 : 32;
+    const int threads = 32;
     if (dtype == TB_F32)
         tb_launch(kv_append_kernel<float>, grid, threads, 0, stream, (const float*)kv, stride, c, b->pos_of, b->seq_of, b->slot_of_seq, b->kv_len);
     else if (dtype == TB_BF16)
