@@ -124,6 +124,7 @@ def time_decode(engine, torch, K, batch, kv_start, steps, warmup, e2e: bool):
         torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches0 = K.launch_count + engine.graph_launches
+        h2d0, d2h0 = engine.h2d_bytes, engine.d2h_bytes
         t0 = time.perf_counter()
         start.record()
         for _ in range(steps):
@@ -132,7 +133,8 @@ def time_decode(engine, torch, K, batch, kv_start, steps, warmup, e2e: bool):
         torch.cuda.synchronize()
         wall_ms = (time.perf_counter() - t0) * 1e3 / steps
         dev_ms = start.elapsed_time(stop) / steps
-        return dev_ms, wall_ms, K.launch_count + engine.graph_launches - launches0
+        return (dev_ms, wall_ms, K.launch_count + engine.graph_launches - launches0,
+                (engine.h2d_bytes - h2d0) // steps, (engine.d2h_bytes - d2h0) // steps)
     finally:
         for s in slots:
             engine.free_slot(s)
@@ -171,7 +173,7 @@ def run_ours(args):
     kv_start = context - (args.steps + args.warmup) - 1
     clocks = ClockSampler()
     clocks.start()
-    dev_ms, wall_ms, launches = time_decode(engine, torch, K, B, kv_start, args.steps, args.warmup, True)
+    dev_ms, wall_ms, launches, h2d, d2h = time_decode(engine, torch, K, B, kv_start, args.steps, args.warmup, True)
     clock_rec = clocks.stop()
     value = B * 1e3 / dev_ms
     e2e = B * 1e3 / wall_ms
@@ -181,7 +183,7 @@ def run_ours(args):
     points = {}
     if not args.skip_points:
         for b in (1, 64):
-            ms, _, _ = time_decode(engine, torch, K, b, kv_start, max(4, args.steps // 2), args.warmup, False)
+            ms = time_decode(engine, torch, K, b, kv_start, max(4, args.steps // 2), args.warmup, False)[0]
             points[f"decode_b{b}"] = round(b * 1e3 / ms, 1)
     T = args.prefill_tokens
     pre_ms = time_prefill(engine, torch, T, 1, 3)
@@ -197,8 +199,7 @@ def run_ours(args):
                    "seq_len": context, "kv_len_at_first_timed_step": kv_start + args.warmup, "prefill_tokens": T,
                    "parallelism": "single_gpu", "l2": "inputs_larger_than_l2", "cache_fill": "random",
                    "peaks": pk["source"]},
-        "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": engine.h2d_bytes // max(1, engine_steps(engine)),
-                "d2h_bytes_per_step": 4 * B},
+        "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "prefill": {"value": round(T * 1e3 / pre_ms, 1), "tokens": T, "ms": round(pre_ms, 3),
                     "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
@@ -210,8 +211,32 @@ def run_ours(args):
     return 0
 
 
-def engine_steps(engine):
-    return getattr(engine, "steps_run", 0) or 1
+def profile_case():
+    """The small case that the ncu summaries under profiles/ were captured on: ONE layer of the
+    benchmark's sizes; two 2,048-token prompts, then decode steps at batch 8 with 8,100 cached tokens
+    per sequence, CUDA graphs off so that every kernel is a launch of its own.  About 4 GB on the device."""
+    import torch
+
+    from titan_b200 import Engine, SamplerParams, StepEntry
+    from titan_b200.config import config_from_dict
+    cfg = dict(QWEN3_8B)
+    cfg["num_hidden_layers"] = 1
+    batch = 8
+    engine = Engine.from_random(config_from_dict(cfg), 2, "bfloat16", max_tokens=batch * 8192 + 4096, max_context=8192,
+                                max_slots=batch + 1, decode_graphs=False)
+    for _ in range(2):
+        s = engine.alloc_slot()
+        engine.step([StepEntry(s, [(13 * i + 5) % 151936 for i in range(2048)], [2047])])
+        engine.free_slot(s)
+    slots = [engine.alloc_slot() for _ in range(batch)]
+    fill_cache_random(engine, slots, 8100)
+    engine.sampler.configure(slots, [SamplerParams.greedy()] * batch, list(range(batch)))
+    tokens = [1] * batch
+    for _ in range(2):
+        tokens = engine.advance(slots, tokens)
+    torch.cuda.synchronize()
+    print("profile case done", tokens)
+    return 0
 
 
 def main():
@@ -225,7 +250,10 @@ def main():
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--profile-case", action="store_true", help="run the small one-layer case used for ncu captures and exit")
     args = ap.parse_args()
+    if args.profile_case:
+        return profile_case()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "berniehans/titan is a Rust workspace (cargo is not installed) "
                           "that needs GGUF Q4_K weights and NVRTC for compute_86; it cannot be installed or run offline here"}))

@@ -127,6 +127,7 @@ struct QkArgs {
     const int* pos_of; const int* seq_of; const int* slot_of_seq;
     TbKvView cache; int append; int T;
     int zero_in;                            // after reading a head, write zeros over it (an accumulation buffer is left clean)
+    const int* kv_len;                      // [B] lengths after the step: in a ring, a row that a later token of the step reuses is not written
 };
 
 #define QK_MAXE 8   // head_dim <= 32 * QK_MAXE
@@ -165,8 +166,11 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
         if (a.zero_in && e < hd) const_cast<TIn*>(x)[e] = TIn(0.f);
     }
     const int pos = a.pos_of[t];
-    const int slot = a.slot_of_seq[a.seq_of[t]];
+    const int seq = a.seq_of[t];
+    const int slot = a.slot_of_seq[seq];
+    const bool to_cache = a.append && !(a.cache.ring_rows && a.kv_len && pos < a.kv_len[seq] - a.cache.ring_rows);
     if (!is_q && !is_k) {   // V: straight copy into the cache
+        if (!to_cache) return;
         TOut* dst = (TOut*)a.cache.storage + kv_half_elems(a.cache) + kv_row_offset(a.cache, slot, pos, head - a.nh - a.nkv);
 #pragma unroll
         for (int j = 0; j < QK_MAXE; ++j) {
@@ -190,7 +194,7 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
     const int half = a.rot >> 1;
     TOut* out = is_q ? (TOut*)a.q_out + (size_t)t * a.q_stride + head * hd
                      : (a.k_out ? (TOut*)a.k_out + (size_t)t * a.k_stride + (head - a.nh) * hd : nullptr);
-    TOut* cdst = (is_k && a.append)
+    TOut* cdst = (is_k && to_cache)
                      ? (TOut*)a.cache.storage + kv_row_offset(a.cache, slot, pos, head - a.nh) : nullptr;
 #pragma unroll
     for (int j = 0; j < QK_MAXE; ++j) {
@@ -208,6 +212,132 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
     }
 }
 
+// Fast path for head sizes 64, 128 and 256 with the rotation over the whole head (or none): a lane
+// holds VE = head_dim / 32 consecutive elements (one 4- to 32-byte load), and an element's rotation
+// partner (head_dim / 2 away) is the same register of the lane 16 further, so no shared memory is
+// needed for the head.  Arguments and results are those of qk_norm_rope_kernel.
+template <typename T, int VE> __device__ __forceinline__ void load_vec(const T* p, float* o) {
+    constexpr int BYTES = VE * (int)sizeof(T);
+    T tmp[VE];
+    if constexpr (BYTES == 32) {
+        const uint4 a = reinterpret_cast<const uint4*>(p)[0], b = reinterpret_cast<const uint4*>(p)[1];
+        memcpy(tmp, &a, 16);
+        memcpy(reinterpret_cast<char*>(tmp) + 16, &b, 16);
+    } else if constexpr (BYTES == 16) {
+        const uint4 a = *reinterpret_cast<const uint4*>(p);
+        memcpy(tmp, &a, 16);
+    } else if constexpr (BYTES == 8) {
+        const uint2 a = *reinterpret_cast<const uint2*>(p);
+        memcpy(tmp, &a, 8);
+    } else {
+        const uint32_t a = *reinterpret_cast<const uint32_t*>(p);
+        memcpy(tmp, &a, 4);
+    }
+#pragma unroll
+    for (int i = 0; i < VE; ++i) o[i] = ldf(tmp + i);
+}
+template <typename T, int VE> __device__ __forceinline__ void store_vec(T* p, const float* v) {
+    constexpr int BYTES = VE * (int)sizeof(T);
+    T tmp[VE];
+#pragma unroll
+    for (int i = 0; i < VE; ++i) stf(tmp + i, v[i]);
+    if constexpr (BYTES == 32) {
+        uint4 a, b;
+        memcpy(&a, tmp, 16);
+        memcpy(&b, reinterpret_cast<char*>(tmp) + 16, 16);
+        reinterpret_cast<uint4*>(p)[0] = a;
+        reinterpret_cast<uint4*>(p)[1] = b;
+    } else if constexpr (BYTES == 16) {
+        uint4 a;
+        memcpy(&a, tmp, 16);
+        *reinterpret_cast<uint4*>(p) = a;
+    } else if constexpr (BYTES == 8) {
+        uint2 a;
+        memcpy(&a, tmp, 8);
+        *reinterpret_cast<uint2*>(p) = a;
+    } else {
+        uint32_t a;
+        memcpy(&a, tmp, 4);
+        *reinterpret_cast<uint32_t*>(p) = a;
+    }
+}
+
+template <typename TIn, typename TOut, int VE>
+__global__ void qk_norm_rope_vec_kernel(QkArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float head_smem[];
+    constexpr int HD = 32 * VE, HALF = HD / 2;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int t = blockIdx.x;
+    const int head = blockIdx.y * nwarp + warp;
+    const int n_heads = a.nh + a.nkv + (a.append ? a.nkv : 0);
+    float* cs = head_smem;
+    float* sn = cs + HALF;
+    if (a.inv_freq) {
+        const float p = (float)a.pos_of[t];
+        for (int k = threadIdx.x; k < HALF; k += blockDim.x) sincosf(p * a.inv_freq[k], &sn[k], &cs[k]);
+    }
+    __syncthreads();
+    if (head >= n_heads) return;
+    const bool is_q = head < a.nh, is_k = !is_q && head < a.nh + a.nkv;
+    const int col = head * HD;                       // Q heads, then K heads, then V heads, all HD wide
+    const TIn* x = (const TIn*)a.in + (size_t)t * a.in_stride + col + lane * VE;
+    float v[VE];
+    load_vec<TIn, VE>(x, v);
+    if (a.zero_in) {
+        float z[VE];
+#pragma unroll
+        for (int i = 0; i < VE; ++i) z[i] = 0.f;
+        store_vec<TIn, VE>(const_cast<TIn*>(x), z);
+    }
+    const int pos = a.pos_of[t];
+    const int seq = a.seq_of[t];
+    const int slot = a.slot_of_seq[seq];
+    const bool to_cache = a.append && !(a.cache.ring_rows && a.kv_len && pos < a.kv_len[seq] - a.cache.ring_rows);
+    if (!is_q && !is_k) {
+        if (to_cache)
+            store_vec<TOut, VE>((TOut*)a.cache.storage + kv_half_elems(a.cache) +
+                                kv_row_offset(a.cache, slot, pos, head - a.nh - a.nkv) + lane * VE, v);
+        return;
+    }
+    const float* w = is_q ? a.q_w : a.k_w;
+    if (w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VE; ++i) ss += v[i] * v[i];
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)HD + a.eps);
+#pragma unroll
+        for (int i = 0; i < VE; ++i) v[i] = v[i] * scale * w[lane * VE + i];
+    }
+    if (a.inv_freq) {
+        const bool first = lane < 16;
+#pragma unroll
+        for (int i = 0; i < VE; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
+            const int k = (lane & 15) * VE + i;
+            const float c = cs[k], s = sn[k];
+            v[i] = first ? v[i] * c - other * s : other * s + v[i] * c;
+        }
+    }
+    if (is_q) {
+        store_vec<TOut, VE>((TOut*)a.q_out + (size_t)t * a.q_stride + head * HD + lane * VE, v);
+    } else {
+        if (a.k_out) store_vec<TOut, VE>((TOut*)a.k_out + (size_t)t * a.k_stride + (head - a.nh) * HD + lane * VE, v);
+        if (to_cache)
+            store_vec<TOut, VE>((TOut*)a.cache.storage + kv_row_offset(a.cache, slot, pos, head - a.nh) + lane * VE, v);
+    }
+}
+
+template <typename TIn, typename TOut>
+static void launch_qk_vec(const QkArgs& a, dim3 grid, int threads, cudaStream_t stream) {
+    const size_t smem = (size_t)a.hd * sizeof(float);
+    if (a.hd == 64) tb_launch(qk_norm_rope_vec_kernel<TIn, TOut, 2>, grid, threads, smem, stream, a);
+    else if (a.hd == 128) tb_launch(qk_norm_rope_vec_kernel<TIn, TOut, 4>, grid, threads, smem, stream, a);
+    else tb_launch(qk_norm_rope_vec_kernel<TIn, TOut, 8>, grid, threads, smem, stream, a);
+}
+
 extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, cudaStream_t stream) {
     QkArgs a = *args;
     TB_REQUIRE(a.T > 0 && a.nh > 0 && a.nkv >= 0, "qk_norm_rope: sizes must be positive");
@@ -221,14 +351,26 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     const int n_heads = a.nh + a.nkv + (a.append ? a.nkv : 0);
     dim3 grid(a.T, (n_heads + warps - 1) / warps);
     const size_t smem = ((size_t)warps * a.hd + a.rot) * sizeof(float);
-    if (in_dtype == TB_F32 && out_dtype == TB_F32)
-        tb_launch(qk_norm_rope_kernel<float, float>, grid, warps * 32, smem, stream, a);
-    else if (in_dtype == TB_BF16 && out_dtype == TB_BF16)
-        tb_launch(qk_norm_rope_kernel<__nv_bfloat16, __nv_bfloat16>, grid, warps * 32, smem, stream, a);
-    else if (in_dtype == TB_F32 && out_dtype == TB_BF16)
-        tb_launch(qk_norm_rope_kernel<float, __nv_bfloat16>, grid, warps * 32, smem, stream, a);
-    else
+    const int in_bytes = in_dtype == TB_F32 ? 4 : 2, out_bytes = out_dtype == TB_F32 ? 4 : 2;
+    const int ve = a.hd / 32;
+    auto aligned = [&](const void* p, long long stride_elems, int esz) {
+        return p == nullptr || (((uintptr_t)p % (size_t)(ve * esz)) == 0 && (stride_elems * esz) % (ve * esz) == 0);
+    };
+    const bool vec = (a.hd == 64 || a.hd == 128 || a.hd == 256) && (a.rot == a.hd || !a.inv_freq) &&
+                     aligned(a.in, a.in_stride, in_bytes) && aligned(a.q_out, a.q_stride, out_bytes) &&
+                     aligned(a.k_out, a.k_stride, out_bytes) && aligned(a.cache.storage, a.hd, out_bytes);
+    if (in_dtype == TB_F32 && out_dtype == TB_F32) {
+        if (vec) launch_qk_vec<float, float>(a, grid, warps * 32, stream);
+        else tb_launch(qk_norm_rope_kernel<float, float>, grid, warps * 32, smem, stream, a);
+    } else if (in_dtype == TB_BF16 && out_dtype == TB_BF16) {
+        if (vec) launch_qk_vec<__nv_bfloat16, __nv_bfloat16>(a, grid, warps * 32, stream);
+        else tb_launch(qk_norm_rope_kernel<__nv_bfloat16, __nv_bfloat16>, grid, warps * 32, smem, stream, a);
+    } else if (in_dtype == TB_F32 && out_dtype == TB_BF16) {
+        if (vec) launch_qk_vec<float, __nv_bfloat16>(a, grid, warps * 32, stream);
+        else tb_launch(qk_norm_rope_kernel<float, __nv_bfloat16>, grid, warps * 32, smem, stream, a);
+    } else {
         TB_REQUIRE(false, "qk_norm_rope: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+    }
     TB_CHECK_LAUNCH("qk_norm_rope");
     return 0;
 }

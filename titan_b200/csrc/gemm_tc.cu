@@ -1,19 +1,25 @@
 // bfloat16 matrix product on the 5th-generation tensor cores (tcgen05) of sm_100a:
 //     out = epilogue(X[M,K] . W[N,K]^T),  float32 accumulation in tensor memory.
 //
-// One CTA computes one 128 x BN tile of D = A . B^T, where A and B are both K-major:
+// Tiles of D = A . B^T are 128 x BN, A and B both K-major:
 //   plain mode  A = X (rows = tokens), B = W (rows = outputs):  D[m][n]     (prompts, M >= 128)
 //   swap mode   A = W,                 B = X:                   D[n][m]     (decode: a few tokens)
-// so that in decode the 128-row side of the instruction is filled by weight rows and the batch
-// is the narrow side (BN = 16..128).  Swap mode can also cut K into slices (grid.z), each CTA
-// adding its partial sum into a float32 output with atomics, to put enough CTAs on the machine
-// when N / 128 is small.
+// so that in decode the 128-row side of the instruction is filled by weight rows and the batch is the
+// narrow side (BN = 16..128).
+//
+// Plain mode is a persistent kernel (gemm_tc_persistent_kernel): one CTA per SM walks over the tiles,
+// the accumulator is double buffered in tensor memory, and the epilogue of a tile overlaps the MMAs
+// of the next.  Swap mode (gemm_tc_kernel) is one tile per CTA with two or three CTAs per SM; it can
+// cut K into slices (grid.z), each CTA adding its partial sum into a float32 output with atomics, to
+// put enough CTAs on the machine when N / 128 is small.
 //
 // Data path: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill outside the tensor) into a
 // ring of shared-memory stages -> tcgen05.mma.cta_group::1.kind::f16 issued by one thread, four
 // K=16 steps per 64-wide stage -> accumulator in TMEM -> tcgen05.ld by four epilogue warps.
 // Warp 0 produces, warp 1 allocates TMEM and issues MMAs, warps 2..5 run the epilogue.
-// No cluster launch, no multicast.
+// No cluster launch, no multicast.  Kernels are launched with programmatic dependent launch: the
+// producer requests the first ring of WEIGHT tiles before it waits for the kernel before (no kernel
+// writes weights), so a decode step's weight stream does not stop between kernels.
 //
 // Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the thread records an error code
 // in a device word (read with tb_gemm_tc_error) and goes on, so the kernel always ends and frees
@@ -266,7 +272,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* empty = full + STAGES;
     uint64_t* accum = empty + STAGES;
     uint32_t* tmem_slot = (uint32_t*)(accum + 1);
-    float* epi_tiles = (float*)(base + STAGES * (A_BYTES + B_BYTES) + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_a = blockIdx.y;                          // tile index along A's rows
@@ -336,16 +341,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int quarter = warp & 3;                     // a warp reads TMEM lanes 32 * (warp % 4) ..
             const int row = tile_a * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16);
-            if (!SWAP && EPI == TB_EPI_ADD) {       // read-modify-write of the residual: whole rows per warp
-                float* tile = epi_tiles + quarter * EPI_TILE_FLOATS;
-                const int row0 = tile_a * BM + quarter * 32;
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
-                    float v[32];
-                    tmem_ld32(taddr + c, v);
-                    epilogue_rows<EPI>(v, tile, a, row0, tile_b * BN + c, a.rows_b, lane);
-                }
-            } else if (BN >= 32) {
+            if (BN >= 32) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 32) {
                     float v[32];

@@ -175,9 +175,18 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(SampleArgs a) {
 
     // ---- maximum and its lowest index (this is the answer when greedy)
     float best = -INFINITY; int best_i = INT_MAX;
-    for (int i = tid; i < V; i += blockDim.x) {
-        const float x = r.value(i);
-        if (best_i == INT_MAX || x > best) { best = x; best_i = i; }
+    for (int i0 = tid; i0 < V; i0 += 8 * blockDim.x) {     // eight loads in flight per thread
+        float xs[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * blockDim.x;
+            xs[u] = i < V ? r.value(i) : -INFINITY;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * blockDim.x;
+            if (i < V && (best_i == INT_MAX || xs[u] > best)) { best = xs[u]; best_i = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

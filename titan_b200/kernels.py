@@ -41,7 +41,7 @@ class QkArgs(Structure):
                 ("k_out", c_void_p), ("k_stride", c_int), ("q_w", c_void_p), ("k_w", c_void_p),
                 ("inv_freq", c_void_p), ("eps", c_float), ("rot", c_int), ("nh", c_int), ("nkv", c_int),
                 ("hd", c_int), ("pos_of", c_void_p), ("seq_of", c_void_p), ("slot_of_seq", c_void_p),
-                ("cache", KvView), ("append", c_int), ("T", c_int), ("zero_in", c_int)]
+                ("cache", KvView), ("append", c_int), ("T", c_int), ("zero_in", c_int), ("kv_len", c_void_p)]
 
 
 class AttnArgs(Structure):

@@ -140,8 +140,13 @@ class AttentionMixer(Mixer):
         qa.eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
         qa.rot, qa.nh, qa.nkv, qa.hd = self.position.rotary_dim, s.num_heads, (0 if self.shared else s.num_kv_heads), hd
         qa.pos_of, qa.seq_of, qa.slot_of_seq = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr()
-        qa.cache, qa.append, qa.T = view, int(decode and not self.shared), T
+        # K and V go into the cache in this kernel when nothing of this step still has to read the rows
+        # they replace: always for single tokens and for caches that keep everything; in a ring only if
+        # every sequence starts at position 0 (attention then reads the step's own rows alone).
+        append_now = not self.shared and (decode or view.ring_rows == 0 or lay.all_fresh)
+        qa.cache, qa.append, qa.T = view, int(append_now), T
         qa.zero_in = int(wide_sum)
+        qa.kv_len = lay.kv_len.data_ptr()
         K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
 
         attn = ctx.empty((T, Q))
@@ -174,7 +179,7 @@ class AttentionMixer(Mixer):
                 K.attn_prefill_mma(aa, lay.all_fresh, ctx.stream)
             else:
                 K.attn_prefill(aa, q_buf.dtype, ctx.stream)
-            if not self.shared:
+            if not self.shared and not append_now:
                 K.kv_append(qkv[:, Q:], view, lay.c_struct(), ctx.stream)
         linear.matmul(attn, self.w_o, out, linear.EPI_ADD, ctx)
 
