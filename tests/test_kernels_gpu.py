@@ -405,11 +405,11 @@ def test_attention_decode_on_tensor_cores(K, nh, nkv, hd, window, ring):
     assert not K.attn_decode_mma_accepts(d, torch.bfloat16)
 
 
-@pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, 0), (6, 6, 64, 0), (4, 1, 128, 100), (3, 1, 64, 64)])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, 0), (6, 6, 64, 0), (4, 1, 128, 100), (3, 1, 64, 64), (2, 1, 128, 300)])
 def test_attention_prefill_on_tensor_cores(K, nh, nkv, hd, window):
     """Fresh prompts of ragged lengths (1 token, ends inside a tile, several tiles) in one step."""
     g = torch.Generator().manual_seed(nh * hd + window)
-    lens = [1, 200, 64, 333, 65]
+    lens = [1, 200, 64, 333, 65, 128, 700]
     slots = list(range(len(lens)))
     lay = layout_for(slots, [0] * len(lens), lens)
     T, Q, KV = sum(lens), nh * hd, nkv * hd
@@ -421,22 +421,26 @@ def test_attention_prefill_on_tensor_cores(K, nh, nkv, hd, window):
         qkv[at + far, Q:Q + KV] = (qkv[at + far, Q:Q + KV].float() * 4).to(torch.bfloat16)
         at += n
     buf = qkv.cuda()
-    outs = []
-    for fast in (True, False):
+    outs = {}
+    for which in (["tc"] if hd == 128 else []) + ["mma", "plain"]:
         out = torch.full((T, Q), float("nan"), dtype=torch.bfloat16, device="cuda")
         a = K.AttnArgs()
         a.q, a.q_stride, a.out, a.out_stride = buf.data_ptr(), Q + 2 * KV, out.data_ptr(), Q
         a.kv_new, a.kv_stride = buf.data_ptr() + Q * 2, Q + 2 * KV
         a.batch = lay.c_struct()
         a.nh, a.nkv, a.hd, a.window, a.scale = nh, nkv, hd, window, scale
-        if fast:
+        if which == "tc":
+            assert K.attn_prefill_tc_accepts(a, torch.bfloat16, True) and not K.attn_prefill_tc_accepts(a, torch.bfloat16, False)
+            K.attn_prefill_tc(a, True, stream())
+            assert K.attn_tc_error() == 0
+        elif which == "mma":
             assert K.attn_prefill_mma_accepts(a, torch.bfloat16, True)
             assert not K.attn_prefill_mma_accepts(a, torch.bfloat16, False)
             K.attn_prefill_mma(a, True, stream())
             assert K.attn_mma_error() == 0
         else:
             K.attn_prefill(a, torch.bfloat16, stream())
-        outs.append(out.float().cpu())
+        outs[which] = out.float().cpu()
     want = torch.zeros(T, nh, hd)
     at = 0
     for n in lens:
@@ -445,6 +449,6 @@ def test_attention_prefill_on_tensor_cores(K, nh, nkv, hd, window):
         for j in range(n):
             want[at + j] = reference_attention(qkv[at + j, :Q].float().view(nh, hd), k, v, j, window, scale)
         at += n
-    assert not torch.isnan(outs[0]).any()
-    assert rel_l2(outs[0], want.reshape(T, Q)) < 8e-3
-    assert rel_l2(outs[0], outs[1]) < 8e-3
+    for which, got in outs.items():
+        assert not torch.isnan(got).any(), which
+        assert rel_l2(got, want.reshape(T, Q)) < 8e-3, which

@@ -82,6 +82,8 @@ def lib():
         l.tb_attn_decode_mma_check.argtypes = [POINTER(AttnArgs), c_int]
         l.tb_attn_prefill_mma.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
         l.tb_attn_prefill_mma_check.argtypes = [POINTER(AttnArgs), c_int, c_int]
+        l.tb_attn_prefill_tc.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
+        l.tb_attn_prefill_tc_check.argtypes = [POINTER(AttnArgs), c_int, c_int]
         l.tb_sample.argtypes = [POINTER(SampleArgs), c_void_p]
         l.tb_decode_prepare.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         l.tb_commit_lengths.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
@@ -208,6 +210,19 @@ def attn_prefill_mma_accepts(args: AttnArgs, dtype: torch.dtype, all_fresh: bool
 def attn_prefill_mma(args: AttnArgs, all_fresh: bool, stream: int) -> None:
     """Causal attention of prompts that start at position 0, on tensor cores (bfloat16, head_dim 64 or 128)."""
     _check(lib().tb_attn_prefill_mma(byref(args), int(all_fresh), stream))
+
+
+def attn_prefill_tc_accepts(args: AttnArgs, dtype: torch.dtype, all_fresh: bool) -> bool:
+    return dtype == torch.bfloat16 and lib().tb_attn_prefill_tc_check(byref(args), BF16, int(all_fresh)) == 0
+
+
+def attn_prefill_tc(args: AttnArgs, all_fresh: bool, stream: int) -> None:
+    """Causal attention of prompts that start at position 0 on the tcgen05 tensor cores (bfloat16, head_dim 128)."""
+    _check(lib().tb_attn_prefill_tc(byref(args), int(all_fresh), stream))
+
+
+def attn_tc_error() -> int:
+    return int(lib().tb_attn_tc_error())
 
 
 def attn_mma_error() -> int:

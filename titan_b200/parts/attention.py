@@ -174,8 +174,10 @@ class AttentionMixer(Mixer):
                 aa.kv_new, aa.kv_stride = None, 0
             else:
                 aa.kv_new, aa.kv_stride = qkv.data_ptr() + Q * esz, width
-            fast = ctx.options.get("attention", "fast") != "plain" and not self.shared
-            if fast and K.attn_prefill_mma_accepts(aa, q_buf.dtype, lay.all_fresh):
+            mode = "plain" if self.shared else ctx.options.get("attention", "fast")   # "fast" | "mma" | "plain"
+            if mode == "fast" and K.attn_prefill_tc_accepts(aa, q_buf.dtype, lay.all_fresh):
+                K.attn_prefill_tc(aa, lay.all_fresh, ctx.stream)
+            elif mode in ("fast", "mma") and K.attn_prefill_mma_accepts(aa, q_buf.dtype, lay.all_fresh):
                 K.attn_prefill_mma(aa, lay.all_fresh, ctx.stream)
             else:
                 K.attn_prefill(aa, q_buf.dtype, ctx.stream)
