@@ -57,9 +57,14 @@ def find_nvcc() -> str:
     raise BuildError("nvcc was not found (CUDA_HOME, /usr/local/cuda/bin, PATH); the kernels cannot be built")
 
 
+def _extra_flags() -> List[str]:
+    """More nvcc flags from the environment (TITAN_B200_NVCC_FLAGS), for experiments such as -DNAME."""
+    return os.environ.get("TITAN_B200_NVCC_FLAGS", "").split()
+
+
 def _stamp() -> str:
     h = hashlib.sha256()
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + _extra_flags()).encode())
     for f in sources() + _headers():
         h.update(f.encode())
         with open(os.path.join(HERE, f), "rb") as fh:
@@ -119,7 +124,7 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> str:
 
     hb = threading.Thread(target=heartbeat, daemon=True)
     hb.start()
-    extra = ["-Xptxas", "-v"] if verbose_ptxas else []
+    extra = (["-Xptxas", "-v"] if verbose_ptxas else []) + _extra_flags()
 
     def one(src: str) -> str:
         obj = os.path.join(out, src[:-3] + ".o")

@@ -11,7 +11,7 @@
 
 namespace tbtma {
 
-constexpr uint32_t WAIT_LIMIT = 1u << 20;
+constexpr uint32_t WAIT_LIMIT = 1u << 18;      // try_wait rounds; each lasts up to the hardware's time limit
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -34,11 +34,21 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// mbarrier.try_wait suspends the thread in hardware until the phase completes or a system time limit
+// (microseconds) passes, so a waiter wakes as soon as the barrier flips; no sleep of our own is added.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* error_word, unsigned code) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        if (mbar_test(bar, parity)) return;
-        if (i > 64) __nanosleep(32);
-        if ((i & 1023u) == 1023u && *(volatile unsigned int*)error_word) break;   // another wait gave up already
+        if (mbar_try(bar, parity)) return;
+        if ((i & 255u) == 255u && *(volatile unsigned int*)error_word) break;     // another wait gave up already
     }
     atomicCAS(error_word, 0u, code);
 }
