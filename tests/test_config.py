@@ -4,7 +4,7 @@ import json
 import pytest
 
 from helpers import TINY_A, TINY_B, TINY_C
-from titan_b200.config import (ConfigError, MixerSpec, Qwen3Config, config_from_dict, known_architectures,
+from titan_b200.config import (ConfigError, Qwen3Config, config_from_dict, known_architectures,
                                load_config, register_architecture)
 
 

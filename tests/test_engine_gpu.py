@@ -1,11 +1,7 @@
 """The engine against the plain implementation, under every way of cutting the work.
 Needs a B200; each case runs in float32 (true 32-bit) and in bfloat16."""
 import os
-import subprocess
-import sys
-import json
 
-import numpy as np
 import pytest
 import torch
 
@@ -283,3 +279,23 @@ def test_captured_decode_steps_equal_eager_ones(worlds, name, dtype):
     assert [r.tokens[0] for r in ref] == first and [r.tokens[1] for r in ref] == second
     assert [r.tokens[21] for r in ref] == last
     graph.cache.check()
+
+
+def test_programmatic_dependent_launch_changes_no_result(worlds):
+    """The same steps with kernels overlapping their predecessors' tails and fully serialised."""
+    from titan_b200 import StepEntry, kernels as K
+    w = worlds["C"]
+    e = w.engine("float32")
+    toks = w.requests[2]
+    outs = []
+    try:
+        for on in (True, False):
+            K.set_pdl(on)
+            s = e.alloc_slot()
+            rows = [e.step([StepEntry(s, toks[:60], list(range(60)))])]
+            rows += [e.step([StepEntry(s, [t], [0])]) for t in toks[60:]]
+            e.free_slot(s)
+            outs.append(torch.cat(rows))
+    finally:
+        K.set_pdl(True)
+    assert torch.equal(outs[0], outs[1])

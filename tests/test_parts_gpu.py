@@ -1,8 +1,5 @@
 """Each part alone, built from its spec, against the plain functions; and a toy mixer with state of
 its own, defined here, registered, built and stepped without touching the library's files."""
-import dataclasses
-import math
-
 import pytest
 import torch
 

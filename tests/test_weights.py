@@ -9,7 +9,7 @@ import torch
 from helpers import TINY_A, TINY_B, random_weights, write_folder
 from titan_b200.config import config_from_dict, load_config
 from titan_b200.parts import declare_weights
-from titan_b200.weights import (DictWeights, FolderWeights, SafetensorsError, SafetensorsFile, WeightError,
+from titan_b200.weights import (FolderWeights, SafetensorsError, SafetensorsFile, WeightError,
                                 write_model_folder, write_safetensors)
 
 

@@ -26,7 +26,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from .slots import CacheError, CacheFull, PagePool
+from .slots import PagePool
 
 
 @dataclass(frozen=True)

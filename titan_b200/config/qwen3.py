@@ -10,10 +10,8 @@ A missing required key is an error that names the key (:94).
 """
 from __future__ import annotations
 
-import json
-import os
-from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from dataclasses import dataclass
+from typing import Any, Dict, Optional, Tuple
 
 from .spec import (ConfigError, FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec,
                    PositionSpec)

@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Any, Callable, Dict
+from typing import Any, Dict
 
 from .spec import ConfigError
 

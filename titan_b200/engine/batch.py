@@ -13,7 +13,7 @@ engine/engine-cuda/kernels/norm_rope.cu:19-22) or read ``*pos_ptr``
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 import torch

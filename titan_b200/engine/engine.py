@@ -13,14 +13,13 @@ forward_driver.rs:947-953, 3037-3043).
 """
 from __future__ import annotations
 
-import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from .. import kernels as K
-from ..cache import PAGE_SIZE, CacheError, CacheFull, SequenceCache
+from ..cache import PAGE_SIZE, CacheFull, SequenceCache
 from ..config import load_config
 from ..sampling import DeviceSampler, SamplerParams
 from ..weights import DictWeights, FolderWeights, RandomWeights

@@ -248,5 +248,10 @@ def commit_lengths(slot_of_seq, kv_len, seq_len, stream: int) -> None:
     _check(lib().tb_commit_lengths(slot_of_seq.data_ptr(), kv_len.data_ptr(), seq_len.data_ptr(), slot_of_seq.numel(), stream))
 
 
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for every kernel launched afterwards (on by default)."""
+    lib().tb_set_pdl(int(bool(on)))
+
+
 def uniform24(seed: int, sequence: int, step: int) -> int:
     return int(lib().tb_uniform24(seed, sequence, step))

@@ -29,7 +29,7 @@ from .. import kernels as K
 from ..cache.groups import CacheNeed, KVGroup
 from ..weights.loader import WeightSpec
 from . import linear
-from .base import MIXERS, NORMS, POSITIONS, Mixer
+from .base import MIXERS, POSITIONS, Mixer
 
 
 def decode_split(lay, kv_heads: int, options, fast: bool):
@@ -39,8 +39,9 @@ def decode_split(lay, kv_heads: int, options, fast: bool):
     bound = int(options.get("max_context", 0)) or lay.max_kv_len
     if not fast:
         chunk = int(options.get("attn_chunk", 256))
-    else:       # enough CTAs to fill the machine a few times over, no more: longer chunks pipeline better
-        want = max(1, -(-4 * int(options.get("sm_count", 148)) // (lay.B * kv_heads)))
+    else:       # two CTAs of the tensor-core kernel fit an SM: aim at (just under) two full rounds of CTAs
+        slots = 2 * int(options.get("sm_count", 148))
+        want = max(1, (2 * slots) // (lay.B * kv_heads))
         chunk = max(256, -(-(-(-bound // want)) // 64) * 64)
     # an eager step launches the splits its longest sequence needs; a captured one, whose grid cannot
     # change, launches what the context limit needs (the extra CTAs leave at once)

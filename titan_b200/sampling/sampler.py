@@ -8,7 +8,7 @@ tokens whatever else is in its batch.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import torch
 

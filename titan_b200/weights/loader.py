@@ -18,7 +18,7 @@ first problem (engine/engine-core/src/forward_driver.rs:315-358, 620-647).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Dict, Iterable, List, Optional, Tuple
+from typing import Dict, Iterable, List, Tuple
 
 import torch
 

@@ -17,7 +17,7 @@ from __future__ import annotations
 import hashlib
 import json
 import os
-from typing import Dict, Iterable, List
+from typing import List
 
 import torch
 

@@ -16,7 +16,7 @@ import mmap
 import os
 import struct
 import warnings
-from typing import Dict, Iterable, Iterator, List, Tuple
+from typing import Dict, Iterable, List, Tuple
 
 import numpy as np
 import torch
