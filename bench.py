@@ -88,6 +88,7 @@ def fill_cache_random(engine, slots, length):
     engine.cache.reserve({s: length for s in slots})
     for s in slots:
         engine.cache.commit(s, length)
+        engine.cache.state.seq_len[s] = length           # the device copy, which a real step advances itself
     for g in engine.cache.groups:
         if hasattr(g, "pool"):
             g.storage.normal_(0.0, 1.0)

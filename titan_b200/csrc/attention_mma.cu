@@ -95,6 +95,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
             const int slot = a.slot_of_seq[b];
             const int* tab = a.table + (size_t)slot * a.table_width;
             const int v_rows = a.num_pages * a.nkv * PAGE;          // rows of the K half
+            const uint64_t once = l2_evict_first_policy();          // a step reads every page once
             for (int i = 0; i < n_pages; ++i) {
                 const int s = i % STAGES, round = i / STAGES;
                 if (round > 0) mbar_wait(empty + s, (round - 1) & 1, &g_attn_error, 1);
@@ -105,8 +106,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
                 mbar_expect_tx(full + s, 2 * TILE_BYTES);
 #pragma unroll
                 for (int x = 0; x < BOXES; ++x) {
-                    tma_load_2d(kd + x * (PAGE * 128), &kv_map, full + s, x * 64, row);
-                    tma_load_2d(kd + TILE_BYTES + x * (PAGE * 128), &kv_map, full + s, x * 64, v_rows + row);
+                    tma_load_2d_hint(kd + x * (PAGE * 128), &kv_map, full + s, x * 64, row, once);
+                    tma_load_2d_hint(kd + TILE_BYTES + x * (PAGE * 128), &kv_map, full + s, x * 64, v_rows + row, once);
                 }
             }
         }

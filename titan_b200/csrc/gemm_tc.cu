@@ -9,7 +9,7 @@
 //
 // Plain mode is a persistent kernel (gemm_tc_persistent_kernel): one CTA per SM walks over the tiles,
 // the accumulator is double buffered in tensor memory, and the epilogue of a tile overlaps the MMAs
-// of the next.  Swap mode (gemm_tc_kernel) is one tile per CTA with two or three CTAs per SM; it can
+// of the next.  Swap mode (gemm_tc_kernel) is one tile per CTA with two CTAs per SM; it can
 // cut K into slices (grid.z), each CTA adding its partial sum into a float32 output with atomics, to
 // put enough CTAs on the machine when N / 128 is small.
 //
@@ -52,6 +52,7 @@ using tbtma::smem_u32;
 using tbtma::mbar_init;
 using tbtma::mbar_expect_tx;
 using tbtma::tma_load_2d;
+using tbtma::tma_load_2d_hint;
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, unsigned code) {
     tbtma::mbar_wait(bar, parity, &g_tc_error, code);
 }
@@ -90,7 +91,9 @@ struct TcArgs {
     int tiles_n;
 };
 
-template <int BN> constexpr int stages_for() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : 4); }   // small tiles: two or three CTAs per SM
+// TMA ring depth.  Decode tiles (BN <= 64) take as many stages as still let two CTAs share an SM: the
+// ring is filled before the wait on the previous kernel, so its depth is what bridges kernel boundaries.
+template <int BN> constexpr int stages_for() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 4 : (BN >= 32 ? 5 : 6))); }
 template <int BN> constexpr int tmem_cols_for() { return BN < 32 ? 32 : BN; }
 constexpr int EPI_TILE_FLOATS = 32 * 33;      // one warp's 32 x 32 transposition tile, padded against bank conflicts
 template <int BN, bool SWAP> constexpr size_t smem_for() {
@@ -254,9 +257,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 // The weight operand (A in swap mode, B in plain mode) is written by no kernel, so its
                 // tiles for the first stages are requested before the wait on the previous kernel.
                 const int pre = n_kb < STAGES ? n_kb : STAGES;
+                const uint64_t once = tbtma::l2_evict_first_policy();     // swap mode: every weight is read once
                 for (int i = 0; i < pre; ++i) {
                     mbar_expect_tx(full + i, A_BYTES + B_BYTES);
-                    if (SWAP) tma_load_2d(smem_a + i * A_BYTES, &map_a, full + i, (kb0 + i) * BK, tile_a * BM);
+                    if (SWAP) tma_load_2d_hint(smem_a + i * A_BYTES, &map_a, full + i, (kb0 + i) * BK, tile_a * BM, once);
                     else tma_load_2d(smem_b + i * B_BYTES, &map_b, full + i, (kb0 + i) * BK, tile_b * BN);
                 }
                 pdl_wait();
@@ -268,7 +272,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int s = i % STAGES, round = i / STAGES;
                     mbar_wait(empty + s, (round - 1) & 1, 1);
                     mbar_expect_tx(full + s, A_BYTES + B_BYTES);
-                    tma_load_2d(smem_a + s * A_BYTES, &map_a, full + s, (kb0 + i) * BK, tile_a * BM);
+                    if (SWAP) tma_load_2d_hint(smem_a + s * A_BYTES, &map_a, full + s, (kb0 + i) * BK, tile_a * BM, once);
+                    else tma_load_2d(smem_a + s * A_BYTES, &map_a, full + s, (kb0 + i) * BK, tile_a * BM);
                     tma_load_2d(smem_b + s * B_BYTES, &map_b, full + s, (kb0 + i) * BK, tile_b * BN);
                 }
             }
@@ -541,6 +546,12 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
     TcArgs a;
     a.out = out; a.K = K; a.ldo = ldo; a.k_blocks_per_split = kb; a.atomic = 0; a.tiles_m = a.tiles_n = 0;
     int rc = 0;
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
     if (!swap) {
         const int bn = N >= 256 ? 256 : 128;
         a.rows_a = M; a.rows_b = N;
@@ -548,12 +559,6 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         if (tb_make_map_bf16(&ma, X, M, K, ldx, BM) || tb_make_map_bf16(&mb, W, N, K, K, bn)) return 1;
         TB_REQUIRE((long long)a.tiles_m * a.tiles_n < (1LL << 30), "gemm_tc: too many tiles");
         const int total = a.tiles_m * a.tiles_n;
-        static int sm_count = 0;
-        if (!sm_count) {
-            int dev = 0;
-            cudaGetDevice(&dev);
-            if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
-        }
         dim3 grid(total < sm_count ? total : sm_count, 1, 1);
         rc = bn == 256 ? launch_persistent<256>(epi, ma, mb, a, grid, stream) : launch_persistent<128>(epi, ma, mb, a, grid, stream);
     } else {
@@ -562,7 +567,9 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         const int tiles = (N + BM - 1) / BM;
         int s = 1;
         if (epi == TB_EPI_ADD) {
-            s = splits > 0 ? splits : (224 + tiles / 2) / tiles;        // about one and a half CTAs per SM
+            // as many K slices as fill the machine once: two CTAs fit an SM up to BN = 64, one above
+            const int room = (bn <= 64 ? 2 : 1) * sm_count;
+            s = splits > 0 ? splits : room / tiles;
             const int max_s = kb / 4 > 0 ? kb / 4 : 1;              // at least four 64-wide blocks per slice
             s = s < 1 ? 1 : (s > max_s ? max_s : s);
         }
