@@ -187,7 +187,7 @@ def run_ours(args):
             ms = time_decode(engine, torch, K, b, kv_start, max(4, args.steps // 2), args.warmup, False)[0]
             points[f"decode_b{b}"] = round(b * 1e3 / ms, 1)
     T = args.prefill_tokens
-    pre_ms = time_prefill(engine, torch, T, 1, 3)
+    pre_ms = time_prefill(engine, torch, T, 3, 5)
     flops = prefill_flops(cfg, args.layers, T)
     err = K.gemm_tc_error() if hasattr(K, "gemm_tc_error") else 0
     line = {

@@ -58,6 +58,29 @@ def test_all_epilogues(K, M, N, Kd):
     assert K.gemm_tc_error() == 0
 
 
+@pytest.mark.parametrize("M,N,Kd", [(1100, 5000, 520), (2048, 4096, 1024), (300, 20000, 64)])
+def test_tail_split_and_whole_tiles_agree(K, M, N, Kd):
+    """ADD epilogue with a last round of tiles that does not fill the SMs: those tiles cut along K
+    (partial sums meet through atomics) against whole tiles per CTA, and both against float64."""
+    g = torch.Generator().manual_seed(N)
+    x = torch.randn(M, Kd, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, Kd, generator=g) * 0.1).to(torch.bfloat16)
+    res = torch.randn(M, N, generator=g)
+    want = res + P.linear(x.float(), w.float())
+    outs = []
+    try:
+        for on in (True, False):
+            K.set_gemm_tail_split(on)
+            acc = res.cuda()
+            K.gemm_tc(x.cuda(), w.cuda(), acc, K.EPI_ADD, stream())
+            assert K.gemm_tc_error() == 0
+            assert rel_l2(acc.cpu(), want) < 1e-5
+            outs.append(acc)
+    finally:
+        K.set_gemm_tail_split(True)
+    assert rel_l2(outs[0].cpu(), outs[1].cpu()) < 1e-6
+
+
 def test_strided_input_rows(K):
     g = torch.Generator().manual_seed(1)
     big = torch.randn(150, 400, generator=g).to(torch.bfloat16).cuda()

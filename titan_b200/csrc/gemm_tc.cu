@@ -89,6 +89,7 @@ struct TcArgs {
     int atomic;      // ADD epilogue through atomics (several K slices)
     int tiles_m;     // persistent kernel: tiles along A's rows and along B's rows
     int tiles_n;
+    int tail_split;  // persistent kernel, ADD epilogue: K parts of the tiles of the last, partly filled round (1: whole)
 };
 
 // TMA ring depth.  Decode tiles (BN <= 64) take as many stages as still let two CTAs share an SM: the
@@ -189,11 +190,30 @@ __device__ __forceinline__ void epilogue_chunk(const float* v, const TcArgs& a, 
 // the output (128 bytes of float32, 64 of bfloat16), eight rows in flight at a time.
 template <int EPI>
 __device__ __forceinline__ void epilogue_rows(const float* val, float* tile, const TcArgs& a, int row0, int col0,
-                                              int n_cols, int lane) {
+                                              int n_cols, int lane, bool atomic = false) {
     __syncwarp();
 #pragma unroll
     for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = val[j];
     __syncwarp();
+    if (EPI == TB_EPI_ADD && atomic) {
+        // four rows per instruction, a lane adds four neighbouring columns with one vector reduction
+        const int sub = lane >> 3, c = (lane & 7) * 4;
+        float* base = (float*)a.out + (size_t)row0 * a.ldo + col0 + c;
+#pragma unroll
+        for (int r4 = 0; r4 < 32; r4 += 4) {
+            const int r = r4 + sub;
+            if (row0 + r >= a.rows_a) continue;
+            const float* t = tile + r * 33 + c;
+            float* dst = base + (size_t)r * a.ldo;
+            if (col0 + c + 3 < n_cols) {
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(t[0]), "f"(t[1]), "f"(t[2]), "f"(t[3]) : "memory");
+            } else {
+                for (int j = 0; j < 4; ++j)
+                    if (col0 + c + j < n_cols) atomicAdd(dst + j, t[j]);
+            }
+        }
+        return;
+    }
     const int col = col0 + lane;
     if (col >= n_cols) return;
     float* o = (float*)a.out + (size_t)row0 * a.ldo + col;
@@ -331,6 +351,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // thread already accumulates tile i + 1 into the other buffer, and the TMA ring never drains between
 // tiles.  Roles and barriers: producer -> full[s] -> MMA -> empty[s] -> producer;
 // MMA -> acc_full[b] -> epilogue -> acc_empty[b] -> MMA.
+// The work of one CTA of the persistent kernel as a list of segments (tile, first k-block, k-blocks).
+// CTA c takes tiles c, c + grid, ... whole, as long as a round of tiles fills the grid.  The tiles of a
+// last, partly filled round can be cut along K into ``tail_split`` parts (ADD epilogue only, where a
+// partial sum can simply be added to the output through atomics), and the parts are dealt out the same
+// way, so that the round takes ceil(tiles * parts / grid) / parts of a tile's time instead of all of it.
+// Part p of every tail tile comes before part p + 1 of any, which keeps the CTAs that share an operand
+// panel at nearby k-blocks (L2 reuse).
+struct Segments {
+    int n_kb, total, head, tail_units, parts, kb_per_part;
+    int next_tile, next_unit, stride;
+    __device__ Segments(const TcArgs& a, int n_kb_) : n_kb(n_kb_) {
+        total = a.tiles_m * a.tiles_n;
+        stride = gridDim.x;
+        parts = 1; kb_per_part = n_kb;
+        head = total;
+        if (a.tail_split > 1) {
+            kb_per_part = (n_kb + a.tail_split - 1) / a.tail_split;
+            parts = (n_kb + kb_per_part - 1) / kb_per_part;
+            head = total / stride * stride;
+        }
+        tail_units = (total - head) * parts;
+        next_tile = blockIdx.x; next_unit = blockIdx.x;
+    }
+    __device__ bool next(int& tile, int& kb0, int& count) {
+        if (next_tile < head) {
+            tile = next_tile; kb0 = 0; count = n_kb; next_tile += stride;
+            return true;
+        }
+        if (next_unit >= tail_units) return false;
+        const int tail_tiles = total - head, part = next_unit / tail_tiles;
+        tile = head + next_unit - part * tail_tiles;
+        kb0 = part * kb_per_part;
+        count = n_kb - kb0 < kb_per_part ? n_kb - kb0 : kb_per_part;
+        next_unit += stride;
+        return true;
+    }
+};
+// The same walk one k-block at a time (for the TMA producer).
+struct KBlocks {
+    Segments seg; int tile, kb, left, tiles_m;
+    __device__ KBlocks(const TcArgs& a, int n_kb) : seg(a, n_kb), tile(0), kb(0), left(0), tiles_m(a.tiles_m) {}
+    __device__ bool next(int& tile_a, int& tile_b, int& k) {
+        if (left == 0) {
+            int kb0, count;
+            if (!seg.next(tile, kb0, count)) return false;
+            kb = kb0; left = count;
+        }
+        tile_a = tile % tiles_m; tile_b = tile / tiles_m; k = kb;
+        ++kb; --left;
+        return true;
+    }
+};
+
 template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs a) {
@@ -350,8 +423,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_kb = (a.K + BK - 1) / BK;
-    const int total = a.tiles_m * a.tiles_n;
-    const int my_tiles = total > (int)blockIdx.x ? (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
@@ -367,44 +438,37 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 
     if (warp == 0) {
         if (lane == 0) {
-            // k-block ``it`` (counted over all of this CTA's tiles) belongs to tile it / n_kb
-            const int total_kb = n_kb * my_tiles;
-            const int pre = total_kb < STAGES ? total_kb : STAGES;
-            auto rows_of = [&](int it, int& row_a, int& row_b, int& k) {
-                const int t = blockIdx.x + (it / n_kb) * gridDim.x;
-                row_a = (t % a.tiles_m) * BM; row_b = (t / a.tiles_m) * BN; k = (it % n_kb) * BK;
-            };
-            int ra, rb, k;
-            for (int it = 0; it < pre; ++it) {                // weights first: no kernel writes them
-                rows_of(it, ra, rb, k);
-                mbar_expect_tx(full + it, A_BYTES + B_BYTES);
-                tma_load_2d(smem_b + it * B_BYTES, &map_b, full + it, k, rb);
+            KBlocks w_blocks(a, n_kb), blocks(a, n_kb);       // two walks over the same k-blocks
+            int ta, tb, k, pre = 0;
+            for (; pre < STAGES && w_blocks.next(ta, tb, k); ++pre) {     // weights first: no kernel writes them
+                mbar_expect_tx(full + pre, A_BYTES + B_BYTES);
+                tma_load_2d(smem_b + pre * B_BYTES, &map_b, full + pre, k * BK, tb * BN);
             }
             pdl_wait();                                       // the activations come from the kernel before
             for (int it = 0; it < pre; ++it) {
-                rows_of(it, ra, rb, k);
-                tma_load_2d(smem_a + it * A_BYTES, &map_a, full + it, k, ra);
+                blocks.next(ta, tb, k);
+                tma_load_2d(smem_a + it * A_BYTES, &map_a, full + it, k * BK, ta * BM);
             }
-            for (int it = pre; it < total_kb; ++it) {
+            for (int it = pre; blocks.next(ta, tb, k); ++it) {
                 const int s = it % STAGES, round = it / STAGES;
-                rows_of(it, ra, rb, k);
                 mbar_wait(empty + s, (round - 1) & 1, 1);
                 mbar_expect_tx(full + s, A_BYTES + B_BYTES);
-                tma_load_2d(smem_a + s * A_BYTES, &map_a, full + s, k, ra);
-                tma_load_2d(smem_b + s * B_BYTES, &map_b, full + s, k, rb);
+                tma_load_2d(smem_a + s * A_BYTES, &map_a, full + s, k * BK, ta * BM);
+                tma_load_2d(smem_b + s * B_BYTES, &map_b, full + s, k * BK, tb * BN);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             pdl_wait();
             constexpr uint32_t idesc = instr_desc(BM, BN);
-            int it = 0;
-            for (int j = 0; j < my_tiles; ++j) {
+            Segments segs(a, n_kb);
+            int it = 0, tile, kb0, count;
+            for (int j = 0; segs.next(tile, kb0, count); ++j) {
                 const int buf = j & 1;
                 if (j >= 2) mbar_wait(acc_empty + buf, ((j >> 1) - 1) & 1, 4);     // the epilogue has drained this buffer
                 tc_fence_after();
                 const uint32_t acc = tmem + buf * BN;
-                for (int i = 0; i < n_kb; ++i, ++it) {
+                for (int i = 0; i < count; ++i, ++it) {
                     const int s = it % STAGES, round = it / STAGES;
                     mbar_wait(full + s, round & 1, 2);
                     tc_fence_after();
@@ -422,9 +486,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         pdl_wait();
         const int quarter = warp & 3;
         float* tile = epi_tiles + quarter * EPI_TILE_FLOATS;
-        for (int j = 0; j < my_tiles; ++j) {
-            const int t = blockIdx.x + j * gridDim.x;
+        Segments segs(a, n_kb);
+        int t, kb0, count;
+        for (int j = 0; segs.next(t, kb0, count); ++j) {
             const int tile_a = t % a.tiles_m, tile_b = t / a.tiles_m;
+            const bool partial = count < n_kb;           // another CTA adds the rest of this tile
             const int buf = j & 1;
             mbar_wait(acc_full + buf, (j >> 1) & 1, 3);
             tc_fence_after();
@@ -436,7 +502,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 for (int c = 0; c < BN; c += 32) {
                     float v[32];
                     tmem_ld32(taddr + c, v);
-                    epilogue_rows<EPI>(v, tile, a, row0, tile_b * BN + c, a.rows_b, lane);
+                    epilogue_rows<EPI>(v, tile, a, row0, tile_b * BN + c, a.rows_b, lane, partial);
                 }
             } else {
 #pragma unroll 1
@@ -517,6 +583,10 @@ int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const TcAr
 
 // Reads and clears the error word of the tensor-core kernels (0: none; 1, 2, 3: a wait of the
 // producer, the MMA issuer or the epilogue ran out).  Synchronises the device.
+int g_tail_split = 1;
+// Prompt products with the ADD epilogue: cut the tiles of a last, partly filled round along K (1, default) or not (0).
+extern "C" void tb_gemm_tc_set_tail_split(int on) { g_tail_split = on ? 1 : 0; }
+
 extern "C" int tb_gemm_tc_error() {
     unsigned int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(v)) != cudaSuccess) return -1;
@@ -544,7 +614,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
     const int kb = (K + BK - 1) / BK;
     CUtensorMap ma, mb;
     TcArgs a;
-    a.out = out; a.K = K; a.ldo = ldo; a.k_blocks_per_split = kb; a.atomic = 0; a.tiles_m = a.tiles_n = 0;
+    a.out = out; a.K = K; a.ldo = ldo; a.k_blocks_per_split = kb; a.atomic = 0; a.tiles_m = a.tiles_n = 0; a.tail_split = 1;
     int rc = 0;
     static int sm_count = 0;
     if (!sm_count) {
@@ -560,6 +630,17 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         TB_REQUIRE((long long)a.tiles_m * a.tiles_n < (1LL << 30), "gemm_tc: too many tiles");
         const int total = a.tiles_m * a.tiles_n;
         dim3 grid(total < sm_count ? total : sm_count, 1, 1);
+        const int tail = total % sm_count;
+        if (epi == TB_EPI_ADD && g_tail_split && total > sm_count && tail) {
+            // parts that make the last round shortest; a part keeps at least four k-blocks
+            int best = 1;
+            double best_cost = 1.0;
+            for (int p = 2; p <= 8 && kb / p >= 4; ++p) {
+                const double cost = (double)((tail * p + sm_count - 1) / sm_count) / p + 0.02 * p;   // + an epilogue per part
+                if (cost < best_cost - 1e-9) { best = p; best_cost = cost; }
+            }
+            a.tail_split = best;
+        }
         rc = bn == 256 ? launch_persistent<256>(epi, ma, mb, a, grid, stream) : launch_persistent<128>(epi, ma, mb, a, grid, stream);
     } else {
         const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));

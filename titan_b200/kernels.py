@@ -253,5 +253,10 @@ def set_pdl(on: bool) -> None:
     lib().tb_set_pdl(int(bool(on)))
 
 
+def set_gemm_tail_split(on: bool) -> None:
+    """Prompt products with the ADD epilogue: cut the tiles of a last, partly filled round along K (on by default) or keep them whole."""
+    lib().tb_gemm_tc_set_tail_split(int(bool(on)))
+
+
 def uniform24(seed: int, sequence: int, step: int) -> int:
     return int(lib().tb_uniform24(seed, sequence, step))
