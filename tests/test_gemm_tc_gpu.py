@@ -25,8 +25,18 @@ SHAPES = [(1, 128, 64), (5, 384, 256), (16, 200, 72), (17, 1000, 520), (40, 130,
           (1100, 5000, 520), (2048, 6144, 256)]      # more tiles than SMs: a CTA walks over two or three tiles
 
 
-@pytest.mark.parametrize("M,N,Kd", SHAPES)
-def test_all_epilogues(K, M, N, Kd):
+@pytest.fixture(params=["pairs", "single"])
+def cta_mode(request, K):
+    """Prompt products run on pairs of CTAs (cta_group::2) by default; the one-CTA kernel is tested too."""
+    K.set_gemm_pair(request.param == "pairs")
+    yield request.param
+    K.set_gemm_pair(True)
+
+
+@pytest.mark.parametrize("M,N,Kd", SHAPES + [(256, 256, 64), (300, 700, 136), (520, 264, 1032)])
+def test_all_epilogues(K, M, N, Kd, cta_mode):
+    if cta_mode == "single" and (M < 256 or N < 256):
+        pytest.skip("pairs are only used from 256 x 256 outputs on")
     g = torch.Generator().manual_seed(M + N + Kd)
     x = torch.randn(M, Kd, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, Kd, generator=g) * 0.1).to(torch.bfloat16)
@@ -59,7 +69,7 @@ def test_all_epilogues(K, M, N, Kd):
 
 
 @pytest.mark.parametrize("M,N,Kd", [(1100, 5000, 520), (2048, 4096, 1024), (300, 20000, 64)])
-def test_tail_split_and_whole_tiles_agree(K, M, N, Kd):
+def test_tail_split_and_whole_tiles_agree(K, M, N, Kd, cta_mode):
     """ADD epilogue with a last round of tiles that does not fill the SMs: those tiles cut along K
     (partial sums meet through atomics) against whole tiles per CTA, and both against float64."""
     g = torch.Generator().manual_seed(N)
@@ -79,6 +89,12 @@ def test_tail_split_and_whole_tiles_agree(K, M, N, Kd):
     finally:
         K.set_gemm_tail_split(True)
     assert rel_l2(outs[0].cpu(), outs[1].cpu()) < 1e-6
+
+
+def test_pairs_are_available(K):
+    """On a B200 every epilogue's pair kernel fits: the default path is the cta_group::2 one."""
+    for epi in (K.EPI_STORE, K.EPI_F32, K.EPI_ADD, K.EPI_SWIGLU):
+        assert K.gemm_pair_clusters(epi) >= 32
 
 
 def test_strided_input_rows(K):

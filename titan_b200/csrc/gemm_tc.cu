@@ -361,9 +361,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 struct Segments {
     int n_kb, total, head, tail_units, parts, kb_per_part;
     int next_tile, next_unit, stride;
-    __device__ Segments(const TcArgs& a, int n_kb_) : n_kb(n_kb_) {
+    __device__ Segments(const TcArgs& a, int n_kb_, int worker, int workers) : n_kb(n_kb_) {
         total = a.tiles_m * a.tiles_n;
-        stride = gridDim.x;
+        stride = workers;
         parts = 1; kb_per_part = n_kb;
         head = total;
         if (a.tail_split > 1) {
@@ -372,7 +372,7 @@ struct Segments {
             head = total / stride * stride;
         }
         tail_units = (total - head) * parts;
-        next_tile = blockIdx.x; next_unit = blockIdx.x;
+        next_tile = worker; next_unit = worker;
     }
     __device__ bool next(int& tile, int& kb0, int& count) {
         if (next_tile < head) {
@@ -391,7 +391,8 @@ struct Segments {
 // The same walk one k-block at a time (for the TMA producer).
 struct KBlocks {
     Segments seg; int tile, kb, left, tiles_m;
-    __device__ KBlocks(const TcArgs& a, int n_kb) : seg(a, n_kb), tile(0), kb(0), left(0), tiles_m(a.tiles_m) {}
+    __device__ KBlocks(const TcArgs& a, int n_kb, int worker, int workers)
+        : seg(a, n_kb, worker, workers), tile(0), kb(0), left(0), tiles_m(a.tiles_m) {}
     __device__ bool next(int& tile_a, int& tile_b, int& k) {
         if (left == 0) {
             int kb0, count;
@@ -438,7 +439,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 
     if (warp == 0) {
         if (lane == 0) {
-            KBlocks w_blocks(a, n_kb), blocks(a, n_kb);       // two walks over the same k-blocks
+            KBlocks w_blocks(a, n_kb, blockIdx.x, gridDim.x), blocks(a, n_kb, blockIdx.x, gridDim.x);       // two walks over the same k-blocks
             int ta, tb, k, pre = 0;
             for (; pre < STAGES && w_blocks.next(ta, tb, k); ++pre) {     // weights first: no kernel writes them
                 mbar_expect_tx(full + pre, A_BYTES + B_BYTES);
@@ -461,7 +462,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         if (lane == 0) {
             pdl_wait();
             constexpr uint32_t idesc = instr_desc(BM, BN);
-            Segments segs(a, n_kb);
+            Segments segs(a, n_kb, blockIdx.x, gridDim.x);
             int it = 0, tile, kb0, count;
             for (int j = 0; segs.next(tile, kb0, count); ++j) {
                 const int buf = j & 1;
@@ -486,7 +487,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         pdl_wait();
         const int quarter = warp & 3;
         float* tile = epi_tiles + quarter * EPI_TILE_FLOATS;
-        Segments segs(a, n_kb);
+        Segments segs(a, n_kb, blockIdx.x, gridDim.x);
         int t, kb0, count;
         for (int j = 0; segs.next(t, kb0, count); ++j) {
             const int tile_a = t % a.tiles_m, tile_b = t / a.tiles_m;
@@ -523,6 +524,136 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------- prompts: pairs of CTAs (cta_group::2)
+// A cluster of two CTAs on neighbouring SMs works on one 256 x 256 tile: each CTA loads 128 rows of X and
+// 128 rows of W per k-block (32 KB instead of the 48 KB a lone CTA needs for 128 x 256, so six stages
+// fit and every byte in shared memory feeds twice the MMA work), the leader (rank 0) issues
+// tcgen05.mma.cta_group::2 with M = 256, which reads both CTAs' shared memory, and each CTA's tensor
+// memory receives its 128 rows of the tile (two buffers of 256 columns: all 512).  Barriers:
+//   full[s]     leader only; both CTAs' TMA loads count their bytes on it (no multicast anywhere)
+//   empty[s]    in both CTAs; the leader's tcgen05.commit arrives on both when the MMAs have read stage s
+//   acc_full[b] in both CTAs, same way;  acc_empty[b]: leader only, the eight epilogue warps of the pair arrive
+// The walk over tiles, the tail split and the epilogues are those of the one-CTA kernel.
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_N = 256;
+constexpr uint32_t PAIR_A_BYTES = BM * BK * 2, PAIR_B_BYTES = 128 * BK * 2;
+constexpr size_t PAIR_SMEM = 1024 + (size_t)PAIR_STAGES * (PAIR_A_BYTES + PAIR_B_BYTES) + 256 + 4 * EPI_TILE_FLOATS * sizeof(float);
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs a) {
+    constexpr int STAGES = PAIR_STAGES;
+    constexpr uint32_t A_BYTES = PAIR_A_BYTES, B_BYTES = PAIR_B_BYTES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem_a = base;
+    uint8_t* smem_b = base + STAGES * A_BYTES;
+    uint64_t* full = (uint64_t*)(base + STAGES * (A_BYTES + B_BYTES));
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;          // [2]
+    uint64_t* acc_empty = acc_full + 2;           // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    float* epi_tiles = (float*)(base + STAGES * (A_BYTES + B_BYTES) + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = tbtma::cluster_rank();
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int n_kb = (a.K + BK - 1) / BK;
+
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, 512);
+    tc_fence_before();
+    tbtma::cluster_sync();                         // both CTAs' barriers exist before either signals the other's
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            KBlocks w_blocks(a, n_kb, pair, pairs), blocks(a, n_kb, pair, pairs);
+            int ta, tb, k, pre = 0;
+            for (; pre < STAGES && w_blocks.next(ta, tb, k); ++pre) {     // weights first: no kernel writes them
+                if (rank == 0) mbar_expect_tx(full + pre, 2 * (A_BYTES + B_BYTES));
+                tbtma::tma_load_2d_pair(smem_b + pre * B_BYTES, &map_b, tbtma::cluster_addr(full + pre, 0), k * BK, tb * PAIR_N + rank * 128);
+            }
+            pdl_wait();
+            for (int it = 0; it < pre; ++it) {
+                blocks.next(ta, tb, k);
+                tbtma::tma_load_2d_pair(smem_a + it * A_BYTES, &map_a, tbtma::cluster_addr(full + it, 0), k * BK, ta * 2 * BM + rank * BM);
+            }
+            for (int it = pre; blocks.next(ta, tb, k); ++it) {
+                const int s = it % STAGES, round = it / STAGES;
+                mbar_wait(empty + s, (round - 1) & 1, 1);
+                if (rank == 0) mbar_expect_tx(full + s, 2 * (A_BYTES + B_BYTES));
+                const uint32_t bar = tbtma::cluster_addr(full + s, 0);
+                tbtma::tma_load_2d_pair(smem_a + s * A_BYTES, &map_a, bar, k * BK, ta * 2 * BM + rank * BM);
+                tbtma::tma_load_2d_pair(smem_b + s * B_BYTES, &map_b, bar, k * BK, tb * PAIR_N + rank * 128);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            pdl_wait();
+            constexpr uint32_t idesc = instr_desc(2 * BM, PAIR_N);
+            Segments segs(a, n_kb, pair, pairs);
+            int it = 0, tile, kb0, count;
+            for (int j = 0; segs.next(tile, kb0, count); ++j) {
+                const int buf = j & 1;
+                if (j >= 2) mbar_wait(acc_empty + buf, ((j >> 1) - 1) & 1, 4);     // both CTAs' epilogues have drained this buffer
+                tc_fence_after();
+                const uint32_t acc = tmem + buf * PAIR_N;
+                for (int i = 0; i < count; ++i, ++it) {
+                    const int s = it % STAGES, round = it / STAGES;
+                    mbar_wait(full + s, round & 1, 2);
+                    tc_fence_after();
+                    const uint64_t da = smem_desc(smem_u32(smem_a + s * A_BYTES));
+                    const uint64_t db = smem_desc(smem_u32(smem_b + s * B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma_pair(acc, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    tc_commit_pair(empty + s, 3);
+                }
+                tc_commit_pair(acc_full + buf, 3);
+            }
+        }
+    } else {
+        pdl_wait();
+        const int quarter = warp & 3;
+        float* tile = epi_tiles + quarter * EPI_TILE_FLOATS;
+        Segments segs(a, n_kb, pair, pairs);
+        int t, kb0, count;
+        for (int j = 0; segs.next(t, kb0, count); ++j) {
+            const int tile_a = t % a.tiles_m, tile_b = t / a.tiles_m;
+            const bool partial = count < n_kb;
+            const int buf = j & 1;
+            mbar_wait(acc_full + buf, (j >> 1) & 1, 3);
+            tc_fence_after();
+            const int row0 = tile_a * 2 * BM + (int)rank * BM + quarter * 32;
+            const uint32_t taddr = tmem + buf * PAIR_N + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < PAIR_N; c += 32) {
+                float v[32];
+                tmem_ld32(taddr + c, v);
+                if (EPI == TB_EPI_ADD) epilogue_rows<EPI>(v, tile, a, row0, tile_b * PAIR_N + c, a.rows_b, lane, partial);
+                else epilogue_chunk<EPI, false, 32>(v, a, row0 + lane, tile_b * PAIR_N + c, lane);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tbtma::mbar_arrive_cluster(tbtma::cluster_addr(acc_empty + buf, 0));
+        }
+    }
+    pdl_wait();
+    tc_fence_before();
+    tbtma::cluster_sync();                         // nobody leaves while the other still reads its shared memory or signals it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem, 512);
     }
 }
 
@@ -567,6 +698,50 @@ int launch_persistent(int epi, const CUtensorMap& ma, const CUtensorMap& mb, con
     return 1;
 }
 
+// Clusters of two that the device can hold at once (0 if the query fails: then the one-CTA kernel runs).
+template <int EPI>
+int pair_clusters() {
+    static int n = -1;
+    if (n < 0) {
+        n = 0;
+        if (cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM) == cudaSuccess) {
+            cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2, 1, 1); cfg.blockDim = dim3(THREADS, 1, 1); cfg.dynamicSmemBytes = PAIR_SMEM;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tc_pair_kernel<EPI>, &cfg) == cudaSuccess && clusters > 0) n = clusters;
+            else cudaGetLastError();
+        } else {
+            cudaGetLastError();
+        }
+    }
+    return n;
+}
+template <int EPI>
+int launch_pair_epi(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, int pairs, cudaStream_t stream) {
+    tb_launch(gemm_tc_pair_kernel<EPI>, dim3(2 * pairs, 1, 1), THREADS, PAIR_SMEM, stream, ma, mb, a);
+    return 0;
+}
+int pair_clusters_for(int epi) {
+    switch (epi) {
+        case TB_EPI_STORE: return pair_clusters<TB_EPI_STORE>();
+        case TB_EPI_F32: return pair_clusters<TB_EPI_F32>();
+        case TB_EPI_ADD: return pair_clusters<TB_EPI_ADD>();
+        case TB_EPI_SWIGLU: return pair_clusters<TB_EPI_SWIGLU>();
+    }
+    return 0;
+}
+int launch_pair(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, int pairs, cudaStream_t stream) {
+    switch (epi) {
+        case TB_EPI_STORE: return launch_pair_epi<TB_EPI_STORE>(ma, mb, a, pairs, stream);
+        case TB_EPI_F32: return launch_pair_epi<TB_EPI_F32>(ma, mb, a, pairs, stream);
+        case TB_EPI_ADD: return launch_pair_epi<TB_EPI_ADD>(ma, mb, a, pairs, stream);
+        case TB_EPI_SWIGLU: return launch_pair_epi<TB_EPI_SWIGLU>(ma, mb, a, pairs, stream);
+    }
+    tb_set_error("gemm_tc: unknown epilogue %d", epi);
+    return 1;
+}
+
 template <int BN, bool SWAP>
 int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t stream) {
     switch (epi) {
@@ -583,6 +758,13 @@ int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const TcAr
 
 // Reads and clears the error word of the tensor-core kernels (0: none; 1, 2, 3: a wait of the
 // producer, the MMA issuer or the epilogue ran out).  Synchronises the device.
+int g_pair = 1;
+// Prompt products on pairs of CTAs (cta_group::2; 1, default) or on single CTAs (0).
+extern "C" void tb_gemm_tc_set_pair(int on) { g_pair = on ? 1 : 0; }
+
+// How many CTA pairs the device holds at once for this epilogue's kernel (0: the pair kernel cannot run).
+extern "C" int tb_gemm_tc_pair_clusters(int epi) { return pair_clusters_for(epi); }
+
 int g_tail_split = 1;
 // Prompt products with the ADD epilogue: cut the tiles of a last, partly filled round along K (1, default) or not (0).
 extern "C" void tb_gemm_tc_set_tail_split(int on) { g_tail_split = on ? 1 : 0; }
@@ -622,7 +804,30 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
     }
-    if (!swap) {
+    // parts along K for the tiles of a last, partly filled round of ``workers``: the fewest that make
+    // the round shortest (an epilogue per part is charged; a part keeps at least four k-blocks)
+    auto tail_parts = [&](int total, int workers) {
+        const int tail = total % workers;
+        int best = 1;
+        if (epi != TB_EPI_ADD || !g_tail_split || total <= workers || !tail) return best;
+        double best_cost = 1.0;
+        for (int p = 2; p <= 8 && kb / p >= 4; ++p) {
+            const double cost = (double)((tail * p + workers - 1) / workers) / p + 0.02 * p;
+            if (cost < best_cost - 1e-9) { best = p; best_cost = cost; }
+        }
+        return best;
+    };
+    const int pairs_max = (!swap && g_pair && M >= 256 && N >= 256) ? pair_clusters_for(epi) : 0;
+    if (pairs_max > 0) {
+        a.rows_a = M; a.rows_b = N;
+        a.tiles_m = (M + 2 * BM - 1) / (2 * BM); a.tiles_n = (N + PAIR_N - 1) / PAIR_N;
+        if (tb_make_map_bf16(&ma, X, M, K, ldx, BM) || tb_make_map_bf16(&mb, W, N, K, K, 128)) return 1;
+        TB_REQUIRE((long long)a.tiles_m * a.tiles_n < (1LL << 30), "gemm_tc: too many tiles");
+        const int total = a.tiles_m * a.tiles_n;
+        const int pairs = total < pairs_max ? total : pairs_max;
+        a.tail_split = tail_parts(total, pairs);
+        rc = launch_pair(epi, ma, mb, a, pairs, stream);
+    } else if (!swap) {
         const int bn = N >= 256 ? 256 : 128;
         a.rows_a = M; a.rows_b = N;
         a.tiles_m = (M + BM - 1) / BM; a.tiles_n = (N + bn - 1) / bn;
@@ -630,17 +835,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         TB_REQUIRE((long long)a.tiles_m * a.tiles_n < (1LL << 30), "gemm_tc: too many tiles");
         const int total = a.tiles_m * a.tiles_n;
         dim3 grid(total < sm_count ? total : sm_count, 1, 1);
-        const int tail = total % sm_count;
-        if (epi == TB_EPI_ADD && g_tail_split && total > sm_count && tail) {
-            // parts that make the last round shortest; a part keeps at least four k-blocks
-            int best = 1;
-            double best_cost = 1.0;
-            for (int p = 2; p <= 8 && kb / p >= 4; ++p) {
-                const double cost = (double)((tail * p + sm_count - 1) / sm_count) / p + 0.02 * p;   // + an epilogue per part
-                if (cost < best_cost - 1e-9) { best = p; best_cost = cost; }
-            }
-            a.tail_split = best;
-        }
+        a.tail_split = tail_parts(total, grid.x);
         rc = bn == 256 ? launch_persistent<256>(epi, ma, mb, a, grid, stream) : launch_persistent<128>(epi, ma, mb, a, grid, stream);
     } else {
         const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));

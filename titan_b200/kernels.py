@@ -258,5 +258,15 @@ def set_gemm_tail_split(on: bool) -> None:
     lib().tb_gemm_tc_set_tail_split(int(bool(on)))
 
 
+def set_gemm_pair(on: bool) -> None:
+    """Prompt products on pairs of CTAs that share one MMA (on by default) or on single CTAs."""
+    lib().tb_gemm_tc_set_pair(int(bool(on)))
+
+
+def gemm_pair_clusters(epi: int) -> int:
+    """CTA pairs the device holds at once for the pair kernel of this epilogue (0: it cannot run)."""
+    return int(lib().tb_gemm_tc_pair_clusters(int(epi)))
+
+
 def uniform24(seed: int, sequence: int, step: int) -> int:
     return int(lib().tb_uniform24(seed, sequence, step))
