@@ -136,7 +136,7 @@ template <typename TIn, typename TOut>
 __global__ void qk_norm_rope_kernel(QkArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float head_smem[];
+    extern __shared__ __align__(16) float head_smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int t = blockIdx.x;
     const int head = blockIdx.y * nwarp + warp;
@@ -213,9 +213,9 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
 }
 
 // Fast path for head sizes 64, 128 and 256 with the rotation over the whole head (or none): a lane
-// holds VE = head_dim / 32 consecutive elements (one 4- to 32-byte load), and an element's rotation
-// partner (head_dim / 2 away) is the same register of the lane 16 further, so no shared memory is
-// needed for the head.  Arguments and results are those of qk_norm_rope_kernel.
+// holds a few consecutive elements of the head's first half and their rotation partners from the second
+// half, so the head never goes through shared memory.  Arguments and results are those of
+// qk_norm_rope_kernel.
 template <typename T, int VE> __device__ __forceinline__ void load_vec(const T* p, float* o) {
     constexpr int BYTES = VE * (int)sizeof(T);
     T tmp[VE];
@@ -262,80 +262,135 @@ template <typename T, int VE> __device__ __forceinline__ void store_vec(T* p, co
     }
 }
 
-template <typename TIn, typename TOut, int VE>
+// A block takes TOK tokens.  First it puts what depends on the token alone into shared memory: the
+// rotation's cosines and sines and the place of the token's row in the cache (position, slot, block
+// table: a chain of dependent loads that is paid once per token, not once per head).  Then every warp
+// walks over heads (blockIdx.y * warps + warp, in steps of gridDim.y * warps), the same head for all TOK
+// tokens, whose TOK loads are in flight together.  A decode step launches one token and few heads per
+// block (many small blocks); a prompt launches four tokens and half of the heads per block.
+template <typename TIn, typename TOut, int HD, int LPH, int TOK>
 __global__ void qk_norm_rope_vec_kernel(QkArgs a) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float head_smem[];
-    constexpr int HD = 32 * VE, HALF = HD / 2;
+    extern __shared__ __align__(16) float head_smem[];
+    constexpr int HALF = HD / 2;
+    __shared__ long long row_off[TOK];              // element offset of the token's cache row for kv head 0; < 0: not written
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-    const int t = blockIdx.x;
-    const int head = blockIdx.y * nwarp + warp;
+    const int t0 = blockIdx.x * TOK;
+    const int n_tok = a.T - t0 < TOK ? a.T - t0 : TOK;
     const int n_heads = a.nh + a.nkv + (a.append ? a.nkv : 0);
-    float* cs = head_smem;
-    float* sn = cs + HALF;
-    if (a.inv_freq) {
-        const float p = (float)a.pos_of[t];
-        for (int k = threadIdx.x; k < HALF; k += blockDim.x) sincosf(p * a.inv_freq[k], &sn[k], &cs[k]);
-    }
-    __syncthreads();
-    if (head >= n_heads) return;
-    const bool is_q = head < a.nh, is_k = !is_q && head < a.nh + a.nkv;
-    const int col = head * HD;                       // Q heads, then K heads, then V heads, all HD wide
-    const TIn* x = (const TIn*)a.in + (size_t)t * a.in_stride + col + lane * VE;
-    float v[VE];
-    load_vec<TIn, VE>(x, v);
-    if (a.zero_in) {
-        float z[VE];
-#pragma unroll
-        for (int i = 0; i < VE; ++i) z[i] = 0.f;
-        store_vec<TIn, VE>(const_cast<TIn*>(x), z);
-    }
-    const int pos = a.pos_of[t];
-    const int seq = a.seq_of[t];
-    const int slot = a.slot_of_seq[seq];
-    const bool to_cache = a.append && !(a.cache.ring_rows && a.kv_len && pos < a.kv_len[seq] - a.cache.ring_rows);
-    if (!is_q && !is_k) {
-        if (to_cache)
-            store_vec<TOut, VE>((TOut*)a.cache.storage + kv_half_elems(a.cache) +
-                                kv_row_offset(a.cache, slot, pos, head - a.nh - a.nkv) + lane * VE, v);
-        return;
-    }
-    const float* w = is_q ? a.q_w : a.k_w;
-    if (w) {
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < VE; ++i) ss += v[i] * v[i];
-        ss = warp_sum(ss);
-        const float scale = 1.0f / sqrtf(ss / (float)HD + a.eps);
-#pragma unroll
-        for (int i = 0; i < VE; ++i) v[i] = v[i] * scale * w[lane * VE + i];
+    float* cs = head_smem;                           // [TOK][HALF] cosines, then [TOK][HALF] sines
+    float* sn = cs + TOK * HALF;
+    if (threadIdx.x < n_tok) {
+        const int t = t0 + threadIdx.x;
+        const int pos = a.pos_of[t], seq = a.seq_of[t];
+        const bool to_cache = a.append && !(a.cache.ring_rows && a.kv_len && pos < a.kv_len[seq] - a.cache.ring_rows);
+        row_off[threadIdx.x] = to_cache ? (long long)kv_row_offset(a.cache, a.slot_of_seq[seq], pos, 0) : -1;
     }
     if (a.inv_freq) {
-        const bool first = lane < 16;
-#pragma unroll
-        for (int i = 0; i < VE; ++i) {
-            const float other = __shfl_xor_sync(0xffffffffu, v[i], 16);
-            const int k = (lane & 15) * VE + i;
-            const float c = cs[k], s = sn[k];
-            v[i] = first ? v[i] * c - other * s : other * s + v[i] * c;
+        for (int i = threadIdx.x; i < n_tok * HALF; i += blockDim.x) {
+            const int j = i / HALF, k = i - j * HALF;
+            sincosf((float)a.pos_of[t0 + j] * a.inv_freq[k], &sn[i], &cs[i]);
         }
     }
-    if (is_q) {
-        store_vec<TOut, VE>((TOut*)a.q_out + (size_t)t * a.q_stride + head * HD + lane * VE, v);
-    } else {
-        if (a.k_out) store_vec<TOut, VE>((TOut*)a.k_out + (size_t)t * a.k_stride + (head - a.nh) * HD + lane * VE, v);
-        if (to_cache)
-            store_vec<TOut, VE>((TOut*)a.cache.storage + kv_row_offset(a.cache, slot, pos, head - a.nh) + lane * VE, v);
+    __syncthreads();
+    const size_t head_stride = (size_t)a.cache.page_size * a.cache.head_dim;      // between kv heads of a page
+    // LPH lanes hold a head, so a warp works on 32 / LPH heads at once.  A lane holds HV = HD / LPH / 2
+    // consecutive elements of the head's first half and the HV elements HD / 2 further on: an element and
+    // its rotation partner sit in the same lane, and both use the same angle.  Every lane runs every
+    // shuffle of the norm's sum: what a lane's head needs (norm, rotation, where it goes) is data, not
+    // control flow.
+    constexpr int HPW = 32 / LPH, HV = HD / LPH / 2;
+    const int sub = lane / LPH, l = lane % LPH;
+    for (int group = blockIdx.y * nwarp + warp; group * HPW < n_heads; group += gridDim.y * nwarp) {
+        const int head = group * HPW + sub;
+        const bool live = head < n_heads;
+        const bool is_q = head < a.nh, is_k = !is_q && head < a.nh + a.nkv;
+        const int col = head * HD + l * HV;          // Q heads, then K heads, then V heads, all HD wide
+        float lo[TOK][HV], hi[TOK][HV];
+#pragma unroll
+        for (int j = 0; j < TOK; ++j) {              // all loads first
+            if (live && j < n_tok) {
+                const TIn* src = (const TIn*)a.in + (size_t)(t0 + j) * a.in_stride + col;
+                load_vec<TIn, HV>(src, lo[j]);
+                load_vec<TIn, HV>(src + HALF, hi[j]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < HV; ++i) lo[j][i] = hi[j][i] = 0.f;
+            }
+        }
+        const float* w = is_q ? a.q_w : (is_k ? a.k_w : nullptr);
+        float wlo[HV], whi[HV];
+#pragma unroll
+        for (int i = 0; i < HV; ++i) {
+            wlo[i] = w ? w[l * HV + i] : 1.f;
+            whi[i] = w ? w[HALF + l * HV + i] : 1.f;
+        }
+        const bool rotate = a.inv_freq && (is_q || is_k);
+        // No early exit from this loop: its TOK bodies are independent, and the compiler interleaves
+        // them; a token beyond the end computes on zeros and stores nothing.
+#pragma unroll
+        for (int j = 0; j < TOK; ++j) {
+            const bool tok_live = live && j < n_tok;
+            const int t = t0 + j;
+            if (a.zero_in && tok_live) {
+                float z[HV];
+#pragma unroll
+                for (int i = 0; i < HV; ++i) z[i] = 0.f;
+                TIn* src = (TIn*)const_cast<void*>(a.in) + (size_t)t * a.in_stride + col;
+                store_vec<TIn, HV>(src, z);
+                store_vec<TIn, HV>(src + HALF, z);
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < HV; ++i) ss += lo[j][i] * lo[j][i] + hi[j][i] * hi[j][i];
+#pragma unroll
+            for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float scale = w ? 1.0f / sqrtf(ss / (float)HD + a.eps) : 1.f;
+#pragma unroll
+            for (int i = 0; i < HV; ++i) {
+                const float x = lo[j][i] * scale * wlo[i], y = hi[j][i] * scale * whi[i];
+                const float c = rotate ? cs[j * HALF + l * HV + i] : 1.f, sv = rotate ? sn[j * HALF + l * HV + i] : 0.f;
+                lo[j][i] = x * c - y * sv;
+                hi[j][i] = y * c + x * sv;
+            }
+            if (!tok_live) continue;
+            const long long off = row_off[j];
+            TOut* dst = nullptr;
+            if (is_q) {
+                dst = (TOut*)a.q_out + (size_t)t * a.q_stride + col;
+            } else if (is_k) {
+                if (a.k_out) {
+                    TOut* kd = (TOut*)a.k_out + (size_t)t * a.k_stride + col - a.nh * HD;
+                    store_vec<TOut, HV>(kd, lo[j]);
+                    store_vec<TOut, HV>(kd + HALF, hi[j]);
+                }
+                if (off >= 0) dst = (TOut*)a.cache.storage + (size_t)off + (size_t)(head - a.nh) * head_stride + l * HV;
+            } else if (off >= 0) {
+                dst = (TOut*)a.cache.storage + kv_half_elems(a.cache) + (size_t)off + (size_t)(head - a.nh - a.nkv) * head_stride + l * HV;
+            }
+            if (dst) {
+                store_vec<TOut, HV>(dst, lo[j]);
+                store_vec<TOut, HV>(dst + HALF, hi[j]);
+            }
+        }
     }
 }
 
+template <typename TIn, typename TOut, int TOK>
+static void launch_qk_vec_tok(const QkArgs& a, int warps, int head_groups, cudaStream_t stream) {
+    dim3 grid((a.T + TOK - 1) / TOK, head_groups);
+    const size_t smem = (size_t)TOK * a.hd * sizeof(float);
+    // sixteen lanes per head where a lane's share still is one or two 16-byte accesses
+    if (a.hd == 64) tb_launch(qk_norm_rope_vec_kernel<TIn, TOut, 64, 16, TOK>, grid, warps * 32, smem, stream, a);
+    else if (a.hd == 128) tb_launch(qk_norm_rope_vec_kernel<TIn, TOut, 128, 16, TOK>, grid, warps * 32, smem, stream, a);
+    else tb_launch(qk_norm_rope_vec_kernel<TIn, TOut, 256, 32, TOK>, grid, warps * 32, smem, stream, a);
+}
 template <typename TIn, typename TOut>
 static void launch_qk_vec(const QkArgs& a, dim3 grid, int threads, cudaStream_t stream) {
-    const size_t smem = (size_t)a.hd * sizeof(float);
-    if (a.hd == 64) tb_launch(qk_norm_rope_vec_kernel<TIn, TOut, 2>, grid, threads, smem, stream, a);
-    else if (a.hd == 128) tb_launch(qk_norm_rope_vec_kernel<TIn, TOut, 4>, grid, threads, smem, stream, a);
-    else tb_launch(qk_norm_rope_vec_kernel<TIn, TOut, 8>, grid, threads, smem, stream, a);
+    (void)threads;
+    if (a.T >= 64) launch_qk_vec_tok<TIn, TOut, 4>(a, 4, 2, stream);          // prompts: half of the heads of four tokens per block
+    else launch_qk_vec_tok<TIn, TOut, 1>(a, 4, (grid.y + 1) / 2, stream);    // decode steps: eight heads of one token per block
 }
 
 extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, cudaStream_t stream) {
@@ -352,9 +407,10 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     dim3 grid(a.T, (n_heads + warps - 1) / warps);
     const size_t smem = ((size_t)warps * a.hd + a.rot) * sizeof(float);
     const int in_bytes = in_dtype == TB_F32 ? 4 : 2, out_bytes = out_dtype == TB_F32 ? 4 : 2;
-    const int ve = a.hd / 32;
+    const int hv = a.hd == 256 ? 4 : a.hd / 32;        // consecutive elements per lane and half of the fast path
     auto aligned = [&](const void* p, long long stride_elems, int esz) {
-        return p == nullptr || (((uintptr_t)p % (size_t)(ve * esz)) == 0 && (stride_elems * esz) % (ve * esz) == 0);
+        const int unit = hv * esz < 16 ? hv * esz : 16;   // read and written in pieces of at most 16 bytes
+        return p == nullptr || (((uintptr_t)p % (size_t)unit) == 0 && (stride_elems * esz) % unit == 0);
     };
     const bool vec = (a.hd == 64 || a.hd == 128 || a.hd == 256) && (a.rot == a.hd || !a.inv_freq) &&
                      aligned(a.in, a.in_stride, in_bytes) && aligned(a.q_out, a.q_stride, out_bytes) &&
