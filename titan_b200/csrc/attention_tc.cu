@@ -2,18 +2,25 @@
 //
 // One CTA per (sequence, query head, block of 128 queries).  Per tile of 64 keys:
 //     S = Q . K^T        tcgen05.mma, A = Q and B = K both K-major in shared memory, S in tensor memory
-//     P = 2^(S*c - m)    eight softmax warps read S with tcgen05.ld (a thread holds half a query row)
-//                        and write P (bfloat16) into shared memory in the 128-byte-swizzled K-major layout
-//     O_t = P . V        tcgen05.mma, A = P (K-major), B = V as MN-major operand (V's rows are keys,
-//                        its contiguous dimension is the output dimension), O_t in tensor memory
-//     O = O * a + O_t    in the softmax threads' registers (64 output dims each), so tensor memory is
-//                        never rescaled
-// S, P and O_t are double buffered: the MMA thread issues S of the next tile before it waits for P of
-// this one, and P of tile j is written while P.V of tile j - 1 still runs; its O is folded afterwards.
-// Warp 0 loads Q once and K, V tiles through TMA (four stages), warp 1 allocates tensor memory and
-// issues the MMAs, warps 2..9 are the softmax / output warps (two per quarter of the rows).  The step's
-// own [T][Q | K | V] rows are the only source (every sequence starts at position 0); the cache is
-// not read.  Tensor memory: S 2 x 64 columns, O_t 2 x 128 columns.
+//     P = 2^(S*c - m)    a softmax thread reads its query row of S with tcgen05.ld and writes P (bfloat16)
+//                        into shared memory in the 128-byte-swizzled K-major layout
+//     O += P . V         tcgen05.mma, A = P (K-major), B = V as MN-major operand (V's rows are keys, its
+//                        contiguous dimension is the output dimension), O accumulated in tensor memory
+// The eight softmax warps form two groups of four (a thread = a query row); group g takes the key tiles
+// j with j % 2 == g as an online softmax of its own: its own P buffer, running maximum and sum, and
+// its own O in tensor memory.  A row's maximum is raised only when a tile exceeds it by more than
+// 2^RESCALE_LOG2 (P stays below that bound, which bfloat16 and the float32 sum hold easily); only then is
+// the group's O rescaled in tensor memory, which after the first tiles is rare.  At the end the groups'
+// (m, l, O) are merged like the parts of a split-key decode.  So a thread reads each score once,
+// nothing passes through registers per tile but the scores, and a group has a whole tile's time of
+// slack before its next scores are needed.
+// Warp 0 loads Q once and K and V tiles through TMA (rings of four each: K_j is free as soon as S_j is
+// done and is wanted four tiles ahead, V_j only after P.V).  Warp 1 allocates tensor memory and issues
+// the S MMAs into four S buffers, up to four tiles ahead; warp 10 issues the P.V MMAs.  The issue is
+// split because the issuing thread is the narrow place: a tcgen05.mma costs it tens of cycles however
+// small the product.  Warps 2..9 are the softmax groups.  The step's own [T][Q | K | V] rows are the
+// only source (every sequence starts at position 0); the cache is not read.
+// Tensor memory: S 4 x 64 columns, O 2 x 128 columns (all 512).
 //
 // All waits are bounded (tma.cuh); tb_attn_tc_error() reads the error word.  Built with -DTB_TC_TIMING
 // (TITAN_B200_NVCC_FLAGS), one warp of the first CTA adds up clock64() per phase of the softmax loop
@@ -42,7 +49,7 @@ __device__ unsigned long long g_tc_clk[16];
 #endif
 
 constexpr int HD = 128, BQ = 128, BKEY = 64;
-constexpr int THREADS = 320;                           // producer, MMA issuer, eight softmax / output warps
+constexpr int THREADS = 352;                           // producer, S issuer, eight softmax warps, P.V issuer
 constexpr uint32_t Q_BYTES = BQ * HD * 2;              // two boxes of 128 rows x 64 columns
 constexpr uint32_t Q_BOX = BQ * 128;
 constexpr uint32_t KV_TILE = BKEY * HD * 2;            // one K or V tile: two boxes of 64 rows x 64 columns
@@ -86,27 +93,30 @@ __device__ __forceinline__ float ex2(float x) {          // 2^x, one instruction
     return y;
 }
 
+constexpr float RESCALE_LOG2 = 8.0f;
+
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, TcAttnArgs a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_smem = base;                                       // 32 KB
     uint8_t* kv_smem = base + Q_BYTES;                            // KV_STAGES x (K 16 KB + V 16 KB)
-    uint8_t* p_smem = kv_smem + KV_STAGES * 2 * KV_TILE;          // 2 x 16 KB
+    uint8_t* p_smem = kv_smem + KV_STAGES * 2 * KV_TILE;          // 2 x 16 KB, one per group
     uint64_t* bars = (uint64_t*)(p_smem + 2 * P_BYTES);
     uint64_t* q_full = bars;
-    uint64_t* kv_full = bars + 1;            // [KV_STAGES]
-    uint64_t* kv_empty = bars + 5;           // [KV_STAGES]
-    uint64_t* s_full = bars + 9;             // [2]
-    uint64_t* p_full = bars + 11;            // [2]
-    uint64_t* o_full = bars + 13;            // [2]
-    uint64_t* o_empty = bars + 15;           // [2]
-    uint32_t* tmem_slot = (uint32_t*)(bars + 17);
-    float* sum_sh = (float*)(bars + 18);     // [2 halves][128 rows]: the halves' sums at the end
+    uint64_t* k_full = bars + 1;             // [KV_STAGES]  K and V have rings of their own: K_j is free as soon as
+    uint64_t* k_empty = bars + 5;            // [KV_STAGES]  S_j is done, long before V_j, and is wanted four tiles ahead
+    uint64_t* v_full = bars + 9;             // [KV_STAGES]
+    uint64_t* v_empty = bars + 13;           // [KV_STAGES]
+    uint64_t* s_full = bars + 17;            // [4] S of tile j is in tensor-memory buffer j % 4
+    uint64_t* p_full = bars + 21;            // [2] the group's four warps have written P
+    uint64_t* o_done = bars + 23;            // [2] the P.V MMAs issued so far into the group's O are complete
+    uint64_t* s_free = bars + 25;            // [4] the group's four warps have read S buffer j % 4
+    uint32_t* tmem_slot = (uint32_t*)(bars + 29);
+    float* ml_sh = (float*)(bars + 30);      // [2 groups][m, l][128 rows]
 
     pdl_launch_dependents();
     pdl_wait();
-    // which sequence and which block of 128 queries (blocks are numbered from the heaviest)
     int rem = blockIdx.x, seq = -1, blk = 0, tok0 = 0, n = 0;
     for (int s = 0; s < a.B; ++s) {
         const int t0 = a.q_start[s], ns = a.q_start[s + 1] - t0, nb = (ns + BQ - 1) / BQ;
@@ -123,10 +133,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(kv_full + s, 1); mbar_init(kv_empty + s, 1); }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(s_full + s, 1); mbar_init(p_full + s, 8); mbar_init(o_full + s, 1); mbar_init(o_empty + s, 8);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1);
+            mbar_init(s_full + s, 1); mbar_init(s_free + s, 4);
         }
+        for (int s = 0; s < 2; ++s) { mbar_init(p_full + s, 4); mbar_init(o_done + s, 1); }
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(tmem_slot, 512);
@@ -134,166 +145,196 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem;             // two S buffers of 64 columns: 0..63, 64..127
-    const uint32_t tmem_o = tmem + 128;       // two O buffers of 128 columns: 128..255, 256..383
+    const uint32_t tmem_s = tmem;             // S of tile j: columns 64 (j % 4) ..; a group owns two of the four buffers
+    const uint32_t tmem_o = tmem + 256;       // O of group g: columns 256 + 128 g ..
 
     if (warp == 0) {
         if (lane == 0) {
             mbar_expect_tx(q_full, Q_BYTES);
             tma_load_2d(q_smem, &q_map, q_full, h * HD, tok0 + r0);
             tma_load_2d(q_smem + Q_BOX, &q_map, q_full, h * HD + 64, tok0 + r0);
-            for (int i = 0; i < n_tiles; ++i) {
-                const int s = i % KV_STAGES;
-                if (i >= KV_STAGES) wait(kv_empty + s, (i / KV_STAGES - 1) & 1, 1);
-                uint8_t* kd = kv_smem + s * 2 * KV_TILE;
-                const int row = tok0 + (kt0 + i) * BKEY;
-                mbar_expect_tx(kv_full + s, 2 * KV_TILE);
-                tma_load_2d(kd, &kv_map, kv_full + s, a.k_col0 + kh * HD, row);
-                tma_load_2d(kd + KV_BOX, &kv_map, kv_full + s, a.k_col0 + kh * HD + 64, row);
-                tma_load_2d(kd + KV_TILE, &kv_map, kv_full + s, a.v_col0 + kh * HD, row);
-                tma_load_2d(kd + KV_TILE + KV_BOX, &kv_map, kv_full + s, a.v_col0 + kh * HD + 64, row);
+            // K and V tiles as their rings allow, whichever is free first (bounded polling)
+            int ki = 0, vi = 0;
+            for (uint32_t spin = 0; (ki < n_tiles || vi < n_tiles) && spin < (tbtma::WAIT_LIMIT << 4); ++spin) {
+                if (ki < n_tiles && (ki < KV_STAGES || tbtma::mbar_test(k_empty + ki % KV_STAGES, (ki / KV_STAGES - 1) & 1))) {
+                    const int s = ki % KV_STAGES, row = tok0 + (kt0 + ki) * BKEY;
+                    uint8_t* kd = kv_smem + s * 2 * KV_TILE;
+                    mbar_expect_tx(k_full + s, KV_TILE);
+                    tma_load_2d(kd, &kv_map, k_full + s, a.k_col0 + kh * HD, row);
+                    tma_load_2d(kd + KV_BOX, &kv_map, k_full + s, a.k_col0 + kh * HD + 64, row);
+                    ++ki; spin = 0;
+                }
+                if (vi < n_tiles && (vi < KV_STAGES || tbtma::mbar_test(v_empty + vi % KV_STAGES, (vi / KV_STAGES - 1) & 1))) {
+                    const int s = vi % KV_STAGES, row = tok0 + (kt0 + vi) * BKEY;
+                    uint8_t* vd = kv_smem + s * 2 * KV_TILE + KV_TILE;
+                    mbar_expect_tx(v_full + s, KV_TILE);
+                    tma_load_2d(vd, &kv_map, v_full + s, a.v_col0 + kh * HD, row);
+                    tma_load_2d(vd + KV_BOX, &kv_map, v_full + s, a.v_col0 + kh * HD + 64, row);
+                    ++vi; spin = 0;
+                }
             }
+            if (ki < n_tiles || vi < n_tiles) atomicCAS(&g_attn_tc_error, 0u, 1u);
         }
     } else if (warp == 1) {
+        // ---- S issuer: S_i = Q . K_i^T into S buffer i % 4, up to four tiles ahead of the softmax.  The
+        // issuing thread is the narrow place of this kernel (a tcgen05.mma costs it tens of cycles however
+        // small the product), so S and P.V are issued by different warps and the descriptors of a tile
+        // differ from a base by constants.
         if (lane == 0) {
-            const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
-            auto issue_s = [&](int i) {                     // S_i = Q . K_i^T into S buffer i & 1
+            const uint64_t q_desc = desc_k_major(smem_u32(q_smem));
+            wait(q_full, 0, 3);
+            for (int i = 0; i < n_tiles; ++i) {
                 const int s = i % KV_STAGES;
-                wait(kv_full + s, (i / KV_STAGES) & 1, 2);
+                if (i >= 4) wait(s_free + (i & 3), ((i >> 2) - 1) & 1, 9);
+                wait(k_full + s, (i / KV_STAGES) & 1, 2);
                 tc_fence_after();
-                const uint32_t k_addr = smem_u32(kv_smem + s * 2 * KV_TILE);
+                const uint64_t k_desc = desc_k_major(smem_u32(kv_smem + s * 2 * KV_TILE));
+                const uint32_t d = tmem_s + (i & 3) * BKEY;
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)        // 16 dims per step: box ks / 4, 32 bytes per step inside it
-                    tc_mma(tmem_s + (i & 1) * BKEY, desc_k_major(q_addr + (ks >> 2) * Q_BOX + (ks & 3) * 32),
-                           desc_k_major(k_addr + (ks >> 2) * KV_BOX + (ks & 3) * 32), IDESC_S, ks > 0 ? 1u : 0u);
-                tc_commit(s_full + (i & 1));
-            };
-            wait(q_full, 0, 3);
-            issue_s(0);
+                    tc_mma(d, q_desc + (uint64_t)(((ks >> 2) * Q_BOX + (ks & 3) * 32) >> 4),
+                           k_desc + (uint64_t)(((ks >> 2) * KV_BOX + (ks & 3) * 32) >> 4), IDESC_S, ks > 0 ? 1u : 0u);
+                tc_commit(s_full + (i & 3));
+                tc_commit(k_empty + s);
+            }
+        }
+    } else if (warp == 10) {
+        // ---- P.V issuer: O_g += P_j . V_j for the group g = j % 2
+        if (lane == 0) {
+            const uint64_t p_desc = desc_k_major(smem_u32(p_smem));
             for (int j = 0; j < n_tiles; ++j) {
-                const int b = j & 1;
-                if (j + 1 < n_tiles) issue_s(j + 1);        // its S buffer was read before P of tile j - 1 was signalled
-                wait(p_full + b, (j >> 1) & 1, 4);
-                if (j >= 2) wait(o_empty + b, ((j >> 1) - 1) & 1, 5);   // O of tile j - 2 has been folded
+                const int g = j & 1, s = j % KV_STAGES;
+                wait(v_full + s, (j / KV_STAGES) & 1, 5);
+                wait(p_full + g, (j >> 1) & 1, 4);          // the group has rescaled O if it had to and written P_j
                 tc_fence_after();
-                const uint32_t v_addr = smem_u32(kv_smem + (j % KV_STAGES) * 2 * KV_TILE + KV_TILE);
+                const uint64_t v_desc = desc_mn_major(smem_u32(kv_smem + s * 2 * KV_TILE + KV_TILE));
+                const uint64_t pd = p_desc + (uint64_t)((g * P_BYTES) >> 4);
+                const uint32_t d = tmem_o + g * HD;
 #pragma unroll
                 for (int ks = 0; ks < BKEY / 16; ++ks)      // 16 keys per step: 32 bytes of a P row, 16 rows of V
-                    tc_mma(tmem_o + b * HD, desc_k_major(p_addr + b * P_BYTES + ks * 32), desc_mn_major(v_addr + ks * 2048),
-                           IDESC_PV, ks > 0 ? 1u : 0u);
-                tc_commit(kv_empty + j % KV_STAGES);        // K_j (read by S_j) and V_j are free
-                tc_commit(o_full + b);
+                    tc_mma(d, pd + (uint64_t)((ks * 32) >> 4), v_desc + (uint64_t)((ks * 2048) >> 4), IDESC_PV, (j >= 2 || ks > 0) ? 1u : 0u);
+                tc_commit(v_empty + s);
+                tc_commit(o_done + g);
             }
         }
     } else {
-        // ---------------- softmax / output warps.  A warp may read the 32 tensor-memory lanes (query rows)
-        // 32 * (warp % 4) ..; two warps share each quarter, one takes the tile's keys 0..31 and output dims
-        // 0..63, the other keys 32..63 and dims 64..127.  The two agree on the row maximum through shared
-        // memory once per tile; each keeps its own partial sum until the end.  P and O are double buffered:
-        // P of tile j is written while the tensor core still multiplies P of tile j - 1 by V, and O of
-        // tile j - 1 is folded into the registers afterwards.
-        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const int g = (warp - 2) >> 2, quarter = warp & 3;       // a warp may touch the tensor-memory lanes 32 * (warp % 4) ..
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const int qpos = r0 + row;
         const int lo = a.window > 0 ? qpos - a.window + 1 : 0;
-        float acc[64];
-#pragma unroll
-        for (int d = 0; d < 64; ++d) acc[d] = 0.f;
-        float m_run = -1e30f, m_acc = -1e30f, l_run = 0.f;       // m_acc: the maximum that acc is scaled to
-        auto fold = [&](int b, uint32_t parity, float m_of_tile) {          // acc = acc * 2^(m_acc - m) + O_tile
-            wait(o_full + b, parity, 7);
-            tc_fence_after();
-            float o[64];
-            tmem_ld32_nowait(tmem_o + b * HD + lane_addr + half * 64, o);
-            tmem_ld32_nowait(tmem_o + b * HD + lane_addr + half * 64 + 32, o + 32);
-            tmem_wait_ld<64>(o);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(o_empty + b);
-            const float f = ex2(m_acc - m_of_tile);
-#pragma unroll
-            for (int i = 0; i < 64; ++i) acc[i] = fmaf(acc[i], f, o[i]);
-            m_acc = m_of_tile;
-        };
+        float m_run = -1e30f, l_run = 0.f;                       // the maximum P is taken against (may lag), the sum
+        int mine = 0;                                            // tiles of this group so far
 #ifdef TB_TC_TIMING
         const bool timing = blockIdx.x == 0 && blockIdx.y == 0 && warp == 2 && lane == 0;
         long long tprev = clock64();
 #endif
-        for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1;
-            const int key0 = (kt0 + j) * BKEY + half * 32;
-            const bool tile_visible = (kt0 + j) * BKEY + BKEY - 1 <= qpos && (kt0 + j) * BKEY >= lo;   // no mask needed in this tile
+        for (int j = g; j < n_tiles; j += 2, ++mine) {
+            const int key0 = (kt0 + j) * BKEY;
+            const bool tile_visible = key0 + BKEY - 1 <= qpos && key0 >= lo;       // no mask needed in this tile
             TCLK(0);
-            wait(s_full + b, (j >> 1) & 1, 6);
+            wait(s_full + (j & 3), (j >> 2) & 1, 6);
             tc_fence_after();
             TCLK(1);
-            // Both threads of a row read all 64 scores for the row maximum (tensor-memory reads are cheap, a
-            // barrier between the two warps is not); each then exponentiates its own 32.
-            float v[32], w[32];
-            tmem_ld32_nowait(tmem_s + b * BKEY + lane_addr + half * 32, v);
-            tmem_ld32_nowait(tmem_s + b * BKEY + lane_addr + (half ^ 1) * 32, w);
-            tmem_wait_ld<32>(v);
-            tmem_wait_ld<32>(w);
+            float v[64];
+            tmem_ld32_nowait(tmem_s + (j & 3) * BKEY + lane_addr, v);
+            tmem_ld32_nowait(tmem_s + (j & 3) * BKEY + lane_addr + 32, v + 32);
+            tmem_wait_ld<64>(v);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free + (j & 3));    // the S issuer may overwrite this buffer
             TCLK(2);
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains, not one of 64 links
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (tile_visible) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(v[i], w[i]));
+                for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
             } else {
-                const int other0 = (kt0 + j) * BKEY + (half ^ 1) * 32;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
+                for (int i = 0; i < 64; ++i) {
                     v[i] = (key0 + i <= qpos && key0 + i >= lo) ? v[i] : -INFINITY;
-                    const float o = (other0 + i <= qpos && other0 + i >= lo) ? w[i] : -INFINITY;
-                    mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(v[i], o));
+                    mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
                 }
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            const float cand = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
+            // Raise the row's maximum only when the tile exceeds it by more than the bound.
+            const bool raise = cand > m_run + RESCALE_LOG2;
+            const float m_new = raise ? cand : m_run;
+            const float f = raise ? ex2(m_run - m_new) : 1.f;
             TCLK(3);
-            const float m_before = m_run;
-            const float m_new = fmaxf(m_run, mx * a.scale_log2);
-            // P = 2^(S * scale - m) as bfloat16 into the swizzled K-major tile (masked keys hold -inf: P = 0).
-            // Its buffer is free: P.V of tile j - 2 had finished when its O was folded.
+            // P.V of the group's previous tile must be complete before P is overwritten (and before O is touched).
+            if (mine >= 1) {
+                wait(o_done + g, (mine - 1) & 1, 7);
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, raise)) {           // rescale this warp's 32 rows of O (f = 1 where nothing changed)
+#pragma unroll 1
+                    for (int c = 0; c < HD; c += 32) {
+                        float o[32];
+                        tmem_ld32(tmem_o + g * HD + lane_addr + c, o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] *= f;
+                        tmem_st32(tmem_o + g * HD + lane_addr + c, o);
+                    }
+                }
+            }
+            TCLK(4);
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
+            for (int i = 0; i < 64; ++i) {
                 v[i] = ex2(fmaf(v[i], a.scale_log2, -m_new));
                 sum4[i & 3] += v[i];
             }
-            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            uint8_t* p_row = p_smem + b * P_BYTES + row * 128;
+            l_run = l_run * f + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            m_run = m_new;
+            uint8_t* p_row = p_smem + g * P_BYTES + row * 128;
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {                // 8 keys = one 16-byte chunk of the row
+            for (int i = 0; i < 64; i += 8) {                // 8 keys = one 16-byte chunk of the row
                 uint4 pk;
                 pk.x = pack_bf16x2(v[i], v[i + 1]); pk.y = pack_bf16x2(v[i + 2], v[i + 3]);
                 pk.z = pack_bf16x2(v[i + 4], v[i + 5]); pk.w = pack_bf16x2(v[i + 6], v[i + 7]);
-                *reinterpret_cast<uint4*>(p_row + (((half * 4 + (i >> 3)) ^ (row & 7)) << 4)) = pk;
+                *reinterpret_cast<uint4*>(p_row + (((i >> 3) ^ (row & 7)) << 4)) = pk;
             }
-            l_run = l_run * ex2(m_run - m_new) + sum;
-            m_run = m_new;
-            TCLK(4);
+            TCLK(5);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full + b);
-            TCLK(5);
-            if (j >= 1) fold(b ^ 1, ((j - 1) >> 1) & 1, m_before);
-            TCLK(6);         // O of tile j - 1, scaled to the maximum it was made with
+            if (lane == 0) mbar_arrive(p_full + g);
+            TCLK(6);
         }
-        fold((n_tiles - 1) & 1, ((n_tiles - 1) >> 1) & 1, m_run);
-        // the two halves' sums
-        sum_sh[half * 128 + row] = l_run;
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter));          // the two warps of this quarter
-        l_run += sum_sh[(half ^ 1) * 128 + row];
-        const float inv = 1.0f / l_run;
+        if (mine >= 1) {                                         // the group's last P.V
+            wait(o_done + g, (mine - 1) & 1, 8);
+            tc_fence_after();
+        }
+        // merge the two groups: weights 2^(m_g - M) / L
+        ml_sh[(g * 2 + 0) * 128 + row] = mine ? m_run : -1e30f;
+        ml_sh[(g * 2 + 1) * 128 + row] = mine ? l_run : 0.f;
+        tc_fence_before();
+        asm volatile("bar.sync 1, 256;" ::: "memory");           // all eight softmax warps
+        tc_fence_after();
+        const float m0 = ml_sh[0 * 128 + row], l0 = ml_sh[1 * 128 + row], m1 = ml_sh[2 * 128 + row], l1 = ml_sh[3 * 128 + row];
+        const float M = fmaxf(m0, m1);
+        const float w0 = ex2(m0 - M), w1 = n_tiles > 1 ? ex2(m1 - M) : 0.f;
+        const float inv = 1.0f / (l0 * w0 + l1 * w1);
+        // this thread: output dims 64 g .. 64 g + 63 of its row, from both groups' O
+        float o0[64], o1[64];
+        tmem_ld32_nowait(tmem_o + lane_addr + g * 64, o0);
+        tmem_ld32_nowait(tmem_o + lane_addr + g * 64 + 32, o0 + 32);
+        if (n_tiles > 1) {                                       // uniform over the CTA
+            tmem_ld32_nowait(tmem_o + HD + lane_addr + g * 64, o1);
+            tmem_ld32_nowait(tmem_o + HD + lane_addr + g * 64 + 32, o1 + 32);
+        }
+        tmem_wait_ld<64>(o0);
+        if (n_tiles > 1) tmem_wait_ld<64>(o1);
         if (qpos < n) {
-            __nv_bfloat16* dst = a.out + (size_t)(tok0 + qpos) * a.out_stride + h * HD + half * 64;
+            const float c0 = w0 * inv, c1 = w1 * inv;
+            __nv_bfloat16* dst = a.out + (size_t)(tok0 + qpos) * a.out_stride + h * HD + g * 64;
 #pragma unroll
             for (int i = 0; i < 64; i += 8) {
+                float r[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) r[e] = n_tiles > 1 ? o0[i + e] * c0 + o1[i + e] * c1 : o0[i + e] * c0;
                 uint4 pk;
-                pk.x = pack_bf16x2(acc[i] * inv, acc[i + 1] * inv); pk.y = pack_bf16x2(acc[i + 2] * inv, acc[i + 3] * inv);
-                pk.z = pack_bf16x2(acc[i + 4] * inv, acc[i + 5] * inv); pk.w = pack_bf16x2(acc[i + 6] * inv, acc[i + 7] * inv);
+                pk.x = pack_bf16x2(r[0], r[1]); pk.y = pack_bf16x2(r[2], r[3]);
+                pk.z = pack_bf16x2(r[4], r[5]); pk.w = pack_bf16x2(r[6], r[7]);
                 *reinterpret_cast<uint4*>(dst + i) = pk;
             }
         }
@@ -333,7 +374,8 @@ extern "C" int tb_attn_prefill_tc(const AttnArgs* args, int all_fresh, cudaStrea
     p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
     p.nh = a.nh; p.nkv = a.nkv; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
     p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd;
-    constexpr size_t smem = 1024 + Q_BYTES + KV_STAGES * 2 * KV_TILE + 2 * P_BYTES + 256 + 2 * 128 * sizeof(float);
+    constexpr size_t smem = 1024 + Q_BYTES + KV_STAGES * 2 * KV_TILE + 2 * P_BYTES + 256 + 4 * 128 * sizeof(float);
+    static_assert(KV_STAGES == 4, "the second kernel's barrier layout and S buffers assume four stages");
     static bool configured = false;
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
