@@ -68,16 +68,15 @@ def test_all_epilogues(K, M, N, Kd, cta_mode):
     assert K.gemm_tc_error() == 0
 
 
-@pytest.mark.parametrize("M,N,Kd", [(1100, 5000, 520), (2048, 4096, 1024), (300, 20000, 64)])
+@pytest.mark.parametrize("M,N,Kd", [(1100, 5000, 520), (2048, 4096, 1024), (300, 20000, 64), (512, 1024, 2048)])
 def test_tail_split_and_whole_tiles_agree(K, M, N, Kd, cta_mode):
-    """ADD epilogue with a last round of tiles that does not fill the SMs: those tiles cut along K
-    (partial sums meet through atomics) against whole tiles per CTA, and both against float64."""
+    """ADD epilogue with a last round of tiles that does not fill the SMs (or fewer tiles than SMs
+    altogether): those tiles cut along K (partial sums meet through atomics) against whole tiles per CTA, and both against float64."""
     g = torch.Generator().manual_seed(N)
     x = torch.randn(M, Kd, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, Kd, generator=g) * 0.1).to(torch.bfloat16)
     res = torch.randn(M, N, generator=g)
     want = res + P.linear(x.float(), w.float())
-    outs = []
     try:
         for on in (True, False):
             K.set_gemm_tail_split(on)

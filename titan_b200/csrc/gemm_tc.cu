@@ -809,7 +809,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
     auto tail_parts = [&](int total, int workers) {
         const int tail = total % workers;
         int best = 1;
-        if (epi != TB_EPI_ADD || !g_tail_split || total <= workers || !tail) return best;
+        if (epi != TB_EPI_ADD || !g_tail_split || !tail) return best;      // total < workers: every tile is in the last round
         double best_cost = 1.0;
         for (int p = 2; p <= 8 && kb / p >= 4; ++p) {
             const double cost = (double)((tail * p + workers - 1) / workers) / p + 0.02 * p;
@@ -824,8 +824,9 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         if (tb_make_map_bf16(&ma, X, M, K, ldx, BM) || tb_make_map_bf16(&mb, W, N, K, K, 128)) return 1;
         TB_REQUIRE((long long)a.tiles_m * a.tiles_n < (1LL << 30), "gemm_tc: too many tiles");
         const int total = a.tiles_m * a.tiles_n;
-        const int pairs = total < pairs_max ? total : pairs_max;
-        a.tail_split = tail_parts(total, pairs);
+        a.tail_split = tail_parts(total, pairs_max);
+        const int units = total < pairs_max ? total * a.tail_split : total;      // fewer tiles than pairs: the parts fill the grid
+        const int pairs = units < pairs_max ? units : pairs_max;
         rc = launch_pair(epi, ma, mb, a, pairs, stream);
     } else if (!swap) {
         const int bn = N >= 256 ? 256 : 128;
@@ -834,8 +835,9 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         if (tb_make_map_bf16(&ma, X, M, K, ldx, BM) || tb_make_map_bf16(&mb, W, N, K, K, bn)) return 1;
         TB_REQUIRE((long long)a.tiles_m * a.tiles_n < (1LL << 30), "gemm_tc: too many tiles");
         const int total = a.tiles_m * a.tiles_n;
-        dim3 grid(total < sm_count ? total : sm_count, 1, 1);
-        a.tail_split = tail_parts(total, grid.x);
+        a.tail_split = tail_parts(total, sm_count);
+        const int units = total < sm_count ? total * a.tail_split : total;
+        dim3 grid(units < sm_count ? units : sm_count, 1, 1);
         rc = bn == 256 ? launch_persistent<256>(epi, ma, mb, a, grid, stream) : launch_persistent<128>(epi, ma, mb, a, grid, stream);
     } else {
         const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
