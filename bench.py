@@ -240,6 +240,84 @@ def profile_case():
     return 0
 
 
+def micro():
+    """Kernels of the benchmark's layer sizes timed alone with CUDA events (back to back, after warm-up);
+    the figures that the summaries under profiles/ quote beside the ncu captures.  Prints text lines."""
+    import torch
+
+    from titan_b200 import Engine, StepEntry, kernels as K
+    from titan_b200.config import config_from_dict
+    K.lib()
+    st = torch.cuda.current_stream().cuda_stream
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n * 1e3           # microseconds
+
+    for n in (16, 32, 64, 128, 192, 256):
+        print(f"tcgen05.mma 128 x {n:3d} x 16: {K.mma_probe(n):6.1f} clocks each, back to back on every SM", flush=True)
+    H, F = QWEN3_8B["hidden_size"], QWEN3_8B["intermediate_size"]
+    QKV = (QWEN3_8B["num_attention_heads"] + 2 * QWEN3_8B["num_key_value_heads"]) * QWEN3_8B["head_dim"]
+    shapes = [("qkv", QKV, H, K.EPI_ADD, K.EPI_STORE), ("o", H, H, K.EPI_ADD, K.EPI_ADD),
+              ("gate+up", 2 * F, H, K.EPI_SWIGLU, K.EPI_SWIGLU), ("down", H, F, K.EPI_ADD, K.EPI_ADD)]
+    copies = 12                                       # different weights per call: more than L2 in total
+    for M in (1, 8, 64):
+        for name, N, Kd, epi, _ in shapes:
+            ws = [torch.randn(N, Kd, device="cuda").to(torch.bfloat16) for _ in range(copies)]
+            x = torch.randn(M, Kd, device="cuda").to(torch.bfloat16)
+            out = torch.zeros(M, N // 2 if epi == K.EPI_SWIGLU else N, device="cuda",
+                              dtype=torch.bfloat16 if epi == K.EPI_SWIGLU else torch.float32)
+            us = timed(lambda: [K.gemm_tc(x, w, out, epi, st) for w in ws], 5) / copies
+            print(f"decode product M={M:2d} {name:8s} {N:6d} x {Kd:5d}: {us:7.1f} us  {N * Kd * 2 / us / 1e6:5.2f} TB/s", flush=True)
+            del ws
+    M = 2048
+    for name, N, Kd, _, epi in shapes:
+        w = torch.randn(N, Kd, device="cuda").to(torch.bfloat16)
+        x = torch.randn(M, Kd, device="cuda").to(torch.bfloat16)
+        out = torch.zeros(M, N // 2 if epi == K.EPI_SWIGLU else N, device="cuda",
+                          dtype=torch.float32 if epi == K.EPI_ADD else torch.bfloat16)
+        for pair in (True, False):
+            K.set_gemm_pair(pair)
+            us = timed(lambda: K.gemm_tc(x, w, out, epi, st), 20)
+            print(f"prompt product M={M} {name:8s} {N:6d} x {Kd:5d} {'CTA pairs' if pair else 'one CTA  '}: {us:7.1f} us  "
+                  f"{2 * M * N * Kd / us / 1e6:5.0f} TFLOP/s", flush=True)
+        K.set_gemm_pair(True)
+    # the other kernels of a prompt, inside one layer's step: each launcher call repeated in place
+    cfg = dict(QWEN3_8B)
+    cfg["num_hidden_layers"] = 1
+    engine = Engine.from_random(config_from_dict(cfg), 2, "bfloat16", max_tokens=8192, max_context=8192, max_slots=2, max_batch=2)
+    found = {}
+
+    def repeated(name):
+        f = getattr(K, name)
+
+        def g(*a, **k):
+            found.setdefault(name, []).append(timed(lambda: f(*a, **k), 20))
+        return g
+    originals = {n: getattr(K, n) for n in ("qk_norm_rope", "rmsnorm", "attn_prefill_tc")}
+    for n in originals:
+        setattr(K, n, repeated(n))
+    try:
+        s = engine.alloc_slot()
+        engine.step([StepEntry(s, [(13 * i + 5) % engine.vocab_size for i in range(M)], [M - 1])])
+    finally:
+        for n, f in originals.items():
+            setattr(K, n, f)
+    for n, v in found.items():
+        print(f"prompt of {M} tokens, {n}: " + ", ".join(f"{x:.1f}" for x in v) + " us (rows: " +
+              ("2048, 2048, 1" if n == "rmsnorm" else "2048") + ")", flush=True)
+    print("wait errors:", K.gemm_tc_error(), K.attn_tc_error())
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -252,9 +330,12 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--profile-case", action="store_true", help="run the small one-layer case used for ncu captures and exit")
+    ap.add_argument("--micro", action="store_true", help="time the layer's kernels alone (CUDA events) and exit; text lines, not the JSON line")
     args = ap.parse_args()
     if args.profile_case:
         return profile_case()
+    if args.micro:
+        return micro()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "berniehans/titan is a Rust workspace (cargo is not installed) "
                           "that needs GGUF Q4_K weights and NVRTC for compute_86; it cannot be installed or run offline here"}))

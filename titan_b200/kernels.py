@@ -268,5 +268,12 @@ def gemm_pair_clusters(epi: int) -> int:
     return int(lib().tb_gemm_tc_pair_clusters(int(epi)))
 
 
+def mma_probe(n: int, iters: int = 4096) -> float:
+    """Clocks one tcgen05.mma of 128 x n x 16 takes, issued back to back on every SM (a measurement, used by no step)."""
+    out = ctypes.c_double(0.0)
+    _check(lib().tb_mma_probe(int(n), int(iters), byref(out)))
+    return float(out.value)
+
+
 def uniform24(seed: int, sequence: int, step: int) -> int:
     return int(lib().tb_uniform24(seed, sequence, step))
