@@ -268,12 +268,12 @@ def test_attention_refuses_bad_heads(K):
 
 # ------------------------------------------------------------------ sampling
 class SamplerBench:
-    def __init__(self, K, V, B, seed=0):
+    def __init__(self, K, V, B, seed=0, parts=None):
         from titan_b200.cache import SlotState
         from titan_b200.sampling import DeviceSampler
         self.K, self.V, self.B = K, V, B
         self.state = SlotState(B + 3, "cuda")
-        self.sampler = DeviceSampler(self.state, B + 3, V, "cuda")
+        self.sampler = DeviceSampler(self.state, B + 3, V, "cuda", parts=parts)
         self.slots = list(range(2, 2 + B))
         self.slot_t = torch.tensor(self.slots, dtype=torch.int32, device="cuda")
 
@@ -303,12 +303,13 @@ def test_argmax_whole_vocabulary_lowest_index_on_ties(K, V):
     logits[1, 77] = logits[1, 400] = 8.0        # a tie
     logits[2, :] = -1.0                         # all equal
     logits[3, 5] = float("nan")
-    b = SamplerBench(K, V, 4)
+    b = SamplerBench(K, V, 4, parts=None if V > 1000 else 3)
     got = b.run(logits, [SamplerParams.greedy()] * 4, [0, 1, 2, 3])[0]
     assert got[:3] == [V - 1, 77, 0] and got[3] == int(torch.argmax(torch.nan_to_num(logits[3], nan=-1e30)))
 
 
-def test_sampling_matches_the_plain_sampler(K):
+@pytest.mark.parametrize("parts", [0, 7])       # the row's maximum by one block, and by seven blocks of uneven slices
+def test_sampling_matches_the_plain_sampler(K, parts):
     from titan_b200.sampling import SamplerParams
     V, B = 1000, 6
     g = torch.Generator().manual_seed(5)
@@ -318,7 +319,7 @@ def test_sampling_matches_the_plain_sampler(K):
               SamplerParams(0.9, 0.8, 50, 1.5, 5), SamplerParams(1.0, 1.0, 2, 1.0, 6), SamplerParams(0.0, 1.0, 0, 2.0, 7)]
     context = [random_ctx.tolist() for random_ctx in torch.randint(0, V, (B, 40), generator=g)]
     context[5] = [int(torch.argmax(logits[5]))] * 3          # the greedy row's winner is penalised away
-    b = SamplerBench(K, V, B)
+    b = SamplerBench(K, V, B, parts=parts)
     steps = 40
     got = b.run(logits, params, [10, 11, 12, 13, 14, 15], context, steps=steps)
     seen = [set(c) for c in context]

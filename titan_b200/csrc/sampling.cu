@@ -1,4 +1,5 @@
-// Token sampling on the device, one block per row of logits.
+// Token sampling on the device: several blocks per row find the maximum and its lowest index (the
+// answer when greedy), then one block per row does the rest.
 //
 // Order of operations, after berniehans/titan's host sampler (engine/engine-core/src/sampler.rs:109-240):
 // repetition penalty over the tokens seen so far (positive logit / pen, else * pen, :132-145);
@@ -25,6 +26,7 @@ struct SampleArgs {
     const long long* seed; const long long* sequence_id; int* sample_step; int* last_token; // per slot
     unsigned* seen; int seen_words;              // per slot bitmap of context tokens, or null
     int* out;                                    // [B]
+    float* part_best; int* part_idx; int parts;  // [B][parts] scratch: the maximum as found by several blocks per row (parts 0: one block scans the row)
 };
 
 typedef unsigned long long u64;
@@ -159,6 +161,68 @@ __device__ int nth_in_order(int V, PFn pred, u64 need, Shared& sh) {
     return sh.result;
 }
 
+// (value, index) pairs: the larger value wins, the lower index among equals; INT_MAX marks "none yet".
+__device__ __forceinline__ bool better(float ob, int oi, float best, int best_i) {
+    return oi != INT_MAX && (best_i == INT_MAX || ob > best || (ob == best && oi < best_i));
+}
+
+// Maximum of value(i) over [lo, hi) and its lowest index, per thread (eight loads in flight).
+__device__ __forceinline__ void scan_max(const Row& r, int lo, int hi, int tid, int nthreads, float& best, int& best_i) {
+    for (int i0 = lo + tid; i0 < hi; i0 += 8 * nthreads) {
+        float xs[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * nthreads;
+            xs[u] = i < hi ? r.value(i) : -INFINITY;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * nthreads;
+            if (i < hi && (best_i == INT_MAX || xs[u] > best)) { best = xs[u]; best_i = i; }
+        }
+    }
+}
+
+__device__ __forceinline__ Row row_of(const SampleArgs& a, int row, int slot, bool greedy, float temperature) {
+    Row r;
+    r.logits = a.logits + (size_t)row * a.ld;
+    r.seen = a.seen ? a.seen + (size_t)slot * a.seen_words : nullptr;
+    r.pen = a.penalty[slot];
+    r.inv_t = greedy ? 1.0f : 1.0f / temperature;
+    r.V = a.V;
+    return r;
+}
+
+// Block (row, part): the maximum of the part's slice of the row, for sample_kernel to finish.
+#define MAX_THREADS 256
+__global__ void __launch_bounds__(MAX_THREADS) sample_max_kernel(SampleArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float fred[MAX_THREADS / 32];
+    __shared__ int ired[MAX_THREADS / 32];
+    const int row = blockIdx.x, part = blockIdx.y, slot = a.slot_of_row[row], tid = threadIdx.x;
+    const float temperature = a.temperature[slot];
+    const Row r = row_of(a, row, slot, temperature <= 1e-4f, temperature);
+    const int per = (a.V + a.parts - 1) / a.parts;
+    const int lo = min(a.V, part * per), hi = min(a.V, lo + per);
+    float best = -INFINITY; int best_i = INT_MAX;
+    scan_max(r, lo, hi, tid, blockDim.x, best, best_i);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (better(ob, oi, best, best_i)) { best = ob; best_i = oi; }
+    }
+    if ((tid & 31) == 0) { fred[tid >> 5] = best; ired[tid >> 5] = best_i; }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < MAX_THREADS / 32; ++w)
+            if (better(fred[w], ired[w], best, best_i)) { best = fred[w]; best_i = ired[w]; }
+        a.part_best[(size_t)row * a.parts + part] = best;
+        a.part_idx[(size_t)row * a.parts + part] = best_i;
+    }
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(SampleArgs a) {
     pdl_launch_dependents();
     pdl_wait();
@@ -166,33 +230,25 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(SampleArgs a) {
     const int row = blockIdx.x, slot = a.slot_of_row[row], V = a.V, tid = threadIdx.x;
     const float temperature = a.temperature[slot];
     const bool greedy = temperature <= 1e-4f;
-    Row r;
-    r.logits = a.logits + (size_t)row * a.ld;
-    r.seen = a.seen ? a.seen + (size_t)slot * a.seen_words : nullptr;
-    r.pen = a.penalty[slot];
-    r.inv_t = greedy ? 1.0f : 1.0f / temperature;
-    r.V = V;
+    const Row r = row_of(a, row, slot, greedy, temperature);
 
-    // ---- maximum and its lowest index (this is the answer when greedy)
+    // ---- maximum and its lowest index (this is the answer when greedy): from the parts that
+    // sample_max_kernel left, or by scanning the row here
     float best = -INFINITY; int best_i = INT_MAX;
-    for (int i0 = tid; i0 < V; i0 += 8 * blockDim.x) {     // eight loads in flight per thread
-        float xs[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int i = i0 + u * blockDim.x;
-            xs[u] = i < V ? r.value(i) : -INFINITY;
+    if (a.parts > 0) {
+        for (int p = tid; p < a.parts; p += blockDim.x) {
+            const float ob = a.part_best[(size_t)row * a.parts + p];
+            const int oi = a.part_idx[(size_t)row * a.parts + p];
+            if (better(ob, oi, best, best_i)) { best = ob; best_i = oi; }
         }
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int i = i0 + u * blockDim.x;
-            if (i < V && (best_i == INT_MAX || xs[u] > best)) { best = xs[u]; best_i = i; }
-        }
+    } else {
+        scan_max(r, 0, V, tid, blockDim.x, best, best_i);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ob = __shfl_xor_sync(0xffffffffu, best, o);
         const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-        if (ob > best || (ob == best && oi < best_i)) { best = ob; best_i = oi; }
+        if (better(ob, oi, best, best_i)) { best = ob; best_i = oi; }
     }
     if ((tid & 31) == 0) { sh.fred[tid >> 5] = best; sh.ired[tid >> 5] = best_i; }
     __syncthreads();
@@ -204,7 +260,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(SampleArgs a) {
         for (int o = 16; o > 0; o >>= 1) {
             const float ob = __shfl_xor_sync(0xffffffffu, best, o);
             const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (ob > best || (ob == best && oi < best_i)) { best = ob; best_i = oi; }
+            if (better(ob, oi, best, best_i)) { best = ob; best_i = oi; }
         }
         if (tid == 0) { sh.fred[32] = best; sh.ired[32] = best_i; }
     }
@@ -287,6 +343,8 @@ extern "C" int tb_sample(const SampleArgs* args, cudaStream_t stream) {
     SampleArgs a = *args;
     TB_REQUIRE(a.B > 0 && a.V > 0 && a.ld >= a.V, "sample: bad sizes (B=%d V=%d ld=%d)", a.B, a.V, a.ld);
     TB_REQUIRE(!a.seen || a.seen_words * 32 >= a.V, "sample: the seen-bitmap is shorter than the vocabulary");
+    TB_REQUIRE(a.parts >= 0 && (a.parts == 0 || (a.part_best && a.part_idx)), "sample: parts without their scratch");
+    if (a.parts > 0) tb_launch(sample_max_kernel, dim3(a.B, a.parts), MAX_THREADS, 0, stream, a);
     tb_launch(sample_kernel, a.B, SAMPLE_THREADS, 0, stream, a);
     TB_CHECK_LAUNCH("sample");
     return 0;

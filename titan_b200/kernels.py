@@ -55,7 +55,8 @@ class SampleArgs(Structure):
     _fields_ = [("logits", c_void_p), ("ld", c_int), ("V", c_int), ("B", c_int), ("slot_of_row", c_void_p),
                 ("temperature", c_void_p), ("top_k", c_void_p), ("top_p", c_void_p), ("penalty", c_void_p),
                 ("seed", c_void_p), ("sequence_id", c_void_p), ("sample_step", c_void_p),
-                ("last_token", c_void_p), ("seen", c_void_p), ("seen_words", c_int), ("out", c_void_p)]
+                ("last_token", c_void_p), ("seen", c_void_p), ("seen_words", c_int), ("out", c_void_p),
+                ("part_best", c_void_p), ("part_idx", c_void_p), ("parts", c_int)]
 
 
 _lib = None

@@ -17,12 +17,16 @@ from .params import SamplerParams
 
 
 class DeviceSampler:
-    def __init__(self, slot_state, max_slots: int, vocab_size: int, device):
+    def __init__(self, slot_state, max_slots: int, vocab_size: int, device, parts: Optional[int] = None):
         self.state, self.V, self.device = slot_state, vocab_size, device
         f = lambda dt, v=0: torch.full((max_slots,), v, dtype=dt, device=device)
         self.temperature, self.top_p = f(torch.float32), f(torch.float32, 1.0)
         self.top_k, self.penalty = f(torch.int32), f(torch.float32, 1.0)
         self.max_slots = max_slots
+        # several blocks per row look for the maximum when a row is long enough to keep them busy
+        self.parts = (32 if vocab_size >= 32 * 1024 else 0) if parts is None else int(parts)
+        self.part_best = torch.empty((max_slots, max(self.parts, 1)), dtype=torch.float32, device=device)
+        self.part_idx = torch.empty((max_slots, max(self.parts, 1)), dtype=torch.int32, device=device)
         self.seen: Optional[torch.Tensor] = None          # [max_slots, ceil(V/32)] bits of context tokens
         self._penalised = set()
 
@@ -67,5 +71,7 @@ class DeviceSampler:
         a.seen = None if self.seen is None else self.seen.data_ptr()
         a.seen_words = 0 if self.seen is None else self.seen.shape[1]
         a.out = out.data_ptr()
+        a.parts = self.parts if B <= self.max_slots else 0
+        a.part_best, a.part_idx = self.part_best.data_ptr(), self.part_idx.data_ptr()
         K.sample(a, stream)
         return out
