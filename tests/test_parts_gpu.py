@@ -231,3 +231,152 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(dtype):
         for i in range(2):
             assert rel_l2(torch.cat(got[i]).cpu(), want[i]) < TOL[dtype]
             e.free_slot(slots[i])
+
+
+# --------------------------------------------------------------------------- #
+# A toy feed-forward with routing and a toy position encoding, again defined here only.
+# --------------------------------------------------------------------------- #
+def more_toy_parts():
+    from titan_b200.parts import FEED_FORWARDS, POSITIONS, FeedForward, PositionEncoding
+    from titan_b200.weights import WeightSpec
+
+    class PickOne(FeedForward):
+        """Each token goes to the ONE expert whose router score (float32) is largest; an expert is
+        down(relu(up(h))).  Which expert a token takes depends on the token alone, so a batch changes nothing."""
+
+        def __init__(self, spec):
+            self.spec, self.experts = spec, spec.option("experts", 2)
+
+        def weight_specs(self, prefix):
+            s, p = self.spec, prefix + self.spec.prefix
+            specs = [WeightSpec(p + "router.weight", (self.experts, s.hidden_size), role="vector")]       # kept in float32
+            for e in range(self.experts):
+                specs += [WeightSpec(p + f"experts.{e}.up.weight", (s.intermediate_size, s.hidden_size)),
+                          WeightSpec(p + f"experts.{e}.down.weight", (s.hidden_size, s.intermediate_size))]
+            return specs
+
+        def bind(self, get):
+            p = self.spec.prefix
+            self.router = get(p + "router.weight")
+            self.up = [get(p + f"experts.{e}.up.weight") for e in range(self.experts)]
+            self.down = [get(p + f"experts.{e}.down.weight") for e in range(self.experts)]
+
+        def forward(self, h, ctx, out):
+            choice = (h.float() @ self.router.t()).argmax(dim=1)          # router logits in float32
+            for e in range(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    act = torch.relu(h[rows].float() @ self.up[e].float().t()).to(h.dtype)
+                    out[rows] += act.float() @ self.down[e].float().t()
+    FEED_FORWARDS.register("toy_pick_one", PickOne)
+
+    class StretchedRotary(PositionEncoding):
+        """The rotary angles of position p / stretch: the attention mixer only asks for ``rotary_dim`` and a table."""
+
+        def __init__(self, spec):
+            self.spec = spec
+
+        @property
+        def rotary_dim(self):
+            return self.spec.rotary_dim
+
+        def tables(self, device):
+            k = torch.arange(self.spec.rotary_dim // 2, dtype=torch.float64)
+            inv = torch.tensor(self.spec.theta, dtype=torch.float64) ** (-2.0 * k / self.spec.rotary_dim) / 4.0
+            return {"inv_freq": inv.to(torch.float32).to(device)}
+    POSITIONS.register("toy_stretched_rope", StretchedRotary)
+
+
+class ToyRoutedConfig:
+    def __init__(self, d):
+        self.d = d
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d)
+
+    def to_dict(self):
+        return dict(self.d)
+
+    def to_model_spec(self):
+        from titan_b200.config import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec
+        d, H = self.d, self.d["width"]
+        layers = []
+        for i in range(d["depth"]):
+            mixer = MixerSpec("attention", H, 3, 1, 32, position=PositionSpec("toy_stretched_rope", 32, 50.0), prefix="attn.")
+            ff = (FeedForwardSpec("toy_pick_one", H, d["ff"], prefix="moe.", extra=(("experts", d["experts"]),)) if i % 2 == 0
+                  else FeedForwardSpec("gated_mlp", H, d["ff"], prefix="ff."))
+            layers.append(LayerSpec(i, "pre_norm", mixer, ff, NormSpec("rmsnorm", H, 1e-6, "n1.weight"),
+                                    NormSpec("rmsnorm", H, 1e-6, "n2.weight"), f"blocks.{i}."))
+        return ModelSpec("ToyRoutedForCausalLM", H, d["vocab"], tuple(layers), tuple(range(d["depth"])),
+                         NormSpec("rmsnorm", H, 1e-6, "final.weight"), embedding="embed.weight", lm_head="head.weight")
+
+
+def toy_routed_plain(d, w, tokens, margins):
+    """Logits; the gap between the two best router scores of every decision is appended to ``margins``."""
+    x = w["embed.weight"][torch.tensor(tokens)]
+    T, pos = len(tokens), torch.arange(len(tokens)) / 4.0
+    for i in range(d["depth"]):
+        p = f"blocks.{i}."
+        h = P.rms_norm(x, w[p + "n1.weight"], 1e-6)
+        q = P.rope_neox(P.linear(h, w[p + "attn.q_proj.weight"]).view(T, 3, 32), pos, 50.0)
+        k = P.rope_neox(P.linear(h, w[p + "attn.k_proj.weight"]).view(T, 1, 32), pos, 50.0)
+        v = P.linear(h, w[p + "attn.v_proj.weight"]).view(T, 1, 32)
+        x = x + P.linear(P.causal_attention(q, k, v).reshape(T, 96), w[p + "attn.o_proj.weight"])
+        h = P.rms_norm(x, w[p + "n2.weight"], 1e-6)
+        if i % 2 == 0:
+            scores = P.linear(h, w[p + "moe.router.weight"])
+            choice = scores.argmax(dim=1)
+            top2 = scores.topk(2, dim=1).values
+            margins.extend((top2[:, 0] - top2[:, 1]).tolist())
+            rows = []
+            for t in range(T):
+                e = int(choice[t])
+                act = torch.relu(P.linear(h[t:t + 1], w[p + f"moe.experts.{e}.up.weight"]))
+                rows.append(P.linear(act, w[p + f"moe.experts.{e}.down.weight"])[0])
+            x = x + torch.stack(rows)
+        else:
+            x = x + P.mlp_part({k_.replace(p + "ff.", "mlp."): v_ for k_, v_ in w.items() if k_.startswith(p + "ff.")}, "", h)
+    return P.linear(P.rms_norm(x, w["final.weight"], 1e-6), w["head.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(dtype):
+    """Registered from outside, built by the registries, stepped by the engine (prompts of unequal
+    lengths, then single tokens): no file of the framework knows either part."""
+    from titan_b200 import Engine, StepEntry, register_architecture
+    from titan_b200.parts import declare_weights
+    more_toy_parts()
+    register_architecture("ToyRoutedForCausalLM", ToyRoutedConfig)
+    d = {"architectures": ["ToyRoutedForCausalLM"], "width": 40, "depth": 3, "ff": 56, "vocab": 90, "experts": 3}
+    cfg = ToyRoutedConfig(d)
+    reqs = [random_tokens(41, 90, 5), random_tokens(17, 90, 6)]
+    # A routing decision is discrete: two scores that nearly tie would flip under bfloat16 rounding and
+    # say nothing about the parts.  So take the first seed whose decisions are all clear in float32.
+    for seed in range(9, 60):
+        g = torch.Generator().manual_seed(seed)
+        w = {}
+        for s in declare_weights(cfg.to_model_spec()):
+            std = 2.0 if "router" in s.name else (0.1 if s.role == "vector" else 0.12)
+            t = torch.randn(s.shape, generator=g) * std + (1.0 if s.role == "vector" and "router" not in s.name else 0.0)
+            w[s.name] = t.to(torch.bfloat16)
+        w32 = {k: v.float() for k, v in w.items()}
+        margins = []
+        want = [toy_routed_plain(d, w32, r, margins) for r in reqs]
+        if min(margins) > 0.5:
+            break
+    else:
+        pytest.fail("no seed gave clear routing decisions")
+    e = Engine.from_tensors(cfg, w, dtype=dtype, max_tokens=512, max_slots=3)
+    slots = [e.alloc_slot(), e.alloc_slot()]
+    out = e.step([StepEntry(slots[0], reqs[0][:33], list(range(33))), StepEntry(slots[1], reqs[1][:9], list(range(9)))])
+    got, at = [[out[:33]], [out[33:]]], [33, 9]
+    while any(a < len(r) for a, r in zip(at, reqs)):
+        live = [i for i in range(2) if at[i] < len(reqs[i])]
+        out = e.step([StepEntry(slots[i], [reqs[i][at[i]]], [0]) for i in live])
+        for k, i in enumerate(live):
+            got[i].append(out[k:k + 1])
+            at[i] += 1
+    for i in range(2):
+        assert rel_l2(torch.cat(got[i]).cpu(), want[i]) < TOL[dtype]
+        e.free_slot(slots[i])
