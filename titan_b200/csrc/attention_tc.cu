@@ -2,13 +2,14 @@
 //
 // One CTA per (sequence, query head, block of 128 queries).  Per tile of 64 keys:
 //     S = Q . K^T        tcgen05.mma, A = Q and B = K both K-major in shared memory, S in tensor memory
-//     P = 2^(S*c - m)    a softmax thread reads its query row of S with tcgen05.ld and writes P (bfloat16)
-//                        into shared memory in the 128-byte-swizzled K-major layout
-//     O += P . V         tcgen05.mma, A = P (K-major), B = V as MN-major operand (V's rows are keys, its
-//                        contiguous dimension is the output dimension), O accumulated in tensor memory
+//     P = 2^(S*c - m)    a softmax thread reads its query row of S with tcgen05.ld and writes P (pairs of
+//                        bfloat16) back over the first half of the same columns with tcgen05.st
+//     O += P . V         tcgen05.mma with A = P from tensor memory, B = V as MN-major operand from shared
+//                        memory (V's rows are keys, its contiguous dimension is the output dimension),
+//                        O accumulated in tensor memory
 // The eight softmax warps form two groups of four (a thread = a query row); group g takes the key tiles
-// j with j % 2 == g as an online softmax of its own: its own P buffer, running maximum and sum, and
-// its own O in tensor memory.  A row's maximum is raised only when a tile exceeds it by more than
+// j with j % 2 == g as an online softmax of its own: its own running maximum and sum, and its own O in
+// tensor memory.  A row's maximum is raised only when a tile exceeds it by more than
 // 2^RESCALE_LOG2 (P stays below that bound, which bfloat16 and the float32 sum hold easily); only then is
 // the group's O rescaled in tensor memory, which after the first tiles is rare.  At the end the groups'
 // (m, l, O) are merged like the parts of a split-key decode.  So a thread reads each score once,
@@ -16,11 +17,13 @@
 // slack before its next scores are needed.
 // Warp 0 loads Q once and K and V tiles through TMA (rings of four each: K_j is free as soon as S_j is
 // done and is wanted four tiles ahead, V_j only after P.V).  Warp 1 allocates tensor memory and issues
-// the S MMAs into four S buffers, up to four tiles ahead; warp 10 issues the P.V MMAs.  The issue is
+// the S MMAs into four S buffers, up to four tiles ahead (a buffer is free again when the P.V of the tile
+// it held is complete); warp 10 issues the P.V MMAs.  The issue is
 // split because the issuing thread is the narrow place: a tcgen05.mma costs it tens of cycles however
 // small the product.  Warps 2..9 are the softmax groups.  The step's own [T][Q | K | V] rows are the
-// only source (every sequence starts at position 0); the cache is not read.
-// Tensor memory: S 4 x 64 columns, O 2 x 128 columns (all 512).
+// only source (every sequence starts at position 0); the cache is not read.  The grid runs over heads
+// fastest, so the heaviest query blocks of all heads start first and the lightest make the tail.
+// Tensor memory: S (then P) 4 x 64 columns, O 2 x 128 columns (all 512).
 //
 // All waits are bounded (tma.cuh); tb_attn_tc_error() reads the error word.  Built with -DTB_TC_TIMING
 // (TITAN_B200_NVCC_FLAGS), one warp of the first CTA adds up clock64() per phase of the softmax loop
@@ -54,7 +57,6 @@ constexpr uint32_t Q_BYTES = BQ * HD * 2;              // two boxes of 128 rows 
 constexpr uint32_t Q_BOX = BQ * 128;
 constexpr uint32_t KV_TILE = BKEY * HD * 2;            // one K or V tile: two boxes of 64 rows x 64 columns
 constexpr uint32_t KV_BOX = BKEY * 128;
-constexpr uint32_t P_BYTES = BQ * BKEY * 2;            // one box of 128 rows x 64 keys
 constexpr int KV_STAGES = 4;                           // K and V tiles in flight: the loads run well ahead of P.V
 
 struct TcAttnArgs {
@@ -101,8 +103,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_smem = base;                                       // 32 KB
     uint8_t* kv_smem = base + Q_BYTES;                            // KV_STAGES x (K 16 KB + V 16 KB)
-    uint8_t* p_smem = kv_smem + KV_STAGES * 2 * KV_TILE;          // 2 x 16 KB, one per group
-    uint64_t* bars = (uint64_t*)(p_smem + 2 * P_BYTES);
+    uint64_t* bars = (uint64_t*)(kv_smem + KV_STAGES * 2 * KV_TILE);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;             // [KV_STAGES]  K and V have rings of their own: K_j is free as soon as
     uint64_t* k_empty = bars + 5;            // [KV_STAGES]  S_j is done, long before V_j, and is wanted four tiles ahead
@@ -111,13 +112,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     uint64_t* s_full = bars + 17;            // [4] S of tile j is in tensor-memory buffer j % 4
     uint64_t* p_full = bars + 21;            // [2] the group's four warps have written P
     uint64_t* o_done = bars + 23;            // [2] the P.V MMAs issued so far into the group's O are complete
-    uint64_t* s_free = bars + 25;            // [4] the group's four warps have read S buffer j % 4
+    uint64_t* s_free = bars + 25;            // [4] P.V of the tile whose S and P lay in buffer j % 4 is complete
     uint32_t* tmem_slot = (uint32_t*)(bars + 29);
     float* ml_sh = (float*)(bars + 30);      // [2 groups][m, l][128 rows]
 
     pdl_launch_dependents();
     pdl_wait();
-    int rem = blockIdx.x, seq = -1, blk = 0, tok0 = 0, n = 0;
+#ifdef TB_TC_TIMING
+    const long long t_entry = clock64();
+#endif
+    // blockIdx.y: which sequence and which block of 128 queries (a sequence's blocks from the heaviest,
+    // the last, down); blockIdx.x, which runs fastest in the dispatch order: the head
+    int rem = blockIdx.y, seq = -1, blk = 0, tok0 = 0, n = 0;
     for (int s = 0; s < a.B; ++s) {
         const int t0 = a.q_start[s], ns = a.q_start[s + 1] - t0, nb = (ns + BQ - 1) / BQ;
         if (rem < nb) { seq = s; blk = nb - 1 - rem; tok0 = t0; n = ns; break; }
@@ -125,7 +131,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     }
     if (seq < 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = blockIdx.y, kh = h / (a.nh / a.nkv);
+    const int h = blockIdx.x, kh = h / (a.nh / a.nkv);
     const int r0 = blk * BQ;
     const int last_key = min(n - 1, r0 + BQ - 1);
     const int first_key = a.window > 0 ? max(0, r0 - a.window + 1) : 0;
@@ -135,7 +141,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         mbar_init(q_full, 1);
         for (int s = 0; s < KV_STAGES; ++s) {
             mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1);
-            mbar_init(s_full + s, 1); mbar_init(s_free + s, 4);
+            mbar_init(s_full + s, 1); mbar_init(s_free + s, 1);
         }
         for (int s = 0; s < 2; ++s) { mbar_init(p_full + s, 4); mbar_init(o_done + s, 1); }
         mbar_fence_init();
@@ -183,10 +189,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         if (lane == 0) {
             const uint64_t q_desc = desc_k_major(smem_u32(q_smem));
             wait(q_full, 0, 3);
+#ifdef TB_TC_TIMING
+            const bool timing = blockIdx.x == 0 && blockIdx.y == 0;
+            long long tprev = clock64();
+#endif
             for (int i = 0; i < n_tiles; ++i) {
                 const int s = i % KV_STAGES;
+                TCLK(8);
                 if (i >= 4) wait(s_free + (i & 3), ((i >> 2) - 1) & 1, 9);
+                TCLK(9);
                 wait(k_full + s, (i / KV_STAGES) & 1, 2);
+                TCLK(10);
                 tc_fence_after();
                 const uint64_t k_desc = desc_k_major(smem_u32(kv_smem + s * 2 * KV_TILE));
                 const uint32_t d = tmem_s + (i & 3) * BKEY;
@@ -201,20 +214,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     } else if (warp == 10) {
         // ---- P.V issuer: O_g += P_j . V_j for the group g = j % 2
         if (lane == 0) {
-            const uint64_t p_desc = desc_k_major(smem_u32(p_smem));
+#ifdef TB_TC_TIMING
+            const bool timing = blockIdx.x == 0 && blockIdx.y == 0;
+            long long tprev = clock64();
+#endif
             for (int j = 0; j < n_tiles; ++j) {
                 const int g = j & 1, s = j % KV_STAGES;
+                TCLK(11);
                 wait(v_full + s, (j / KV_STAGES) & 1, 5);
+                TCLK(12);
                 wait(p_full + g, (j >> 1) & 1, 4);          // the group has rescaled O if it had to and written P_j
+                TCLK(13);
                 tc_fence_after();
                 const uint64_t v_desc = desc_mn_major(smem_u32(kv_smem + s * 2 * KV_TILE + KV_TILE));
-                const uint64_t pd = p_desc + (uint64_t)((g * P_BYTES) >> 4);
+                const uint32_t p_tmem = tmem_s + (j & 3) * BKEY;      // P_j lies over the first half of S_j
                 const uint32_t d = tmem_o + g * HD;
 #pragma unroll
-                for (int ks = 0; ks < BKEY / 16; ++ks)      // 16 keys per step: 32 bytes of a P row, 16 rows of V
-                    tc_mma(d, pd + (uint64_t)((ks * 32) >> 4), v_desc + (uint64_t)((ks * 2048) >> 4), IDESC_PV, (j >= 2 || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < BKEY / 16; ++ks)      // 16 keys per step: 8 columns of P, 16 rows of V
+                    tc_mma_a_tmem(d, p_tmem + ks * 8, v_desc + (uint64_t)((ks * 2048) >> 4), IDESC_PV, (j >= 2 || ks > 0) ? 1u : 0u);
                 tc_commit(v_empty + s);
                 tc_commit(o_done + g);
+                tc_commit(s_free + (j & 3));                // the buffer that held S_j, then P_j
             }
         }
     } else {
@@ -228,6 +248,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #ifdef TB_TC_TIMING
         const bool timing = blockIdx.x == 0 && blockIdx.y == 0 && warp == 2 && lane == 0;
         long long tprev = clock64();
+        if (timing) atomicAdd(&g_tc_clk[14], (unsigned long long)(tprev - t_entry));     // entry to the first tile
 #endif
         for (int j = g; j < n_tiles; j += 2, ++mine) {
             const int key0 = (kt0 + j) * BKEY;
@@ -240,9 +261,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tmem_ld32_nowait(tmem_s + (j & 3) * BKEY + lane_addr, v);
             tmem_ld32_nowait(tmem_s + (j & 3) * BKEY + lane_addr + 32, v + 32);
             tmem_wait_ld<64>(v);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_free + (j & 3));    // the S issuer may overwrite this buffer
             TCLK(2);
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (tile_visible) {
@@ -285,16 +303,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             }
             l_run = l_run * f + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             m_run = m_new;
-            uint8_t* p_row = p_smem + g * P_BYTES + row * 128;
+            // P as bfloat16 pairs over the first 32 columns of this tile's S buffer (this thread's lane: its
+            // scores are all in registers by now): the A operand of P.V, which never touches shared memory
+            uint32_t pk[32];
 #pragma unroll
-            for (int i = 0; i < 64; i += 8) {                // 8 keys = one 16-byte chunk of the row
-                uint4 pk;
-                pk.x = pack_bf16x2(v[i], v[i + 1]); pk.y = pack_bf16x2(v[i + 2], v[i + 3]);
-                pk.z = pack_bf16x2(v[i + 4], v[i + 5]); pk.w = pack_bf16x2(v[i + 6], v[i + 7]);
-                *reinterpret_cast<uint4*>(p_row + (((i >> 3) ^ (row & 7)) << 4)) = pk;
-            }
+            for (int i = 0; i < 32; ++i) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+            tmem_st32_bits(tmem_s + (j & 3) * BKEY + lane_addr, pk);
             TCLK(5);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core's proxy
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + g);
@@ -345,6 +360,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
+#ifdef TB_TC_TIMING
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64) atomicAdd(&g_tc_clk[15], (unsigned long long)(clock64() - t_entry));
+#endif
 }
 
 }  // namespace
@@ -374,7 +392,7 @@ extern "C" int tb_attn_prefill_tc(const AttnArgs* args, int all_fresh, cudaStrea
     p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
     p.nh = a.nh; p.nkv = a.nkv; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
     p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd;
-    constexpr size_t smem = 1024 + Q_BYTES + KV_STAGES * 2 * KV_TILE + 2 * P_BYTES + 256 + 4 * 128 * sizeof(float);
+    constexpr size_t smem = 1024 + Q_BYTES + KV_STAGES * 2 * KV_TILE + 256 + 4 * 128 * sizeof(float);
     static_assert(KV_STAGES == 4, "the second kernel's barrier layout and S buffers assume four stages");
     static bool configured = false;
     if (!configured) {
@@ -383,8 +401,8 @@ extern "C" int tb_attn_prefill_tc(const AttnArgs* args, int all_fresh, cudaStrea
         configured = true;
     }
     const int blocks = (a.batch.T + BQ - 1) / BQ + a.batch.B;      // upper bound on sum over sequences of ceil(n / 128)
-    TB_REQUIRE(a.nh <= 65535, "attn_prefill_tc: too many heads");
-    tb_launch(attn_prefill_tc_kernel, dim3(blocks, a.nh), THREADS, smem, stream, q_map, kv_map, p);
+    TB_REQUIRE(blocks <= 65535, "attn_prefill_tc: too many query blocks (%d)", blocks);
+    tb_launch(attn_prefill_tc_kernel, dim3(a.nh, blocks), THREADS, smem, stream, q_map, kv_map, p);      // heads fastest: the heaviest blocks of all heads start first
     TB_CHECK_LAUNCH("attn_prefill_tc");
     return 0;
 }
