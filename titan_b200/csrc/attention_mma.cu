@@ -268,7 +268,7 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, PreArgs a) 
     pdl_launch_dependents();
     pdl_wait();
     // which sequence and which block of it (blocks are numbered from the heaviest)
-    int rem = blockIdx.x, seq = -1, blk = 0, tok0 = 0, n = 0;
+    int rem = blockIdx.y, seq = -1, blk = 0, tok0 = 0, n = 0;       // heads run fastest: the heaviest blocks of all heads start first
     for (int s = 0; s < a.B; ++s) {
         const int t0 = a.q_start[s], ns = a.q_start[s + 1] - t0, nb = (ns + 63) >> 6;
         if (rem < nb) { seq = s; blk = nb - 1 - rem; tok0 = t0; n = ns; break; }
@@ -276,7 +276,7 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, PreArgs a) 
     }
     if (seq < 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = blockIdx.y, kh = h / (a.nh / a.nkv);
+    const int h = blockIdx.x, kh = h / (a.nh / a.nkv);
     const int r0 = blk * 64;                                         // first query position of the block
     const int last_key = min(n - 1, r0 + 63);
     const int first_key = a.window > 0 ? max(0, r0 - a.window + 1) : 0;
@@ -510,8 +510,8 @@ extern "C" int tb_attn_prefill_mma(const AttnArgs* args, int all_fresh, cudaStre
     p.nh = a.nh; p.nkv = a.nkv; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
     p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd;
     const int blocks = (a.batch.T + 63) / 64 + a.batch.B;          // upper bound on sum over sequences of ceil(n / 64)
-    TB_REQUIRE(a.nh <= 65535, "attn_prefill_mma: too many heads");
-    dim3 grid(blocks, a.nh);
+    TB_REQUIRE(blocks <= 65535, "attn_prefill_mma: too many query blocks (%d)", blocks);
+    dim3 grid(a.nh, blocks);
     const int rc = a.hd == 128 ? launch_prefill<128>(map, p, grid, stream) : launch_prefill<64>(map, p, grid, stream);
     if (rc) return rc;
     TB_CHECK_LAUNCH("attn_prefill_mma");

@@ -17,10 +17,12 @@
 // slack before its next scores are needed.
 // Warp 0 loads Q once and K and V tiles through TMA (rings of four each: K_j is free as soon as S_j is
 // done and is wanted four tiles ahead, V_j only after P.V).  Warp 1 allocates tensor memory and issues
-// the S MMAs into four S buffers, up to four tiles ahead (a buffer is free again when the P.V of the tile
-// it held is complete); warp 10 issues the P.V MMAs.  The issue is
-// split because the issuing thread is the narrow place: a tcgen05.mma costs it tens of cycles however
-// small the product.  Warps 2..9 are the softmax groups.  The step's own [T][Q | K | V] rows are the
+// the S MMAs of the even tiles, warp 11 those of the odd tiles, into four S buffers, up to four tiles
+// ahead (a buffer is free again when the P.V of the tile it held is complete); warp 10 issues the P.V
+// MMAs.  The issue is split three ways because the issuing thread is the narrow place: a tcgen05.mma
+// costs it tens of cycles however small the product.  One tcgen05.commit per event: "S_j done" serves the
+// softmax group and the K ring, "P.V_j done" the V ring, the S issuer and (for a rescale, and at the
+// end) the group.  Warps 2..9 are the softmax groups.  The step's own [T][Q | K | V] rows are the
 // only source (every sequence starts at position 0); the cache is not read.  The grid runs over heads
 // fastest, so the heaviest query blocks of all heads start first and the lightest make the tail.
 // Tensor memory: S (then P) 4 x 64 columns, O 2 x 128 columns (all 512).
@@ -52,7 +54,7 @@ __device__ unsigned long long g_tc_clk[16];
 #endif
 
 constexpr int HD = 128, BQ = 128, BKEY = 64;
-constexpr int THREADS = 352;                           // producer, S issuer, eight softmax warps, P.V issuer
+constexpr int THREADS = 384;                           // producer, S issuer (even tiles), eight softmax warps, P.V issuer, S issuer (odd tiles)
 constexpr uint32_t Q_BYTES = BQ * HD * 2;              // two boxes of 128 rows x 64 columns
 constexpr uint32_t Q_BOX = BQ * 128;
 constexpr uint32_t KV_TILE = BKEY * HD * 2;            // one K or V tile: two boxes of 64 rows x 64 columns
@@ -89,6 +91,11 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&p);
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {      // one instruction on sm_100
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
 __device__ __forceinline__ float ex2(float x) {          // 2^x, one instruction; -inf gives 0
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -105,16 +112,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     uint8_t* kv_smem = base + Q_BYTES;                            // KV_STAGES x (K 16 KB + V 16 KB)
     uint64_t* bars = (uint64_t*)(kv_smem + KV_STAGES * 2 * KV_TILE);
     uint64_t* q_full = bars;
-    uint64_t* k_full = bars + 1;             // [KV_STAGES]  K and V have rings of their own: K_j is free as soon as
-    uint64_t* k_empty = bars + 5;            // [KV_STAGES]  S_j is done, long before V_j, and is wanted four tiles ahead
-    uint64_t* v_full = bars + 9;             // [KV_STAGES]
-    uint64_t* v_empty = bars + 13;           // [KV_STAGES]
-    uint64_t* s_full = bars + 17;            // [4] S of tile j is in tensor-memory buffer j % 4
-    uint64_t* p_full = bars + 21;            // [2] the group's four warps have written P
-    uint64_t* o_done = bars + 23;            // [2] the P.V MMAs issued so far into the group's O are complete
-    uint64_t* s_free = bars + 25;            // [4] P.V of the tile whose S and P lay in buffer j % 4 is complete
-    uint32_t* tmem_slot = (uint32_t*)(bars + 29);
-    float* ml_sh = (float*)(bars + 30);      // [2 groups][m, l][128 rows]
+    uint64_t* k_full = bars + 1;             // [4] K and V have rings of their own: K_j is free as soon as S_j is
+    uint64_t* v_full = bars + 5;             // [4] done, long before V_j, and is wanted four tiles ahead
+    uint64_t* s_done = bars + 9;             // [4] S of tile j is in tensor-memory buffer j % 4 (and K stage j % 4 is free)
+    uint64_t* pv_done = bars + 13;           // [4] P.V of tile j is complete: V stage j % 4 and S buffer j % 4 are free, O holds it
+    uint64_t* p_full = bars + 17;            // [2] the group's four warps have written P
+    uint32_t* tmem_slot = (uint32_t*)(bars + 19);
+    float* ml_sh = (float*)(bars + 20);      // [2 groups][m, l][128 rows]
 
     pdl_launch_dependents();
     pdl_wait();
@@ -140,10 +144,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < KV_STAGES; ++s) {
-            mbar_init(k_full + s, 1); mbar_init(k_empty + s, 1); mbar_init(v_full + s, 1); mbar_init(v_empty + s, 1);
-            mbar_init(s_full + s, 1); mbar_init(s_free + s, 1);
+            mbar_init(k_full + s, 1); mbar_init(v_full + s, 1); mbar_init(s_done + s, 1); mbar_init(pv_done + s, 1);
         }
-        for (int s = 0; s < 2; ++s) { mbar_init(p_full + s, 4); mbar_init(o_done + s, 1); }
+        for (int s = 0; s < 2; ++s) mbar_init(p_full + s, 4);
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(tmem_slot, 512);
@@ -162,7 +165,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             // K and V tiles as their rings allow, whichever is free first (bounded polling)
             int ki = 0, vi = 0;
             for (uint32_t spin = 0; (ki < n_tiles || vi < n_tiles) && spin < (tbtma::WAIT_LIMIT << 4); ++spin) {
-                if (ki < n_tiles && (ki < KV_STAGES || tbtma::mbar_test(k_empty + ki % KV_STAGES, (ki / KV_STAGES - 1) & 1))) {
+                if (ki < n_tiles && (ki < KV_STAGES || tbtma::mbar_test(s_done + ki % KV_STAGES, (ki / KV_STAGES - 1) & 1))) {
                     const int s = ki % KV_STAGES, row = tok0 + (kt0 + ki) * BKEY;
                     uint8_t* kd = kv_smem + s * 2 * KV_TILE;
                     mbar_expect_tx(k_full + s, KV_TILE);
@@ -170,7 +173,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     tma_load_2d(kd + KV_BOX, &kv_map, k_full + s, a.k_col0 + kh * HD + 64, row);
                     ++ki; spin = 0;
                 }
-                if (vi < n_tiles && (vi < KV_STAGES || tbtma::mbar_test(v_empty + vi % KV_STAGES, (vi / KV_STAGES - 1) & 1))) {
+                if (vi < n_tiles && (vi < KV_STAGES || tbtma::mbar_test(pv_done + vi % KV_STAGES, (vi / KV_STAGES - 1) & 1))) {
                     const int s = vi % KV_STAGES, row = tok0 + (kt0 + vi) * BKEY;
                     uint8_t* vd = kv_smem + s * 2 * KV_TILE + KV_TILE;
                     mbar_expect_tx(v_full + s, KV_TILE);
@@ -181,22 +184,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             }
             if (ki < n_tiles || vi < n_tiles) atomicCAS(&g_attn_tc_error, 0u, 1u);
         }
-    } else if (warp == 1) {
-        // ---- S issuer: S_i = Q . K_i^T into S buffer i % 4, up to four tiles ahead of the softmax.  The
-        // issuing thread is the narrow place of this kernel (a tcgen05.mma costs it tens of cycles however
-        // small the product), so S and P.V are issued by different warps and the descriptors of a tile
-        // differ from a base by constants.
+    } else if (warp == 1 || warp == 11) {
+        // ---- S issuers (warp 1: even tiles, warp 11: odd tiles): S_i = Q . K_i^T into S buffer i % 4, up to
+        // four tiles ahead of the softmax; a tile's descriptors differ from a base by constants.
         if (lane == 0) {
             const uint64_t q_desc = desc_k_major(smem_u32(q_smem));
             wait(q_full, 0, 3);
 #ifdef TB_TC_TIMING
-            const bool timing = blockIdx.x == 0 && blockIdx.y == 0;
+            const bool timing = blockIdx.x == 0 && blockIdx.y == 0 && warp == 1;
             long long tprev = clock64();
 #endif
-            for (int i = 0; i < n_tiles; ++i) {
+            for (int i = warp == 1 ? 0 : 1; i < n_tiles; i += 2) {
                 const int s = i % KV_STAGES;
                 TCLK(8);
-                if (i >= 4) wait(s_free + (i & 3), ((i >> 2) - 1) & 1, 9);
+                if (i >= 4) wait(pv_done + (i & 3), ((i >> 2) - 1) & 1, 9);       // the buffer held S, then P, of tile i - 4
                 TCLK(9);
                 wait(k_full + s, (i / KV_STAGES) & 1, 2);
                 TCLK(10);
@@ -207,8 +208,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 for (int ks = 0; ks < HD / 16; ++ks)        // 16 dims per step: box ks / 4, 32 bytes per step inside it
                     tc_mma(d, q_desc + (uint64_t)(((ks >> 2) * Q_BOX + (ks & 3) * 32) >> 4),
                            k_desc + (uint64_t)(((ks >> 2) * KV_BOX + (ks & 3) * 32) >> 4), IDESC_S, ks > 0 ? 1u : 0u);
-                tc_commit(s_full + (i & 3));
-                tc_commit(k_empty + s);
+                tc_commit(s_done + (i & 3));                // one arrival for the softmax group and for the K ring
             }
         }
     } else if (warp == 10) {
@@ -232,9 +232,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #pragma unroll
                 for (int ks = 0; ks < BKEY / 16; ++ks)      // 16 keys per step: 8 columns of P, 16 rows of V
                     tc_mma_a_tmem(d, p_tmem + ks * 8, v_desc + (uint64_t)((ks * 2048) >> 4), IDESC_PV, (j >= 2 || ks > 0) ? 1u : 0u);
-                tc_commit(v_empty + s);
-                tc_commit(o_done + g);
-                tc_commit(s_free + (j & 3));                // the buffer that held S_j, then P_j
+                tc_commit(pv_done + (j & 3));               // one arrival for the V ring, the S issuer and the group
             }
         }
     } else {
@@ -254,7 +252,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const int key0 = (kt0 + j) * BKEY;
             const bool tile_visible = key0 + BKEY - 1 <= qpos && key0 >= lo;       // no mask needed in this tile
             TCLK(0);
-            wait(s_full + (j & 3), (j >> 2) & 1, 6);
+            wait(s_done + (j & 3), (j >> 2) & 1, 6);
             tc_fence_after();
             TCLK(1);
             float v[64];
@@ -263,15 +261,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tmem_wait_ld<64>(v);
             TCLK(2);
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            if (tile_visible) {
+            if (!tile_visible) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
-            } else {
+                for (int i = 0; i < 64; ++i) v[i] = (key0 + i <= qpos && key0 + i >= lo) ? v[i] : -INFINITY;
+            }
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    v[i] = (key0 + i <= qpos && key0 + i >= lo) ? v[i] : -INFINITY;
-                    mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
-                }
+            for (int i = 0; i < 64; i += 8) {               // four chains of three-input maxima
+                mx4[0] = max3(mx4[0], v[i], v[i + 1]); mx4[1] = max3(mx4[1], v[i + 2], v[i + 3]);
+                mx4[2] = max3(mx4[2], v[i + 4], v[i + 5]); mx4[3] = max3(mx4[3], v[i + 6], v[i + 7]);
             }
             const float cand = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
             // Raise the row's maximum only when the tile exceeds it by more than the bound.
@@ -279,19 +276,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const float m_new = raise ? cand : m_run;
             const float f = raise ? ex2(m_run - m_new) : 1.f;
             TCLK(3);
-            // P.V of the group's previous tile must be complete before P is overwritten (and before O is touched).
-            if (mine >= 1) {
-                wait(o_done + g, (mine - 1) & 1, 7);
+            // Only a rescale touches O, and only then must the group's earlier P.V be complete (P itself goes
+            // into this tile's own S buffer).  f = 1 for the rows of the warp that keep their maximum.
+            if (mine >= 1 && __any_sync(0xffffffffu, raise)) {
+                wait(pv_done + ((j - 2) & 3), ((j - 2) >> 2) & 1, 7);
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, raise)) {           // rescale this warp's 32 rows of O (f = 1 where nothing changed)
 #pragma unroll 1
-                    for (int c = 0; c < HD; c += 32) {
-                        float o[32];
-                        tmem_ld32(tmem_o + g * HD + lane_addr + c, o);
+                for (int c = 0; c < HD; c += 32) {
+                    float o[32];
+                    tmem_ld32(tmem_o + g * HD + lane_addr + c, o);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] *= f;
-                        tmem_st32(tmem_o + g * HD + lane_addr + c, o);
-                    }
+                    for (int i = 0; i < 32; ++i) o[i] *= f;
+                    tmem_st32(tmem_o + g * HD + lane_addr + c, o);
                 }
             }
             TCLK(4);
@@ -316,7 +312,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             TCLK(6);
         }
         if (mine >= 1) {                                         // the group's last P.V
-            wait(o_done + g, (mine - 1) & 1, 8);
+            const int last = g + 2 * (mine - 1);
+            wait(pv_done + (last & 3), (last >> 2) & 1, 8);
             tc_fence_after();
         }
         // merge the two groups: weights 2^(m_g - M) / L
