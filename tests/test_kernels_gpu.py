@@ -383,8 +383,9 @@ def test_attention_decode_on_tensor_cores(K, nh, nkv, hd, window, ring):
     for chunk in (64, 256, 1024):
         splits = -(-max(lens) // chunk)
         outs = []
-        for fast in (True, False):
-            out = torch.empty(B, Q, dtype=torch.bfloat16, device="cuda")
+        for mode in ("mma", "mma through scratch", "plain"):     # up to 8 splits merge inside a cluster unless told otherwise
+            fast = mode != "plain"
+            out = torch.full((B, Q), float("nan"), dtype=torch.bfloat16, device="cuda")
             scratch = torch.full((B * nh * splits * (hd + 2),), float("nan"), device="cuda")
             d = K.AttnArgs()
             d.q, d.q_stride, d.out, d.out_stride = qb.data_ptr(), Q, out.data_ptr(), Q
@@ -393,13 +394,19 @@ def test_attention_decode_on_tensor_cores(K, nh, nkv, hd, window, ring):
             d.chunk, d.n_splits, d.scratch = chunk, splits, scratch.data_ptr()
             if fast:
                 assert K.attn_decode_mma_accepts(d, torch.bfloat16)
-                K.attn_decode_mma(d, stream())
-                assert K.attn_mma_error() == 0
+                K.set_attn_decode_cluster(mode == "mma")
+                try:
+                    K.attn_decode_mma(d, stream())
+                    assert K.attn_mma_error() == 0
+                finally:
+                    K.set_attn_decode_cluster(True)
             else:
                 K.attn_decode(d, torch.bfloat16, stream())
             outs.append(out.float().cpu())
         assert rel_l2(outs[0], want) < 8e-3, chunk        # P is rounded to bfloat16 before P.V
-        assert rel_l2(outs[0], outs[1]) < 8e-3, chunk
+        assert rel_l2(outs[1], want) < 8e-3, chunk
+        assert rel_l2(outs[0], outs[2]) < 8e-3, chunk
+        assert rel_l2(outs[0], outs[1]) < 1e-5, chunk     # the two merges add the same parts in the same order
     d.chunk = 100
     assert not K.attn_decode_mma_accepts(d, torch.bfloat16)
     d.chunk, d.hd = 64, 96

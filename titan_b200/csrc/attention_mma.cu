@@ -39,6 +39,7 @@ struct DecArgs {
     const int* slot_of_seq; const int* kv_len;
     int nh; int nkv; int window; float scale_log2;   // scale * log2(e)
     int chunk; int n_splits;
+    __nv_bfloat16* out; int out_stride;      // [B][out_stride]: written by the kernel itself when its splits form a cluster
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -61,7 +62,11 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 __device__ __forceinline__ uint32_t swz(int row, int chunk16) { return (uint32_t)(row * 128 + ((chunk16 ^ (row & 7)) << 4)); }
 
 // HD: head size (64 or 128).  WIDE: the group has more than 8 query heads (rows 8..15 of the tile are live).
-template <int HD, bool WIDE>
+// CL: the splits of a (sequence, kv head) are the CTAs of one thread-block cluster (at most 8): each leaves
+// its part (m, l, O) in its own shared memory, and after a cluster barrier every CTA merges a slice of the
+// output rows from all of them through distributed shared memory and writes the result; no scratch
+// memory, no merge kernel.
+template <int HD, bool WIDE, bool CL>
 __global__ void __launch_bounds__(DEC_THREADS)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     constexpr int STAGES = HD == 128 ? 3 : 4;
@@ -78,7 +83,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     pdl_launch_dependents();
     pdl_wait();                                         // lengths, queries and the newest cache row come from earlier kernels
     const int len = a.kv_len[b];
-    if (split * a.chunk >= len) return;                 // uniform over the CTA; the merge skips these splits
+    if (!CL && split * a.chunk >= len) return;          // uniform over the CTA; the merge skips these splits (in a cluster the CTA stays, with no pages, for the barrier)
     const int group = a.nh / a.nkv;
     const int wlo = a.window > 0 ? max(0, len - a.window) : 0;       // first visible key of position len - 1
     const int lo = max(wlo, split * a.chunk), hi = min(len, (split + 1) * a.chunk);
@@ -111,10 +116,13 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
                 }
             }
         }
-        return;
+        if (!CL) return;
     }
 
     // ---------------- compute warps: this warp takes keys 16 * warp .. + 15 of every page
+    constexpr int FIN_OFFSET = 48 * 1024;               // the CTA's part for the cluster merge: [16][HD] sums, [16] maxima, [16] sums of weights
+    float* fin = reinterpret_cast<float*>(base + FIN_OFFSET);
+    if (warp < DEC_WARPS) {
     const int g = lane >> 2, t = lane & 3;
     uint32_t qf[KS][4];
     {
@@ -231,9 +239,34 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
             acc += f * mo[(w * 16 + row) * HD + d];
             L += f * ml[w * 16 + row];
         }
-        float* part = a.scratch + ((size_t)(b * a.nh + kh * group + row) * a.n_splits + split) * (HD + 2);
-        part[d] = acc;
-        if (d == 0) { part[HD] = M * ln2; part[HD + 1] = L; }     // the merge works with natural exponents
+        if (CL) {
+            fin[row * HD + d] = acc;
+            if (d == 0) { fin[16 * HD + row] = M; fin[16 * HD + 16 + row] = L; }
+        } else {
+            float* part = a.scratch + ((size_t)(b * a.nh + kh * group + row) * a.n_splits + split) * (HD + 2);
+            part[d] = acc;
+            if (d == 0) { part[HD] = M * ln2; part[HD + 1] = L; }     // the merge works with natural exponents
+        }
+    }
+    }       // compute warps
+    if (CL) {
+        // every thread of every CTA of the cluster (the producer warp too): parts written -> merged -> may leave
+        tbtma::cluster_sync();
+        const int n = a.n_splits, total = group * HD;
+        const int per = (total + n - 1) / n, first = (int)tbtma::cluster_rank() * per, last = min(total, first + per);
+        for (int idx = first + (int)threadIdx.x; idx < last; idx += DEC_THREADS) {
+            const int row = idx / HD, d = idx % HD;
+            float M = -1e30f;
+            for (int r = 0; r < n; ++r) M = fmaxf(M, tbtma::ld_cluster_f32(tbtma::cluster_addr(fin + 16 * HD + row, r)));
+            float acc = 0.f, L = 0.f;
+            for (int r = 0; r < n; ++r) {               // in the order of the splits
+                const float f = exp2f(tbtma::ld_cluster_f32(tbtma::cluster_addr(fin + 16 * HD + row, r)) - M);
+                acc += f * tbtma::ld_cluster_f32(tbtma::cluster_addr(fin + row * HD + d, r));
+                L += f * tbtma::ld_cluster_f32(tbtma::cluster_addr(fin + 16 * HD + 16 + row, r));
+            }
+            a.out[(size_t)b * a.out_stride + (size_t)(kh * group + row) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        }
+        tbtma::cluster_sync();
     }
 }
 
@@ -410,20 +443,33 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, PreArgs a) 
 
 extern "C" int tb_attn_merge(const AttnArgs* args, int dtype, cudaStream_t stream);
 
-template <int HD, bool WIDE>
+template <int HD, bool WIDE, bool CL>
 static int launch_decode(const CUtensorMap& map, const DecArgs& d, dim3 grid, cudaStream_t stream) {
     constexpr int STAGES = HD == 128 ? 3 : 4;
     constexpr size_t smem = 1024 + (size_t)STAGES * 2 * PAGE * HD * 2 + 2 * STAGES * sizeof(uint64_t);
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // room for several CTAs per SM
+        const cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE, CL>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // room for several CTAs per SM
         TB_REQUIRE(e == cudaSuccess, "attn_decode_mma: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    tb_launch(attn_decode_mma_kernel<HD, WIDE>, grid, DEC_THREADS, smem, stream, map, d);
+    if (CL) {
+        const cudaError_t e = tb_launch_cluster_z(attn_decode_mma_kernel<HD, WIDE, CL>, grid, DEC_THREADS, smem, stream, (int)grid.z, map, d);
+        TB_REQUIRE(e == cudaSuccess, "attn_decode_mma: cluster launch failed: %s", cudaGetErrorString(e));
+    } else {
+        tb_launch(attn_decode_mma_kernel<HD, WIDE, CL>, grid, DEC_THREADS, smem, stream, map, d);
+    }
     return 0;
 }
+template <int HD, bool WIDE>
+static int launch_decode_any(const CUtensorMap& map, const DecArgs& d, dim3 grid, bool cluster, cudaStream_t stream) {
+    return cluster ? launch_decode<HD, WIDE, true>(map, d, grid, stream) : launch_decode<HD, WIDE, false>(map, d, grid, stream);
+}
+
+int g_decode_cluster = 1;
+// The splits of decode attention merge inside a thread-block cluster (1, default, up to 8 splits) or through scratch memory and the merge kernel (0).
+extern "C" void tb_attn_decode_set_cluster(int on) { g_decode_cluster = on ? 1 : 0; }
 
 // 0 if the tensor-core decode kernel takes this problem, else 1 with the reason in tb_last_error().
 extern "C" int tb_attn_decode_mma_check(const AttnArgs* a, int dtype) {
@@ -439,7 +485,9 @@ extern "C" int tb_attn_decode_mma_check(const AttnArgs* a, int dtype) {
 extern "C" int tb_attn_decode_mma(const AttnArgs* args, cudaStream_t stream) {
     const AttnArgs& a = *args;
     if (tb_attn_decode_mma_check(args, TB_BF16)) return 1;
-    TB_REQUIRE(a.batch.B > 0 && a.cache.storage && a.scratch, "attn_decode_mma: needs sequences, a cache and scratch");
+    // up to 8 splits: they form a cluster and merge among themselves; more: parts go to scratch and tb_attn_merge finishes
+    const bool cluster = g_decode_cluster && a.n_splits <= 8 && a.out != nullptr;
+    TB_REQUIRE(a.batch.B > 0 && a.cache.storage && (cluster || a.scratch), "attn_decode_mma: needs sequences, a cache and scratch");
     TB_REQUIRE(a.n_splits > 0 && a.n_splits <= 65535 && a.nkv <= 65535, "attn_decode_mma: bad grid");
     TB_REQUIRE((long long)a.chunk * a.n_splits >= a.batch.max_kv_len, "attn_decode_mma: %d splits of %d keys do not cover %d keys", a.n_splits, a.chunk, a.batch.max_kv_len);
     TB_REQUIRE(a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv, "attn_decode_mma: the cache view does not match the heads");
@@ -452,14 +500,15 @@ extern "C" int tb_attn_decode_mma(const AttnArgs* args, cudaStream_t stream) {
     d.slot_of_seq = a.batch.slot_of_seq; d.kv_len = a.batch.kv_len;
     d.nh = a.nh; d.nkv = a.nkv; d.window = a.window; d.scale_log2 = a.scale * 1.4426950408889634f;
     d.chunk = a.chunk; d.n_splits = a.n_splits;
+    d.out = (__nv_bfloat16*)a.out; d.out_stride = a.out_stride;
     dim3 grid(a.batch.B, a.nkv, a.n_splits);
     const bool wide = a.nh / a.nkv > 8;
     int rc;
-    if (a.hd == 128) rc = wide ? launch_decode<128, true>(map, d, grid, stream) : launch_decode<128, false>(map, d, grid, stream);
-    else rc = wide ? launch_decode<64, true>(map, d, grid, stream) : launch_decode<64, false>(map, d, grid, stream);
+    if (a.hd == 128) rc = wide ? launch_decode_any<128, true>(map, d, grid, cluster, stream) : launch_decode_any<128, false>(map, d, grid, cluster, stream);
+    else rc = wide ? launch_decode_any<64, true>(map, d, grid, cluster, stream) : launch_decode_any<64, false>(map, d, grid, cluster, stream);
     if (rc) return rc;
     TB_CHECK_LAUNCH("attn_decode_mma");
-    return tb_attn_merge(args, TB_BF16, stream);
+    return cluster ? 0 : tb_attn_merge(args, TB_BF16, stream);
 }
 
 // Reads and clears the error word of this file's kernels (0: none).  Synchronises the device.

@@ -204,6 +204,12 @@ def attn_decode_mma(args: AttnArgs, stream: int) -> None:
     _check(lib().tb_attn_decode_mma(byref(args), stream))
 
 
+def set_attn_decode_cluster(on: bool) -> None:
+    """Decode attention with up to 8 splits: merge them inside a thread-block cluster (on by default) or through
+    scratch memory and the merge kernel."""
+    lib().tb_attn_decode_set_cluster(int(bool(on)))
+
+
 def attn_prefill_mma_accepts(args: AttnArgs, dtype: torch.dtype, all_fresh: bool) -> bool:
     return dtype == torch.bfloat16 and lib().tb_attn_prefill_mma_check(byref(args), BF16, int(all_fresh)) == 0
 

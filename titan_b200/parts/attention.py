@@ -46,6 +46,10 @@ def decode_split(lay, kv_heads: int, options, fast: bool):
         places = 2 * int(options.get("sm_count", 148))
         pairs = lay.B * kv_heads
         want = max(1, (3 * places // 4 + pairs // 2) // pairs)
+        # Up to 8 splits merge inside a thread-block cluster (no scratch, no merge kernel), which is worth
+        # fewer CTAs as long as a chunk stays at about a thousand keys (batch 1 and 2 at 8,192 keys).
+        if want > 8 and -(-bound // 8) <= 1024:
+            want = 8
         chunk = max(512, -(-(-(-bound // want)) // 64) * 64)
     # an eager step launches the splits its longest sequence needs; a captured one, whose grid cannot
     # change, launches what the context limit needs (the extra CTAs leave at once)
