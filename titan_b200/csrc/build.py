@@ -1,9 +1,12 @@
-"""Compiles the CUDA sources of this folder for sm_100a into one shared library and loads it.
+"""Compiles the CUDA sources of this folder for sm_100a into two shared libraries and loads them.
 
-The library is built in-tree (``_build/libtitan_b200.so``) by calling nvcc
-directly: one object per source, in parallel, then one link.  A stamp of the
-sources' contents decides whether a build is current, so a fresh checkout
-compiles at its first call and later calls only load.  If the tree cannot be
+``core`` (``_build/libtitan_b200.so``): what every model needs in either dtype (element-wise kernels,
+the CUDA-core matrix product and attention, sampling).  ``tensor``
+(``_build/libtitan_b200_tensor.so``): the tcgen05 / TMA / mma.sync kernels that bfloat16 runs use; it
+is built and loaded when the first of them is asked for, so a float32 run never compiles it.  Each is
+built in-tree by calling nvcc directly: one object per source, in parallel, then one link.  A stamp
+of the sources' contents decides whether a build is current, so a fresh checkout compiles at its
+first call and later calls only load.  If the tree cannot be
 written, the build goes to a per-user folder under the system's temporary
 directory.  Progress is printed to stderr, a line per file and one every few
 seconds while nvcc runs.
@@ -27,21 +30,26 @@ from concurrent.futures import ThreadPoolExecutor
 from typing import List, Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_NAME = "libtitan_b200.so"
+LIBS = {"core": "libtitan_b200.so", "tensor": "libtitan_b200_tensor.so"}
+TENSOR_SOURCES = ("gemm_tc.cu", "attention_mma.cu", "attention_tc.cu", "tma_host.cu", "mma_probe.cu")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fvisibility=default"]
 
-_lib: Optional[ctypes.CDLL] = None
-_lock = threading.Lock()
+_libs = {}
+_lock = threading.RLock()
 
 
 class BuildError(RuntimeError):
     pass
 
 
-def sources() -> List[str]:
-    return sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
+def sources(which: Optional[str] = None) -> List[str]:
+    """The sources of one library ("core", "tensor") or of both (None)."""
+    every = sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
+    if which is None:
+        return every
+    return [f for f in every if (f in TENSOR_SOURCES) == (which == "tensor")]
 
 
 def _headers() -> List[str]:
@@ -62,10 +70,10 @@ def _extra_flags() -> List[str]:
     return os.environ.get("TITAN_B200_NVCC_FLAGS", "").split()
 
 
-def _stamp() -> str:
+def _stamp(which: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + _extra_flags()).encode())
-    for f in sources() + _headers():
+    for f in sources(which) + _headers():
         h.update(f.encode())
         with open(os.path.join(HERE, f), "rb") as fh:
             h.update(fh.read())
@@ -104,17 +112,20 @@ def _run(cmd: List[str], what: str) -> None:
         raise BuildError(f"{what} failed:\n{' '.join(cmd)}\n{p.stdout}")
 
 
-def build(force: bool = False, verbose_ptxas: bool = False) -> str:
-    """Build if the library is missing or stale; return its path."""
+def build(force: bool = False, verbose_ptxas: bool = False, which: Optional[str] = None) -> str:
+    """Build what is missing or stale of one library (or of both, ``which=None``); return the path of the last."""
+    if which is None:
+        build(force, verbose_ptxas, "core")
+        return build(force, verbose_ptxas, "tensor")
     out = build_dir()
-    lib = os.path.join(out, LIB_NAME)
-    stamp_file = os.path.join(out, "stamp.txt")
-    stamp = _stamp()
+    lib = os.path.join(out, LIBS[which])
+    stamp_file = os.path.join(out, f"stamp_{which}.txt")
+    stamp = _stamp(which)
     if not force and os.path.isfile(lib) and os.path.isfile(stamp_file) and open(stamp_file).read().strip() == stamp:
         return lib
     nvcc = find_nvcc()
-    srcs = sources()
-    _say(f"compiling {len(srcs)} CUDA sources for sm_100a into {out} (first call only)")
+    srcs = sources(which)
+    _say(f"compiling {len(srcs)} CUDA sources ({which} kernels) for sm_100a into {out} (first call only)")
     t0 = time.time()
     done = threading.Event()
 
@@ -136,24 +147,26 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> str:
         with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
             objs = list(pool.map(one, srcs))
         tmp = lib + f".{os.getpid()}.tmp"
-        _run([nvcc, *ARCH_FLAGS, "-shared", "-o", tmp, *objs], "linking")
+        _run([nvcc, *ARCH_FLAGS, "-shared", "-o", tmp, *objs], "linking")     # the tensor library's few outside symbols resolve against core at load time
         os.replace(tmp, lib)
         with open(stamp_file, "w") as f:
             f.write(stamp)
     finally:
         done.set()
-    _say(f"built {LIB_NAME} in {time.time() - t0:.0f} s")
+    _say(f"built {LIBS[which]} in {time.time() - t0:.0f} s")
     return lib
 
 
-def load() -> ctypes.CDLL:
-    """The loaded library; builds it first if need be.  Raises if that fails."""
-    global _lib
+def load(which: str = "core") -> ctypes.CDLL:
+    """The loaded library; builds it first if need be.  Raises if that fails.  ``tensor`` loads ``core``
+    first (with global symbols: error reporting, launch settings and the merge kernel live there)."""
     with _lock:
-        if _lib is None:
-            path = build()
+        if which not in _libs:
+            if which == "tensor":
+                load("core")
+            path = build(which=which)
             try:
-                _lib = ctypes.CDLL(path)
+                _libs[which] = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
             except OSError as e:
                 raise BuildError(f"{path} was built but cannot be loaded: {e}") from None
-        return _lib
+        return _libs[which]

@@ -73,24 +73,38 @@ def lib():
         l.tb_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         l.tb_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
         l.tb_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
-        l.tb_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
-        l.tb_gemm_tc_check.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
         l.tb_qk_norm_rope.argtypes = [POINTER(QkArgs), c_int, c_int, c_void_p]
         l.tb_kv_append.argtypes = [c_void_p, c_int, c_int, POINTER(KvView), POINTER(Batch), c_void_p]
         l.tb_attn_prefill.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
         l.tb_attn_decode.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
-        l.tb_attn_decode_mma.argtypes = [POINTER(AttnArgs), c_void_p]
-        l.tb_attn_decode_mma_check.argtypes = [POINTER(AttnArgs), c_int]
-        l.tb_attn_prefill_mma.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
-        l.tb_attn_prefill_mma_check.argtypes = [POINTER(AttnArgs), c_int, c_int]
-        l.tb_attn_prefill_tc.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
-        l.tb_attn_prefill_tc_check.argtypes = [POINTER(AttnArgs), c_int, c_int]
         l.tb_sample.argtypes = [POINTER(SampleArgs), c_void_p]
         l.tb_decode_prepare.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         l.tb_commit_lengths.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         l.tb_mark_seen.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
         _lib = l
     return _lib
+
+
+_tlib = None
+
+
+def tlib():
+    """The library of tensor-core kernels (tcgen05 / TMA / mma.sync), built and loaded when first asked for."""
+    global _tlib
+    if _tlib is None:
+        lib()
+        l = _build.load("tensor")
+        l.tb_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        l.tb_gemm_tc_check.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
+        l.tb_attn_decode_mma.argtypes = [POINTER(AttnArgs), c_void_p]
+        l.tb_attn_decode_mma_check.argtypes = [POINTER(AttnArgs), c_int]
+        l.tb_attn_prefill_mma.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
+        l.tb_attn_prefill_mma_check.argtypes = [POINTER(AttnArgs), c_int, c_int]
+        l.tb_attn_prefill_tc.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
+        l.tb_attn_prefill_tc_check.argtypes = [POINTER(AttnArgs), c_int, c_int]
+        l.tb_mma_probe.argtypes = [c_int, c_int, POINTER(ctypes.c_double)]
+        _tlib = l
+    return _tlib
 
 
 def _check(rc: int) -> None:
@@ -154,7 +168,7 @@ def gemm_tc_accepts(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: in
         return False
     if x.stride(1) != 1 or out.stride(1) != 1 or x.shape[1] != w.shape[1]:
         return False
-    return lib().tb_gemm_tc_check(x.shape[0], w.shape[0], x.shape[1], x.stride(0), out.stride(0), epi,
+    return tlib().tb_gemm_tc_check(x.shape[0], w.shape[0], x.shape[1], x.stride(0), out.stride(0), epi,
                                   x.data_ptr(), w.data_ptr(), out.data_ptr()) == 0
 
 
@@ -170,13 +184,13 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, strea
     N = w.shape[0]
     if w.shape[1] != K_ or not w.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError(f"gemm_tc: shapes do not fit: x {tuple(x.shape)} w {tuple(w.shape)}")
-    _check(lib().tb_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K_, x.stride(0), out.stride(0), epi,
+    _check(tlib().tb_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K_, x.stride(0), out.stride(0), epi,
                             splits, stream))
 
 
 def gemm_tc_error() -> int:
     """Error word of the tensor-core kernels (0: none); synchronises the device and clears the word."""
-    return int(lib().tb_gemm_tc_error())
+    return int(tlib().tb_gemm_tc_error())
 
 
 def qk_norm_rope(args: QkArgs, in_dtype: torch.dtype, out_dtype: torch.dtype, stream: int) -> None:
@@ -196,44 +210,44 @@ def attn_decode(args: AttnArgs, dtype: torch.dtype, stream: int) -> None:
 
 
 def attn_decode_mma_accepts(args: AttnArgs, dtype: torch.dtype) -> bool:
-    return dtype == torch.bfloat16 and lib().tb_attn_decode_mma_check(byref(args), BF16) == 0
+    return dtype == torch.bfloat16 and tlib().tb_attn_decode_mma_check(byref(args), BF16) == 0
 
 
 def attn_decode_mma(args: AttnArgs, stream: int) -> None:
     """Decode attention on tensor cores (bfloat16, head_dim 64 or 128), then the merge of the splits."""
-    _check(lib().tb_attn_decode_mma(byref(args), stream))
+    _check(tlib().tb_attn_decode_mma(byref(args), stream))
 
 
 def set_attn_decode_cluster(on: bool) -> None:
     """Decode attention with up to 8 splits: merge them inside a thread-block cluster (on by default) or through
     scratch memory and the merge kernel."""
-    lib().tb_attn_decode_set_cluster(int(bool(on)))
+    tlib().tb_attn_decode_set_cluster(int(bool(on)))
 
 
 def attn_prefill_mma_accepts(args: AttnArgs, dtype: torch.dtype, all_fresh: bool) -> bool:
-    return dtype == torch.bfloat16 and lib().tb_attn_prefill_mma_check(byref(args), BF16, int(all_fresh)) == 0
+    return dtype == torch.bfloat16 and tlib().tb_attn_prefill_mma_check(byref(args), BF16, int(all_fresh)) == 0
 
 
 def attn_prefill_mma(args: AttnArgs, all_fresh: bool, stream: int) -> None:
     """Causal attention of prompts that start at position 0, on tensor cores (bfloat16, head_dim 64 or 128)."""
-    _check(lib().tb_attn_prefill_mma(byref(args), int(all_fresh), stream))
+    _check(tlib().tb_attn_prefill_mma(byref(args), int(all_fresh), stream))
 
 
 def attn_prefill_tc_accepts(args: AttnArgs, dtype: torch.dtype, all_fresh: bool) -> bool:
-    return dtype == torch.bfloat16 and lib().tb_attn_prefill_tc_check(byref(args), BF16, int(all_fresh)) == 0
+    return dtype == torch.bfloat16 and tlib().tb_attn_prefill_tc_check(byref(args), BF16, int(all_fresh)) == 0
 
 
 def attn_prefill_tc(args: AttnArgs, all_fresh: bool, stream: int) -> None:
     """Causal attention of prompts that start at position 0 on the tcgen05 tensor cores (bfloat16, head_dim 128)."""
-    _check(lib().tb_attn_prefill_tc(byref(args), int(all_fresh), stream))
+    _check(tlib().tb_attn_prefill_tc(byref(args), int(all_fresh), stream))
 
 
 def attn_tc_error() -> int:
-    return int(lib().tb_attn_tc_error())
+    return int(tlib().tb_attn_tc_error())
 
 
 def attn_mma_error() -> int:
-    return int(lib().tb_attn_mma_error())
+    return int(tlib().tb_attn_mma_error())
 
 
 def sample(args: SampleArgs, stream: int) -> None:
@@ -262,23 +276,23 @@ def set_pdl(on: bool) -> None:
 
 def set_gemm_tail_split(on: bool) -> None:
     """Prompt products with the ADD epilogue: cut the tiles of a last, partly filled round along K (on by default) or keep them whole."""
-    lib().tb_gemm_tc_set_tail_split(int(bool(on)))
+    tlib().tb_gemm_tc_set_tail_split(int(bool(on)))
 
 
 def set_gemm_pair(on: bool) -> None:
     """Prompt products on pairs of CTAs that share one MMA (on by default) or on single CTAs."""
-    lib().tb_gemm_tc_set_pair(int(bool(on)))
+    tlib().tb_gemm_tc_set_pair(int(bool(on)))
 
 
 def gemm_pair_clusters(epi: int) -> int:
     """CTA pairs the device holds at once for the pair kernel of this epilogue (0: it cannot run)."""
-    return int(lib().tb_gemm_tc_pair_clusters(int(epi)))
+    return int(tlib().tb_gemm_tc_pair_clusters(int(epi)))
 
 
 def mma_probe(n: int, iters: int = 4096) -> float:
     """Clocks one tcgen05.mma of 128 x n x 16 takes, issued back to back on every SM (a measurement, used by no step)."""
     out = ctypes.c_double(0.0)
-    _check(lib().tb_mma_probe(int(n), int(iters), byref(out)))
+    _check(tlib().tb_mma_probe(int(n), int(iters), byref(out)))
     return float(out.value)
 
 
