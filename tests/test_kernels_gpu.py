@@ -171,6 +171,55 @@ def test_qk_norm_rope_in_place_and_append(K, dtype, nh, nkv, hd, rot):
         K.qk_norm_rope(a, DT[dtype], DT[dtype], stream())
 
 
+@pytest.mark.parametrize("M,nh,nkv,Kd,ring", [(1, 4, 2, 256, 0), (8, 32, 8, 1024, 0), (13, 3, 1, 520, 0), (16, 6, 3, 4096, 128)])
+def test_fused_qkv_projection_norm_rotary_append(K, M, nh, nkv, Kd, ring):
+    """Projection, head norm, rotation and cache append in one kernel (K slices of a head summed inside a
+    thread-block cluster) against the plain functions: single tokens of M sequences at scattered
+    positions, ragged K, a ring cache; the cache rows of other tokens must stay as they were."""
+    hd, theta, eps = 128, 1e4, 1e-6
+    g = torch.Generator().manual_seed(M * 7 + nh)
+    N = (nh + 2 * nkv) * hd
+    x = torch.randn(M, Kd, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, Kd, generator=g) * 0.05).to(torch.bfloat16)
+    qw, kw = 1 + 0.1 * torch.randn(hd, generator=g), 1 + 0.1 * torch.randn(hd, generator=g)
+    lens = [int(v) for v in torch.randint(1, 300, (M,), generator=g)]          # after the step; the new token sits at len - 1
+    slots = torch.randperm(M + 2, generator=g)[:M].tolist()
+    pos = torch.tensor([n - 1 for n in lens])
+    full = P.linear(x.float(), w.float())
+    want_q = P.rope_neox(P.rms_norm(full[:, :nh * hd].view(M, nh, hd), qw, eps), pos, theta)
+    want_k = P.rope_neox(P.rms_norm(full[:, nh * hd:(nh + nkv) * hd].view(M, nkv, hd), kw, eps), pos, theta)
+    want_v = full[:, (nh + nkv) * hd:].view(M, nkv, hd)
+    cache = Paged(K, slots, lens, nkv, hd, torch.bfloat16, ring_rows=ring)
+    before = cache.storage.clone()
+    lay = layout_for(slots, [n - 1 for n in lens], [1] * M)
+    k_ = torch.arange(hd // 2, dtype=torch.float64)
+    inv = (torch.tensor(theta, dtype=torch.float64) ** (-2 * k_ / hd)).float()
+    keep = (qw.cuda(), kw.cuda(), inv.cuda(), x.cuda(), w.cuda())
+    q_out = torch.full((M, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    a = K.QkArgs()
+    a.inp, a.in_stride, a.q_out, a.q_stride, a.k_out, a.k_stride = None, 0, q_out.data_ptr(), nh * hd, None, 0
+    a.q_w, a.k_w, a.inv_freq = keep[0].data_ptr(), keep[1].data_ptr(), keep[2].data_ptr()
+    a.eps, a.rot, a.nh, a.nkv, a.hd = eps, hd, nh, nkv, hd
+    a.pos_of, a.seq_of, a.slot_of_seq, a.kv_len = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr(), lay.kv_len.data_ptr()
+    a.cache, a.append, a.T, a.zero_in = cache.view, 1, M, 0
+    assert K.gemm_qkv_accepts(keep[3], keep[4], a, torch.bfloat16)
+    K.gemm_qkv(keep[3], keep[4], a, stream())
+    assert K.gemm_qkv_error() == 0
+    assert rel_l2(q_out.float().cpu(), want_q.reshape(M, -1)) < 6e-3
+    changed = torch.zeros_like(before, dtype=torch.bool)
+    for i, (s, p) in enumerate(zip(slots, pos.tolist())):
+        ck, cv = cache.get(s, p)
+        assert rel_l2(ck, want_k[i]) < 6e-3 and rel_l2(cv, want_v[i]) < 6e-3
+        row = p % ring if ring else p
+        page = int(cache.table[s, row // 64])
+        changed[:, page, :, row % 64] = True
+    assert torch.equal(cache.storage[~changed], before[~changed])             # nothing else was written
+    a.hd = 64
+    assert not K.gemm_qkv_accepts(keep[3], keep[4], a, torch.bfloat16)
+    a.hd, a.T = 128, M + 1
+    assert not K.gemm_qkv_accepts(keep[3], keep[4], a, torch.bfloat16)
+
+
 def reference_attention(q, keys, vals, qpos, window, scale):
     """q [nh, hd] at position qpos; keys/vals [len, nkv, hd]; float64."""
     nh, nkv = q.shape[0], keys.shape[1]

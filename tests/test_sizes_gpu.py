@@ -18,12 +18,15 @@ BIG = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_la
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_mid_size_model_against_the_plain_implementation(dtype):
+@pytest.mark.parametrize("qkv", ["fused", "split"])     # decode: projection + norm + rotary + append as one kernel, and as three
+def test_mid_size_model_against_the_plain_implementation(dtype, qkv):
     from titan_b200 import Engine, StepEntry
     from titan_b200.config import config_from_dict
+    if dtype == "float32" and qkv == "split":
+        pytest.skip("the 32-bit path has one way only")
     w = random_weights(MID, 11, torch.bfloat16, std=0.03)
     w32 = {k: v.float() for k, v in w.items()}
-    e = Engine.from_tensors(config_from_dict(MID), w, dtype=dtype, max_tokens=2048)
+    e = Engine.from_tensors(config_from_dict(MID), w, dtype=dtype, max_tokens=2048, qkv=qkv)
     reqs = [random_tokens(n, MID["vocab_size"], 50 + n) for n in (300, 130, 70)]
     want = [P.forward_logits(MID, w32, r) for r in reqs]
     slots = [e.alloc_slot() for _ in reqs]

@@ -7,6 +7,7 @@
 // (kernels/gemm_quant.cu:2570-2587).  Sums of squares, the norm scale and the rotation
 // angle are float32 with precise sqrtf / sincosf (the reference uses fast-math, norm_rope.cu:101-113).
 #include "common.cuh"
+#include "qk_args.h"
 
 // ------------------------------------------------------------------ embedding
 template <typename T>
@@ -117,19 +118,6 @@ extern "C" int tb_rmsnorm(const float* x, const float* w, void* y, int dtype, co
 // weight (skipped when the weight pointer is null), then the half-split rotation of the first
 // ``rot`` dims: for k < rot/2, angle = pos * inv_freq[k], (y_k, y_{k+rot/2}) rotated
 // (kernels/norm_rope.cu:226-245 and :83-117 in berniehans/titan).
-struct QkArgs {
-    const void* in; int in_stride;          // [T][in_stride]: Q | K | V
-    void* q_out; int q_stride;              // [T][q_stride]
-    void* k_out; int k_stride;              // [T][k_stride] (null: K goes to the cache only)
-    const float* q_w; const float* k_w;     // [hd] or null
-    const float* inv_freq;                  // [rot/2] or null (no rotation)
-    float eps; int rot; int nh; int nkv; int hd;
-    const int* pos_of; const int* seq_of; const int* slot_of_seq;
-    TbKvView cache; int append; int T;
-    int zero_in;                            // after reading a head, write zeros over it (an accumulation buffer is left clean)
-    const int* kv_len;                      // [B] lengths after the step: in a ring, a row that a later token of the step reuses is not written
-};
-
 #define QK_MAXE 8   // head_dim <= 32 * QK_MAXE
 
 template <typename TIn, typename TOut>

@@ -103,6 +103,8 @@ def tlib():
         l.tb_attn_prefill_tc.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
         l.tb_attn_prefill_tc_check.argtypes = [POINTER(AttnArgs), c_int, c_int]
         l.tb_mma_probe.argtypes = [c_int, c_int, POINTER(ctypes.c_double)]
+        l.tb_gemm_qkv.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, POINTER(QkArgs), c_int, c_void_p]
+        l.tb_gemm_qkv_check.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_void_p, POINTER(QkArgs), c_int]
         _tlib = l
     return _tlib
 
@@ -186,6 +188,24 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, strea
         raise KernelError(f"gemm_tc: shapes do not fit: x {tuple(x.shape)} w {tuple(w.shape)}")
     _check(tlib().tb_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K_, x.stride(0), out.stride(0), epi,
                             splits, stream))
+
+
+def gemm_qkv_accepts(x: torch.Tensor, w: torch.Tensor, args: QkArgs, out_dtype: torch.dtype) -> bool:
+    """Can the Q | K | V projection run fused with head norm, rotation and cache append (tb_gemm_qkv)?"""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out_dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous():
+        return False
+    return tlib().tb_gemm_qkv_check(x.shape[0], w.shape[0], x.shape[1], x.stride(0), x.data_ptr(), w.data_ptr(), byref(args), BF16) == 0
+
+
+def gemm_qkv(x: torch.Tensor, w: torch.Tensor, args: QkArgs, stream: int) -> None:
+    """Q | K | V = x . w^T per head, head norm, rotation, Q rows out and K, V rows into the cache: one kernel
+    (a decode step of at most 16 tokens, heads of 128, bfloat16)."""
+    _need_cuda(x, w)
+    _check(tlib().tb_gemm_qkv(x.data_ptr(), w.data_ptr(), x.shape[0], w.shape[0], x.shape[1], x.stride(0), byref(args), BF16, stream))
+
+
+def gemm_qkv_error() -> int:
+    return int(tlib().tb_gemm_qkv_error())
 
 
 def gemm_tc_error() -> int:

@@ -116,6 +116,23 @@ class AttentionMixer(Mixer):
                                         group.need.head_dim)
         return self._views[key]
 
+    def _qk_args(self, qkv, width, q_buf, q_stride, view, lay, inv_freq, T, hd, append: bool, zero_in: bool) -> K.QkArgs:
+        s = self.spec
+        qa = K.QkArgs()
+        qa.inp, qa.in_stride = (None if qkv is None else qkv.data_ptr()), width
+        qa.q_out, qa.q_stride = q_buf.data_ptr(), q_stride
+        qa.k_out, qa.k_stride = None, 0
+        qa.q_w = None if self.q_norm is None else self.q_norm.data_ptr()
+        qa.k_w = None if self.k_norm is None else self.k_norm.data_ptr()
+        qa.inv_freq = None if inv_freq is None else inv_freq.data_ptr()
+        qa.eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
+        qa.rot, qa.nh, qa.nkv, qa.hd = self.position.rotary_dim, s.num_heads, (0 if self.shared else s.num_kv_heads), hd
+        qa.pos_of, qa.seq_of, qa.slot_of_seq = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr()
+        qa.cache, qa.append, qa.T = view, int(append), T
+        qa.zero_in = int(zero_in)
+        qa.kv_len = lay.kv_len.data_ptr()
+        return qa
+
     def forward(self, h: torch.Tensor, ctx, cache, out: torch.Tensor) -> None:
         s, lay = self.spec, ctx.layout
         T, Q, KV, hd = lay.T, self.Q, self.KV, s.head_dim
@@ -127,7 +144,19 @@ class AttentionMixer(Mixer):
         # A decode step in bfloat16 sums Q | K | V in float32 (K slices of the product add into a zeroed
         # buffer), and the norm/rotary kernel rounds once, into the query buffer and the cache.
         wide_sum = decode and not self.shared and h.dtype == torch.bfloat16 and ctx.options.get("gemm", "fast") != "plain"
-        if wide_sum:
+        # ... or, on request (option qkv="fused") and where the kernel takes the shapes (heads of 128, at most
+        # 16 tokens), the projection itself sums its K slices inside a thread-block cluster and does norm,
+        # rotation and append.
+        fused = None
+        if wide_sum and ctx.options.get("qkv", "split") == "fused":
+            q_buf = ctx.empty((T, Q))
+            fused = self._qk_args(None, 0, q_buf, Q, view, lay, inv_freq, T, hd, append=True, zero_in=False)
+            if not K.gemm_qkv_accepts(h, self.w_qkv, fused, q_buf.dtype):
+                fused = None
+        if fused is not None:
+            K.gemm_qkv(h, self.w_qkv, fused, ctx.stream)
+            q_stride = Q
+        elif wide_sum:
             key = f"qkv_sum_{T}x{width}"            # zeroed once; the norm/rotary kernel leaves it zeroed again
             qkv = ctx.scratch.get(key)
             if qkv is None:
@@ -138,25 +167,17 @@ class AttentionMixer(Mixer):
             qkv = ctx.empty((T, width))
             linear.matmul(h, self.w_qkv, qkv, linear.EPI_STORE, ctx)
             q_buf, q_stride = qkv, width
-        esz = qkv.element_size()
-        qa = K.QkArgs()
-        qa.inp, qa.in_stride = qkv.data_ptr(), width
-        qa.q_out, qa.q_stride = q_buf.data_ptr(), q_stride
-        qa.k_out, qa.k_stride = (None, 0) if (self.shared or wide_sum) else (qkv.data_ptr() + Q * esz, width)
-        qa.q_w = None if self.q_norm is None else self.q_norm.data_ptr()
-        qa.k_w = None if self.k_norm is None else self.k_norm.data_ptr()
-        qa.inv_freq = None if inv_freq is None else inv_freq.data_ptr()
-        qa.eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
-        qa.rot, qa.nh, qa.nkv, qa.hd = self.position.rotary_dim, s.num_heads, (0 if self.shared else s.num_kv_heads), hd
-        qa.pos_of, qa.seq_of, qa.slot_of_seq = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr()
-        # K and V go into the cache in this kernel when nothing of this step still has to read the rows
-        # they replace: always for single tokens and for caches that keep everything; in a ring only if
-        # every sequence starts at position 0 (attention then reads the step's own rows alone).
-        append_now = not self.shared and (decode or view.ring_rows == 0 or lay.all_fresh)
-        qa.cache, qa.append, qa.T = view, int(append_now), T
-        qa.zero_in = int(wide_sum)
-        qa.kv_len = lay.kv_len.data_ptr()
-        K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
+        if fused is None:
+            # K and V go into the cache in this kernel when nothing of this step still has to read the rows
+            # they replace: always for single tokens and for caches that keep everything; in a ring only if
+            # every sequence starts at position 0 (attention then reads the step's own rows alone).
+            append_now = not self.shared and (decode or view.ring_rows == 0 or lay.all_fresh)
+            qa = self._qk_args(qkv, width, q_buf, q_stride, view, lay, inv_freq, T, hd, append=append_now, zero_in=wide_sum)
+            if not (self.shared or wide_sum):
+                qa.k_out, qa.k_stride = qkv.data_ptr() + Q * qkv.element_size(), width
+            K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
+        else:
+            append_now = True
 
         attn = ctx.empty((T, Q))
         aa = K.AttnArgs()
@@ -182,7 +203,7 @@ class AttentionMixer(Mixer):
             if self.shared:
                 aa.kv_new, aa.kv_stride = None, 0
             else:
-                aa.kv_new, aa.kv_stride = qkv.data_ptr() + Q * esz, width
+                aa.kv_new, aa.kv_stride = qkv.data_ptr() + Q * qkv.element_size(), width
             mode = "plain" if self.shared else ctx.options.get("attention", "fast")   # "fast" | "mma" | "plain"
             if mode == "fast" and K.attn_prefill_tc_accepts(aa, q_buf.dtype, lay.all_fresh):
                 K.attn_prefill_tc(aa, lay.all_fresh, ctx.stream)
