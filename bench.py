@@ -192,7 +192,7 @@ def run_ours(args):
     pre_ms, pre_best = time_prefill(engine, torch, T, 3, 12)       # ~0.4 s back to back: the power cap is reached
     pre_rec = pre_clocks.stop()
     flops = prefill_flops(cfg, args.layers, T)
-    err = K.gemm_tc_error() if hasattr(K, "gemm_tc_error") else 0
+    err = max(K.gemm_tc_error(), K.attn_tc_error(), K.attn_mma_error())      # a bounded wait that gave up anywhere (0: none)
     line = {
         "metric": "decode tok/s (Qwen3-8B layer sizes, bf16, batch 8)", "value": round(value, 1), "unit": "tok/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms, 4),

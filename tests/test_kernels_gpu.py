@@ -220,6 +220,36 @@ def test_fused_qkv_projection_norm_rotary_append(K, M, nh, nkv, Kd, ring):
     assert not K.gemm_qkv_accepts(keep[3], keep[4], a, torch.bfloat16)
 
 
+def test_attention_prefill_tensor_cores_long_prompt_many_times(K):
+    """A long prompt (125 key tiles for the last query block, 32 heads) run repeatedly: the roles of the tcgen05 kernel
+    hand tiles to each other through barriers whose phases must never get two apart, which only shows
+    after many tiles and not on every run.  Checked against the mma.sync kernel and the error words."""
+    nh, nkv, hd, T = 32, 8, 128, 8000
+    g = torch.Generator().manual_seed(3)
+    lay = layout_for([0], [0], [T])
+    Q, KV = nh * hd, nkv * hd
+    buf = torch.randn(T, Q + 2 * KV, generator=g).to(torch.bfloat16).cuda()
+    outs = {}
+    for which, reps in (("mma", 1), ("tc", 40)):
+        for _ in range(reps):
+            out = torch.full((T, Q), float("nan"), dtype=torch.bfloat16, device="cuda")
+            a = K.AttnArgs()
+            a.q, a.q_stride, a.out, a.out_stride = buf.data_ptr(), Q + 2 * KV, out.data_ptr(), Q
+            a.kv_new, a.kv_stride = buf.data_ptr() + Q * 2, Q + 2 * KV
+            a.batch = lay.c_struct()
+            a.nh, a.nkv, a.hd, a.window, a.scale = nh, nkv, hd, 0, 1 / math.sqrt(hd)
+            if which == "tc":
+                K.attn_prefill_tc(a, True, stream())
+                assert K.attn_tc_error() == 0
+                if _ % 10 == 0:
+                    assert rel_l2(out.float().cpu(), outs["mma"]) < 8e-3
+            else:
+                K.attn_prefill_mma(a, True, stream())
+                assert K.attn_mma_error() == 0
+                outs["mma"] = out.float().cpu()
+    assert not torch.isnan(outs["mma"]).any()
+
+
 def reference_attention(q, keys, vals, qpos, window, scale):
     """q [nh, hd] at position qpos; keys/vals [len, nkv, hd]; float64."""
     nh, nkv = q.shape[0], keys.shape[1]

@@ -306,6 +306,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             for (int i = 0; i < 32; ++i) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
             tmem_st32_bits(tmem_s + (j & 3) * BKEY + lane_addr, pk);
             TCLK(5);
+            // The P.V issuer must have seen this group's previous arrival before the next one, or the
+            // barrier would run two phases ahead of it and its parity wait would never end.  P.V of that
+            // tile complete implies it; by now (a whole tile later) this wait is almost always over.
+            if (mine >= 1) wait(pv_done + ((j - 2) & 3), ((j - 2) >> 2) & 1, 10);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + g);

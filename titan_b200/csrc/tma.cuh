@@ -11,7 +11,10 @@
 
 namespace tbtma {
 
-constexpr uint32_t WAIT_LIMIT = 1u << 18;      // try_wait rounds; each lasts up to the hardware's time limit
+#ifndef TB_WAIT_LIMIT_LOG2
+#define TB_WAIT_LIMIT_LOG2 18
+#endif
+constexpr uint32_t WAIT_LIMIT = 1u << TB_WAIT_LIMIT_LOG2;      // try_wait rounds; each lasts up to the hardware's time limit
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

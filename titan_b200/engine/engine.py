@@ -253,6 +253,13 @@ class Engine:
     def finish(self, slot) -> None:
         self.cache.free_slot(slot)
 
+    def check_kernels(self) -> None:
+        """Raise if a bounded wait inside a kernel gave up since the last check (the results of that step
+        are invalid).  Synchronises the device; the generation loop calls it once per batch."""
+        bad = K.wait_errors()
+        if bad:
+            raise StepError("a kernel's bounded wait gave up, results are invalid: " + ", ".join(f"{k} (code {v})" for k, v in bad.items()))
+
     def _step_and_sample(self, entries) -> List[int]:
         x, layout, ctx = self.forward(entries)
         logits = self.model.logits(x, ctx, layout.want)

@@ -96,6 +96,9 @@ def generate(backend, requests: Sequence[GenerationRequest], first_sequence_id: 
         batch = plan_batch(pending, requests, backend)
         pending = [i for i in pending if i not in batch]
         _run_batch(backend, [requests[i] for i in batch], [first_sequence_id + i for i in batch], batch, results)
+        check = getattr(backend, "check_kernels", None)
+        if check is not None:
+            check()                               # a kernel that gave up on a wait fails the batch loudly
     return results  # type: ignore[return-value]
 
 

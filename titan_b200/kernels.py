@@ -289,6 +289,16 @@ def commit_lengths(slot_of_seq, kv_len, seq_len, stream: int) -> None:
     _check(lib().tb_commit_lengths(slot_of_seq.data_ptr(), kv_len.data_ptr(), seq_len.data_ptr(), slot_of_seq.numel(), stream))
 
 
+def wait_errors() -> dict:
+    """The error words of the kernels whose waits are bounded (a wait that gave up leaves a code there and the
+    step's result is invalid).  Reads and clears them; synchronises the device.  Empty if all is well, and
+    if the tensor-core library was never loaded."""
+    if _tlib is None:
+        return {}
+    found = {"gemm_tc": gemm_tc_error(), "gemm_qkv": gemm_qkv_error(), "attn_prefill_tc": attn_tc_error(), "attn_mma": attn_mma_error()}
+    return {k: v for k, v in found.items() if v}
+
+
 def set_pdl(on: bool) -> None:
     """Programmatic dependent launch for every kernel launched afterwards (on by default)."""
     lib().tb_set_pdl(int(bool(on)))

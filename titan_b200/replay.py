@@ -57,6 +57,7 @@ def main(argv=None) -> int:
             if logits is not None:
                 arr = logits.float().cpu().numpy().astype("<f4", copy=False)
                 arr.tofile(os.path.join(args.out, f"{step}.f32"))
+                engine.check_kernels()                 # the copy above has synchronised: a wait that gave up fails the replay
         for rid in rec.get("end", []):
             rid = str(rid)
             if rid in slots:
