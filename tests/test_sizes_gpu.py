@@ -74,3 +74,32 @@ def test_benchmark_layer_sizes_bfloat16_against_float32():
     assert rel_l2(logits["bfloat16"], logits["float32"]) < TOL["bfloat16"]
     # greedy tokens agree until rounding decides a near-tie: the first token of each sequence at least
     assert [t[0] for t in tokens["bfloat16"]] == [t[0] for t in tokens["float32"]]
+
+
+def test_long_prompts_and_decoding_fast_kernels_against_plain_kernels():
+    """The same mid-size model in bfloat16 with the tensor-core kernels and with the any-size CUDA-core
+    kernels: prompts of thousands of tokens (dozens of key tiles, several chunks of decode attention,
+    cluster merges), then 48 single-token steps, one batch after another so that slots are used again.
+    Both must agree within the bfloat16 tolerance, and no kernel may have given up on a wait."""
+    from titan_b200 import Engine, StepEntry, kernels as K
+    from titan_b200.config import config_from_dict
+    w = random_weights(MID, 12, torch.bfloat16, std=0.03)
+    engines = {"fast": Engine.from_tensors(config_from_dict(MID), w, dtype="bfloat16", max_tokens=3 * 3072, max_context=3072),
+               "plain kernels": Engine.from_tensors(config_from_dict(MID), w, dtype="bfloat16", max_tokens=3 * 3072, max_context=3072,
+                                                    gemm="plain", attention="plain")}
+    got = {}
+    for name, e in engines.items():
+        rows = []
+        for round_ in range(2):
+            reqs = [random_tokens(n, MID["vocab_size"], 70 + n + round_) for n in (2300, 900, 1500)]
+            slots = [e.alloc_slot() for _ in reqs]
+            rows.append(e.step([StepEntry(s, r, [len(r) - 1, 0, len(r) // 2]) for s, r in zip(slots, reqs)]))
+            for step in range(48):
+                live = slots if step < 30 else slots[:2]               # the third sequence ends earlier
+                rows.append(e.step([StepEntry(s, [(11 * step + 3 * i) % MID["vocab_size"]], [0]) for i, s in enumerate(live)]))
+            for s in slots:
+                e.free_slot(s)
+        e.check_kernels()
+        got[name] = torch.cat(rows).float().cpu()
+    assert K.wait_errors() == {}
+    assert rel_l2(got["fast"], got["plain kernels"]) < TOL["bfloat16"]
