@@ -7,17 +7,20 @@
 // so that in decode the 128-row side of the instruction is filled by weight rows and the batch is the
 // narrow side (BN = 16..128).
 //
-// Plain mode is a persistent kernel (gemm_tc_persistent_kernel): one CTA per SM walks over the tiles,
-// the accumulator is double buffered in tensor memory, and the epilogue of a tile overlaps the MMAs
-// of the next.  Swap mode (gemm_tc_kernel) is one tile per CTA with two CTAs per SM; it can
-// cut K into slices (grid.z), each CTA adding its partial sum into a float32 output with atomics, to
-// put enough CTAs on the machine when N / 128 is small.
+// Plain mode is persistent.  From 256 x 256 outputs on it runs on PAIRS of CTAs (gemm_tc_pair_kernel, a
+// cluster of two, tcgen05.mma.cta_group::2 with M = 256: see the comment above that kernel); smaller
+// outputs run on single CTAs (gemm_tc_persistent_kernel: one CTA per SM walks over 128 x 256 tiles).
+// In both the accumulator is double buffered in tensor memory, so the epilogue of a tile overlaps the
+// MMAs of the next, and the tiles of a last, partly filled round can be cut along K for the ADD
+// epilogue (struct Segments).  Swap mode (gemm_tc_kernel) is one tile per CTA with two CTAs per SM; it
+// can cut K into slices (grid.z), each CTA adding its partial sum into a float32 output with atomics, to
+// fill the machine once when N / 128 is small; its weights are loaded with the L2 evict-first hint.
 //
 // Data path: TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, zero fill outside the tensor) into a
-// ring of shared-memory stages -> tcgen05.mma.cta_group::1.kind::f16 issued by one thread, four
-// K=16 steps per 64-wide stage -> accumulator in TMEM -> tcgen05.ld by four epilogue warps.
+// ring of shared-memory stages -> tcgen05.mma.kind::f16 issued by one thread, four K=16 steps per
+// 64-wide stage -> accumulator in TMEM -> tcgen05.ld by four epilogue warps.
 // Warp 0 produces, warp 1 allocates TMEM and issues MMAs, warps 2..5 run the epilogue.
-// No cluster launch, no multicast.  Kernels are launched with programmatic dependent launch: the
+// No TMA multicast anywhere.  Kernels are launched with programmatic dependent launch: the
 // producer requests the first ring of WEIGHT tiles before it waits for the kernel before (no kernel
 // writes weights), so a decode step's weight stream does not stop between kernels.
 //
