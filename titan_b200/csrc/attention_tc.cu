@@ -104,6 +104,24 @@ __device__ __forceinline__ float ex2(float x) {          // 2^x, one instruction
 
 constexpr float RESCALE_LOG2 = 8.0f;
 
+// Barriers and why no waiter can fall behind.  A parity wait only tells "the phase with this parity is
+// over" from the barrier's CURRENT phase, so a waiter must see phase k before phase k + 1 ends; every
+// barrier below keeps that by construction (tile j uses slot j % 4; a slot's phases are tiles j, j + 4, ..).
+//   k_full[s], v_full[s]   TMA bytes of K_j, V_j.  Waited by the S issuer of tile j / the P.V issuer.  The
+//                          next load into the slot needs s_done / pv_done of tile j, i.e. the MMAs that
+//                          the waiter issued after its wait.
+//   s_done[s]              tcgen05.commit after S_j.  Waited by the softmax group of tile j (every phase)
+//                          and polled by the producer for K_{j+4}; S_{j+4} needs that K tile and pv_done(j),
+//                          which needs the group's P_j.
+//   p_full[g]              four arrivals (the group's warps) per tile of group g.  Waited by the P.V issuer,
+//                          every phase.  The group arrives for tile j only after pv_done(j - 2): without
+//                          that, a group that never rescales could arrive for j and j + 2 before the
+//                          issuer had looked once (an intermittent deadlock on long prompts).
+//   pv_done[s]             tcgen05.commit after P.V_j.  Polled by the producer for V_{j+4}, waited by the S
+//                          issuer of tile j + 4 (both every phase) and by the group of tile j + 2 before it
+//                          arrives (and before a rescale, and once after its last tile); P.V_{j+4} needs
+//                          all three to have moved on.
+
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, TcAttnArgs a) {
     extern __shared__ uint8_t smem_raw[];
