@@ -459,10 +459,10 @@ def test_attention_decode_on_tensor_cores(K, nh, nkv, hd, window, ring):
     lay = layout_for(slots, [n - 1 for n in lens], [1] * B)
     qb = q.reshape(B, Q).cuda()
     want = torch.stack([reference_attention(q[i].float(), ks[i].float(), vs[i].float(), lens[i] - 1, window, scale) for i in range(B)]).reshape(B, Q)
-    for chunk in (64, 256, 1024):
+    for chunk in (64, 128, 256, 1024):              # 24 splits (scratch), 12 (a cluster beyond the portable 8), 6, 2
         splits = -(-max(lens) // chunk)
         outs = []
-        for mode in ("mma", "mma through scratch", "plain"):     # up to 8 splits merge inside a cluster unless told otherwise
+        for mode in ("mma", "mma through scratch", "plain"):     # up to 16 splits merge inside a cluster unless told otherwise
             fast = mode != "plain"
             out = torch.full((B, Q), float("nan"), dtype=torch.bfloat16, device="cuda")
             scratch = torch.full((B * nh * splits * (hd + 2),), float("nan"), device="cuda")

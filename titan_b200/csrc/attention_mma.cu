@@ -451,6 +451,7 @@ static int launch_decode(const CUtensorMap& map, const DecArgs& d, dim3 grid, cu
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE, CL>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // room for several CTAs per SM
+        if (CL) cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);    // clusters of up to 16
         TB_REQUIRE(e == cudaSuccess, "attn_decode_mma: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
@@ -462,13 +463,42 @@ static int launch_decode(const CUtensorMap& map, const DecArgs& d, dim3 grid, cu
     }
     return 0;
 }
+// The largest cluster of this kernel that the device can place: 16 where the non-portable size is allowed
+// and fits (B200), else 8, else 1 (no clusters).
 template <int HD, bool WIDE>
-static int launch_decode_any(const CUtensorMap& map, const DecArgs& d, dim3 grid, bool cluster, cudaStream_t stream) {
-    return cluster ? launch_decode<HD, WIDE, true>(map, d, grid, stream) : launch_decode<HD, WIDE, false>(map, d, grid, stream);
+static int cluster_limit() {
+    static int limit = -1;
+    if (limit < 0) {
+        limit = 1;
+        constexpr int STAGES = HD == 128 ? 3 : 4;
+        constexpr size_t smem = 1024 + (size_t)STAGES * 2 * PAGE * HD * 2 + 2 * STAGES * sizeof(uint64_t);
+        auto kernel = attn_decode_mma_kernel<HD, WIDE, true>;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        for (int size : {16, 8}) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(1, 1, size); cfg.blockDim = dim3(DEC_THREADS, 1, 1); cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)size;
+            cfg.attrs = attr; cfg.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters > 0) { limit = size; break; }
+            cudaGetLastError();
+        }
+    }
+    return limit;
+}
+// Launches the kernel; *merged says whether the splits merged among themselves (a cluster) or left their parts in scratch.
+template <int HD, bool WIDE>
+static int launch_decode_any(const CUtensorMap& map, const DecArgs& d, dim3 grid, bool may_cluster, bool* merged, cudaStream_t stream) {
+    *merged = may_cluster && (int)grid.z <= cluster_limit<HD, WIDE>();
+    TB_REQUIRE(*merged || d.scratch, "attn_decode_mma: %d splits need scratch memory", (int)grid.z);
+    return *merged ? launch_decode<HD, WIDE, true>(map, d, grid, stream) : launch_decode<HD, WIDE, false>(map, d, grid, stream);
 }
 
 int g_decode_cluster = 1;
-// The splits of decode attention merge inside a thread-block cluster (1, default, up to 8 splits) or through scratch memory and the merge kernel (0).
+// The splits of decode attention merge inside a thread-block cluster (1, default, up to 16 splits where the device places such clusters) or through scratch memory and the merge kernel (0).
 extern "C" void tb_attn_decode_set_cluster(int on) { g_decode_cluster = on ? 1 : 0; }
 
 // 0 if the tensor-core decode kernel takes this problem, else 1 with the reason in tb_last_error().
@@ -485,9 +515,9 @@ extern "C" int tb_attn_decode_mma_check(const AttnArgs* a, int dtype) {
 extern "C" int tb_attn_decode_mma(const AttnArgs* args, cudaStream_t stream) {
     const AttnArgs& a = *args;
     if (tb_attn_decode_mma_check(args, TB_BF16)) return 1;
-    // up to 8 splits: they form a cluster and merge among themselves; more: parts go to scratch and tb_attn_merge finishes
-    const bool cluster = g_decode_cluster && a.n_splits <= 8 && a.out != nullptr;
-    TB_REQUIRE(a.batch.B > 0 && a.cache.storage && (cluster || a.scratch), "attn_decode_mma: needs sequences, a cache and scratch");
+    // few enough splits form a cluster and merge among themselves; more leave parts in scratch and tb_attn_merge finishes
+    const bool may_cluster = g_decode_cluster && a.out != nullptr;
+    TB_REQUIRE(a.batch.B > 0 && a.cache.storage, "attn_decode_mma: needs sequences and a cache");
     TB_REQUIRE(a.n_splits > 0 && a.n_splits <= 65535 && a.nkv <= 65535, "attn_decode_mma: bad grid");
     TB_REQUIRE((long long)a.chunk * a.n_splits >= a.batch.max_kv_len, "attn_decode_mma: %d splits of %d keys do not cover %d keys", a.n_splits, a.chunk, a.batch.max_kv_len);
     TB_REQUIRE(a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv, "attn_decode_mma: the cache view does not match the heads");
@@ -504,11 +534,12 @@ extern "C" int tb_attn_decode_mma(const AttnArgs* args, cudaStream_t stream) {
     dim3 grid(a.batch.B, a.nkv, a.n_splits);
     const bool wide = a.nh / a.nkv > 8;
     int rc;
-    if (a.hd == 128) rc = wide ? launch_decode_any<128, true>(map, d, grid, cluster, stream) : launch_decode_any<128, false>(map, d, grid, cluster, stream);
-    else rc = wide ? launch_decode_any<64, true>(map, d, grid, cluster, stream) : launch_decode_any<64, false>(map, d, grid, cluster, stream);
+    bool merged = false;
+    if (a.hd == 128) rc = wide ? launch_decode_any<128, true>(map, d, grid, may_cluster, &merged, stream) : launch_decode_any<128, false>(map, d, grid, may_cluster, &merged, stream);
+    else rc = wide ? launch_decode_any<64, true>(map, d, grid, may_cluster, &merged, stream) : launch_decode_any<64, false>(map, d, grid, may_cluster, &merged, stream);
     if (rc) return rc;
     TB_CHECK_LAUNCH("attn_decode_mma");
-    return cluster ? 0 : tb_attn_merge(args, TB_BF16, stream);
+    return merged ? 0 : tb_attn_merge(args, TB_BF16, stream);
 }
 
 // Reads and clears the error word of this file's kernels (0: none).  Synchronises the device.

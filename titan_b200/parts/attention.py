@@ -40,16 +40,14 @@ def decode_split(lay, kv_heads: int, options, fast: bool):
     if not fast:
         chunk = int(options.get("attn_chunk", 256))
     else:
-        # Two CTAs of the tensor-core kernel fit an SM.  Measured over batch sizes 1 to 8 at 8,192 keys:
-        # one round of CTAs that fills about three quarters of those places is fastest (more splits make
-        # the merge longer, a second round costs a whole chunk), and chunks under 512 keys never pay.
+        # Two CTAs of the tensor-core kernel fit an SM.  Measured over batch sizes 1 to 8 at 8,192 keys: one
+        # round of CTAs on about 0.6 of those places is fastest (a second round costs a whole chunk, more
+        # splits a longer merge), chunks under 512 keys never pay, and at most 16 splits: up to 16 merge
+        # inside a thread-block cluster (no scratch, no merge kernel), which at batch 1 beats more, smaller
+        # chunks through scratch.
         places = 2 * int(options.get("sm_count", 148))
         pairs = lay.B * kv_heads
-        want = max(1, (3 * places // 4 + pairs // 2) // pairs)
-        # Up to 8 splits merge inside a thread-block cluster (no scratch, no merge kernel), which is worth
-        # fewer CTAs as long as a chunk stays at about a thousand keys (batch 1 and 2 at 8,192 keys).
-        if want > 8 and -(-bound // 8) <= 1024:
-            want = 8
+        want = min(16, max(1, (3 * places // 5 + pairs // 2) // pairs))
         chunk = max(512, -(-(-(-bound // want)) // 64) * 64)
     # an eager step launches the splits its longest sequence needs; a captured one, whose grid cannot
     # change, launches what the context limit needs (the extra CTAs leave at once)
