@@ -309,13 +309,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                 }
             }
             TCLK(4);
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            // two scores per instruction where the hardware has one (packed float32 FMA and add on sm_100):
+            // the softmax warps are short of issue slots, not only of special-function units
+            const float2 scale2 = make_float2(a.scale_log2, a.scale_log2), shift2 = make_float2(-m_new, -m_new);
+            float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                v[i] = ex2(fmaf(v[i], a.scale_log2, -m_new));
-                sum4[i & 3] += v[i];
+            for (int i = 0; i < 64; i += 2) {
+                const float2 x = __ffma2_rn(make_float2(v[i], v[i + 1]), scale2, shift2);
+                v[i] = ex2(x.x); v[i + 1] = ex2(x.y);
+                sum2[(i >> 1) & 1] = __fadd2_rn(sum2[(i >> 1) & 1], make_float2(v[i], v[i + 1]));
             }
-            l_run = l_run * f + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            l_run = l_run * f + ((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y));
             m_run = m_new;
             // P as bfloat16 pairs over the first 32 columns of this tile's S buffer (this thread's lane: its
             // scores are all in registers by now): the A operand of P.V, which never touches shared memory
