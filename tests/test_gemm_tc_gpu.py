@@ -25,17 +25,19 @@ SHAPES = [(1, 128, 64), (5, 384, 256), (16, 200, 72), (17, 1000, 520), (40, 130,
           (1100, 5000, 520), (2048, 6144, 256)]      # more tiles than SMs: a CTA walks over two or three tiles
 
 
-@pytest.fixture(params=["pairs", "single"])
+@pytest.fixture(params=["auto", "pairs", "single 128x256", "single 128x128"])
 def cta_mode(request, K):
-    """Prompt products run on pairs of CTAs (cta_group::2) by default; the one-CTA kernel is tested too."""
-    K.set_gemm_pair(request.param == "pairs")
+    """Prompt products choose among three tile shapes; every shape is forced in turn and tested on every size."""
+    K.set_gemm_plain_tile(["auto", "pairs", "single 128x256", "single 128x128"].index(request.param))
     yield request.param
-    K.set_gemm_pair(True)
+    K.set_gemm_plain_tile(0)
 
 
 @pytest.mark.parametrize("M,N,Kd", SHAPES + [(256, 256, 64), (300, 700, 136), (520, 264, 1032)])
 def test_all_epilogues(K, M, N, Kd, cta_mode):
-    if cta_mode == "single" and (M < 256 or N < 256):
+    if cta_mode != "auto" and M < 128:
+        pytest.skip("decode-sized products have one kernel")
+    if cta_mode == "pairs" and (M < 256 or N < 256):
         pytest.skip("pairs are only used from 256 x 256 outputs on")
     g = torch.Generator().manual_seed(M + N + Kd)
     x = torch.randn(M, Kd, generator=g).to(torch.bfloat16)

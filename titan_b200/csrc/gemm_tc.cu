@@ -761,6 +761,10 @@ int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const TcAr
 
 // Reads and clears the error word of the tensor-core kernels (0: none; 1, 2, 3: a wait of the
 // producer, the MMA issuer or the epilogue ran out).  Synchronises the device.
+int g_plain_tile = 0;
+// Prompt products: 0 chooses the tile shape, 1 forces CTA pairs (256 x 256), 2 single CTAs with 128 x 256, 3 with 128 x 128.
+extern "C" void tb_gemm_tc_set_plain_tile(int which) { g_plain_tile = which; }
+
 int g_pair = 1;
 // Prompt products on pairs of CTAs (cta_group::2; 1, default) or on single CTAs (0).
 extern "C" void tb_gemm_tc_set_pair(int on) { g_pair = on ? 1 : 0; }
@@ -820,7 +824,29 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         }
         return best;
     };
-    const int pairs_max = (!swap && g_pair && M >= 256 && N >= 256) ? pair_clusters_for(epi) : 0;
+    int pairs_max = (!swap && g_pair && M >= 256 && N >= 256) ? pair_clusters_for(epi) : 0;
+    int single_bn = N >= 256 ? 256 : 128;
+    if (!swap && M < 1024) {
+        // Which tile shape is fastest for this output (from 1,024 rows on: pairs).  Measured at M = 128 .. 1024: where rows are few, a CTA
+        // is bound by the tiles it loads, and a tile of a pair's CTA (128 rows of X, 128 of W for 128 x 256
+        // outputs) costs 1, a lone 128 x 256 tile 1.1 and a 128 x 128 tile 0.85; what decides is how many
+        // rounds of tiles the shape needs and how many rows its padding wastes.  The ADD epilogue cuts a
+        // last round into K parts, so its rounds count as fractions.
+        const bool parts = epi == TB_EPI_ADD && g_tail_split;
+        auto rounds = [&](long long tiles, int workers) {
+            const double r = parts ? (double)tiles / workers : (double)((tiles + workers - 1) / workers);
+            return r < 0.125 ? 0.125 : r;
+        };
+        const long long m128 = (M + 127) / 128, m256 = (M + 255) / 256;
+        const double t_pair = pairs_max > 0 ? rounds(m256 * ((N + 255) / 256), pairs_max) * 1.0 : 1e30;
+        const double t_256 = N >= 256 ? rounds(m128 * ((N + 255) / 256), sm_count) * 1.1 : 1e30;
+        const double t_128 = rounds(m128 * ((N + 127) / 128), sm_count) * 0.85;
+        if (t_128 < t_pair && t_128 < t_256) { pairs_max = 0; single_bn = 128; }
+        else if (t_256 < t_pair) pairs_max = 0;
+    }
+    if (!swap && g_plain_tile == 1 && M >= 256 && N >= 256) pairs_max = pair_clusters_for(epi);
+    if (!swap && g_plain_tile == 2) { pairs_max = 0; single_bn = N >= 256 ? 256 : 128; }
+    if (!swap && g_plain_tile == 3) { pairs_max = 0; single_bn = 128; }
     if (pairs_max > 0) {
         a.rows_a = M; a.rows_b = N;
         a.tiles_m = (M + 2 * BM - 1) / (2 * BM); a.tiles_n = (N + PAIR_N - 1) / PAIR_N;
@@ -832,7 +858,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         const int pairs = units < pairs_max ? units : pairs_max;
         rc = launch_pair(epi, ma, mb, a, pairs, stream);
     } else if (!swap) {
-        const int bn = N >= 256 ? 256 : 128;
+        const int bn = single_bn;
         a.rows_a = M; a.rows_b = N;
         a.tiles_m = (M + BM - 1) / BM; a.tiles_n = (N + bn - 1) / bn;
         if (tb_make_map_bf16(&ma, X, M, K, ldx, BM) || tb_make_map_bf16(&mb, W, N, K, K, bn)) return 1;

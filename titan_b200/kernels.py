@@ -314,6 +314,12 @@ def set_gemm_pair(on: bool) -> None:
     tlib().tb_gemm_tc_set_pair(int(bool(on)))
 
 
+def set_gemm_plain_tile(which: int) -> None:
+    """Prompt products: 0 lets the launcher choose the tile shape (default), 1 forces CTA pairs with 256 x 256 tiles
+    (from 256 x 256 outputs on), 2 single CTAs with 128 x 256 tiles, 3 single CTAs with 128 x 128 tiles."""
+    tlib().tb_gemm_tc_set_plain_tile(int(which))
+
+
 def gemm_pair_clusters(epi: int) -> int:
     """CTA pairs the device holds at once for the pair kernel of this epilogue (0: it cannot run)."""
     return int(tlib().tb_gemm_tc_pair_clusters(int(epi)))
