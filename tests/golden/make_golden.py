@@ -80,5 +80,11 @@ def main(root):
     print(f"whole forward: max |reference - plain| = {d:.3e} over logits of magnitude {np.abs(ref['logits']).max():.3f}")
 
 
+def reference_dir():
+    """Where the reference's checkout is looked for: ``TITAN_REFERENCE_DIR``, else a folder ``reference``
+    beside this repository."""
+    return os.environ.get("TITAN_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else reference_dir())

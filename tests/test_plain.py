@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from golden.make_golden import op_inputs
+from golden.make_golden import op_inputs, reference_dir
 from helpers import TINY_A, TINY_C, random_tokens, random_weights
 from plain import qwen3_plain as P
 
@@ -64,11 +64,11 @@ def test_against_the_references_numpy_functions():
     assert np.abs(ref - mine).max() < 1e-6 * np.abs(ref).max()
 
 
-@pytest.mark.skipif(not os.path.isfile("/root/reference/tools/build_synthetic_gguf.py"), reason="reference not mounted")
+@pytest.mark.skipif(not os.path.isfile(os.path.join(reference_dir(), "tools", "build_synthetic_gguf.py")), reason="reference not mounted")
 def test_whole_forward_against_the_reference_when_it_is_mounted():
     from golden.make_golden import load_reference, plain_whole_forward
     with np.errstate(over="ignore"):
-        ref, mine = plain_whole_forward(load_reference("/root/reference"))
+        ref, mine = plain_whole_forward(load_reference(reference_dir()))
     assert np.abs(np.array(ref["logits"]) - mine.numpy()).max() < 1e-6 * np.abs(ref["logits"]).max()
 
 
