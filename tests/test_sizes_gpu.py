@@ -103,3 +103,58 @@ def test_long_prompts_and_decoding_fast_kernels_against_plain_kernels():
         got[name] = torch.cat(rows).float().cpu()
     assert K.wait_errors() == {}
     assert rel_l2(got["fast"], got["plain kernels"]) < TOL["bfloat16"]
+
+
+def _random_configuration(seed):
+    """A Qwen3 configuration drawn at random: head sizes in steps of 16 up to 256, any number of heads and
+    groups (group sizes beyond what the tensor-core kernels take included), widths and vocabularies that are
+    no power of two, windows on some layers."""
+    import random
+    r = random.Random(seed)
+    hd = r.choice([64, 128]) if r.random() < 0.4 else 16 * r.randint(1, 16)
+    nkv = r.choice([1, 1, 2, 3, 4, 5, 8])
+    group = r.choice([1, 2, 3, 4, 4, 5, 7, 8, 16, 20])
+    while nkv * group * hd > 4096:
+        group = max(1, group // 2)
+    layers = r.randint(1, 3)
+    cfg = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=layers,
+               hidden_size=r.choice([512, 1024, 2048]) if r.random() < 0.3 else 8 * r.randint(8, 200),
+               num_attention_heads=nkv * group, num_key_value_heads=nkv, head_dim=hd,
+               intermediate_size=8 * r.randint(8, 400), vocab_size=r.randint(100, 7000),
+               rope_theta=r.choice([1e4, 5e5, 1e6]), rms_norm_eps=r.choice([1e-6, 1e-5, 3e-6]),
+               tie_word_embeddings=r.random() < 0.3, max_position_embeddings=4096)
+    if r.random() < 0.35:
+        cfg["sliding_window"] = r.randint(5, 300)
+        cfg["layer_types"] = [r.choice(["sliding_attention", "full_attention"]) for _ in range(layers)]
+    return cfg, [r.randint(1, 900), r.randint(1, 300), r.randint(1, 64)]
+
+
+@pytest.mark.parametrize("seed", range(2000, 2010))
+def test_random_configurations_against_the_plain_implementation(seed):
+    """Unequal prompts in one step, then single tokens (the shortest request ends earlier), in both dtypes."""
+    from titan_b200 import Engine, StepEntry
+    from titan_b200.config import config_from_dict
+    cfg, lens = _random_configuration(seed)
+    steps = 5
+    w = random_weights(cfg, seed, torch.bfloat16, std=0.03)
+    w32 = {k: v.float() for k, v in w.items()}
+    reqs = [random_tokens(n + steps, cfg["vocab_size"], 7 * n + seed) for n in lens]
+    want = [P.forward_logits(cfg, w32, q) for q in reqs]
+    for dtype in ("bfloat16", "float32"):
+        e = Engine.from_tensors(config_from_dict(cfg), w, dtype=dtype, max_tokens=2048, max_context=1024)
+        slots = [e.alloc_slot() for _ in reqs]
+        out = e.step([StepEntry(s, q[:n], list(range(n))) for s, q, n in zip(slots, reqs, lens)])
+        got, at = [], 0
+        for n in lens:
+            got.append([out[at:at + n]])
+            at += n
+        for d in range(steps):
+            live = [0, 1, 2] if d < 3 else [0, 1]
+            out = e.step([StepEntry(slots[i], [reqs[i][lens[i] + d]], [0]) for i in live])
+            for k, i in enumerate(live):
+                got[i].append(out[k:k + 1])
+        e.check_kernels()
+        for i in range(3):
+            g = torch.cat(got[i]).float().cpu()
+            assert rel_l2(g, want[i][:g.shape[0]]) < TOL[dtype], (cfg, lens, dtype, i)
+        del e
