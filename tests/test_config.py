@@ -39,10 +39,22 @@ def test_missing_key_is_named(key):
     ({"attention_bias": True}, "attention_bias"), ({"rope_scaling": {"type": "yarn"}}, "rope_scaling"),
     ({"hidden_size": 2.5}, "integer"), ({"vocab_size": 0}, "positive"), ({"eos_token_id": 999}, "vocabulary"),
     ({"layer_types": ["full_attention"]}, "layer_types"), ({"architectures": ["NopeForCausalLM"]}, "Qwen3ForCausalLM"),
+    ({"rope_parameters": {"rope_type": "yarn", "factor": 4.0, "rope_theta": 1e6}}, "rope_parameters"),
+    ({"rope_parameters": {"rope_type": "default", "rope_theta": 5.0}}, "disagree"),
+    ({"mlp_bias": True}, "mlp_bias"), ({"partial_rotary_factor": 0.5}, "partial_rotary_factor"),
 ])
 def test_bad_values_are_refused(patch, word):
     with pytest.raises(ConfigError, match=word):
         config_from_dict({**TINY_A, **patch})
+
+
+def test_frequency_base_in_either_key():
+    """Newer files carry the frequency base inside rope_parameters; it is never silently defaulted."""
+    d = {k: v for k, v in TINY_A.items() if k != "rope_theta"}
+    assert config_from_dict({**d, "rope_parameters": {"rope_type": "default", "rope_theta": 123456.0}}).rope_theta == 123456.0
+    assert config_from_dict({**d, "rope_theta": 777.0, "rope_scaling": None, "rope_parameters": None}).rope_theta == 777.0
+    assert config_from_dict({**d, "rope_theta": 777.0, "rope_scaling": {"rope_type": "default"}}).rope_theta == 777.0
+    assert config_from_dict({**TINY_A, "rope_parameters": {"rope_theta": TINY_A["rope_theta"]}}).rope_theta == TINY_A["rope_theta"]
 
 
 def test_windows_per_layer():

@@ -74,10 +74,28 @@ class Qwen3Config:
             raise ConfigError(f"hidden_act '{act}' is not supported (only 'silu')")
         if d.get("attention_bias"):
             raise ConfigError("attention_bias = true is not supported")
-        if d.get("rope_scaling") not in (None, {}):
-            raise ConfigError("rope_scaling is not supported")
+        if d.get("mlp_bias"):
+            raise ConfigError("mlp_bias = true is not supported")
+        if d.get("partial_rotary_factor") not in (None, 1, 1.0):
+            raise ConfigError("partial_rotary_factor other than 1 is not supported")
+        theta = d.get("rope_theta")
+        # the frequency base and a scaling rule travel either as rope_theta + rope_scaling or, in newer
+        # files, together in rope_parameters; only the unscaled ("default") rule is built
+        for key in ("rope_scaling", "rope_parameters"):
+            rule = d.get(key)
+            if rule in (None, {}):
+                continue
+            if not isinstance(rule, dict):
+                raise ConfigError(f"config.json key '{key}' must be an object, found {rule!r}")
+            kind = rule.get("rope_type", rule.get("type", "default"))
+            if kind != "default" or any(k not in ("rope_type", "type", "rope_theta") for k in rule):
+                raise ConfigError(f"{key} {rule!r} is not supported (only the unscaled rotary encoding)")
+            if rule.get("rope_theta") is not None:
+                if theta is not None and float(theta) != float(rule["rope_theta"]):
+                    raise ConfigError(f"rope_theta {theta} and {key}.rope_theta {rule['rope_theta']} disagree")
+                theta = rule["rope_theta"]
         eps = float(d.get("rms_norm_eps", 1e-5))
-        theta = float(d.get("rope_theta", 10000.0))
+        theta = float(10000.0 if theta is None else theta)
         if not eps > 0 or not theta > 0:
             raise ConfigError("rms_norm_eps and rope_theta must be positive")
         vocab = _as_int(d, "vocab_size")
