@@ -420,6 +420,37 @@ def test_sampling_matches_the_plain_sampler(K, parts):
     assert all(got[s][4] in (10, 20) for s in range(steps))   # top_k = 2 of three tied: the two lowest indices
 
 
+@pytest.mark.parametrize("V", [40000, 151936])
+def test_sampling_large_vocabulary_matches_the_plain_sampler(K, V):
+    """Vocabularies of several selection bins and several levels of the ordered search: top_k on the gathered
+    list (up to 1,024 kept) and over the whole row (more), top_p alone, ties at both borders that lie far apart."""
+    from titan_b200.sampling import SamplerParams
+    B = 7 if V < 100000 else 3
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(B, V, generator=g) * 2.5
+    logits[1] = torch.round(logits[1] * 2) / 2                       # thousands of ties everywhere: top_p cuts inside a tie
+    logits[2, 5] = logits[2, V // 2] = logits[2, V - 1] = logits[2].max() + 1   # top_k = 2 of three tied, far apart
+    params = [SamplerParams(0.8, 0.95, 40, 1.0, 3), SamplerParams(1.0, 0.7, 0, 1.0, 4), SamplerParams(1.0, 1.0, 2, 1.0, 5),
+              SamplerParams(1.1, 1.0, 2000, 1.0, 6), SamplerParams(0.9, 0.5, 1024, 1.2, 7), SamplerParams(1.0, 1.0, 0, 1.0, 8),
+              SamplerParams(0.7, 0.9, 1500, 1.0, 9)][:B]
+    context = [torch.randint(0, V, (30,), generator=g).tolist() for _ in range(B)]
+    b = SamplerBench(K, V, B)
+    steps = 4 if V < 100000 else 2
+    got = b.run(logits, params, list(range(20, 20 + B)), context, steps=steps)
+    seen = [set(c) for c in context]
+    agree = total = 0
+    for step in range(steps):
+        for r in range(B):
+            p = params[r]
+            want = P.sample(logits[r], seen[r], p.temperature, p.top_k, p.top_p, p.repetition_penalty,
+                            P.uniform_draw(p.seed_value(), 20 + r, step))
+            total += 1
+            agree += int(want == got[step][r])
+            seen[r].add(got[step][r])
+    assert agree >= total - 1, (agree, total, got)
+    assert all(got[s][2] in (5, V // 2) for s in range(steps))
+
+
 def penalised(row, seen, pen):
     x = row.clone()
     for t in seen:

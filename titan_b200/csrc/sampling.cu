@@ -95,70 +95,170 @@ __device__ u64 block_exclusive_scan(u64 v, u64* smem /* 33 */, u64* total) {
 
 #define SAMPLE_THREADS 1024
 #define FIX_ONE 1099511627776.0f     // 2^40
+#define DIGIT_BINS 4096              // a selection pass sorts by 12 bits of the key (12 + 12 + 8)
+#define LIST_MAX 1024                // top_k up to this many: the kept tokens are gathered, later passes walk the list
 
 struct Shared {
-    u64 hist[256];
+    unsigned hist_lo[DIGIT_BINS], hist_hi[DIGIT_BINS];     // a 64-bit sum per bin, kept as two words (see bin_add)
     u64 scan[33];
     u64 bcast[4];
     float fred[33];
     int ired[33];
     int result;
+    int count;
+    int list_idx[LIST_MAX];
+    float list_x[LIST_MAX];
 };
 
-// Largest key ``thr`` such that the weight of {key >= thr} reaches ``target``; ``above`` = weight of
+// Adds to a bin's 64-bit sum with 32-bit shared-memory atomics (the hardware has those; a 64-bit add in
+// shared memory is a compare-and-swap loop): the low word wraps and its carry goes to the high word.
+__device__ __forceinline__ void bin_add(Shared& sh, int b, u64 w) {
+    const unsigned lo = (unsigned)w, hi = (unsigned)(w >> 32);
+    const unsigned old = atomicAdd(&sh.hist_lo[b], lo);
+    const unsigned carry = (old + lo < old) ? 1u : 0u;
+    if (hi + carry) atomicAdd(&sh.hist_hi[b], hi + carry);
+}
+__device__ __forceinline__ u64 bin_sum(const Shared& sh, int b) { return ((u64)sh.hist_hi[b] << 32) + sh.hist_lo[b]; }
+
+// What a pass walks: every token of the row (values made on the fly), or the tokens that top_k kept.
+struct WholeRow {
+    Row r;
+    __device__ __forceinline__ int size() const { return r.V; }
+    __device__ __forceinline__ int index(int j) const { return j; }
+    __device__ __forceinline__ float value(int j) const { return r.value(j); }
+};
+struct KeptList {                    // in vocabulary order
+    const int* idx; const float* x; int n;
+    __device__ __forceinline__ int size() const { return n; }
+    __device__ __forceinline__ int index(int j) const { return idx[j]; }
+    __device__ __forceinline__ float value(int j) const { return x[j]; }
+};
+
+// Calls body(j, value(j)) for every position of the source, eight loads in flight per thread.
+template <typename Src, typename Body>
+__device__ __forceinline__ void for_each(const Src& src, Body body) {
+    const int n = src.size(), step = blockDim.x;
+    for (int j0 = threadIdx.x; j0 < n; j0 += 8 * step) {
+        float xs[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int j = j0 + u * step;
+            xs[u] = j < n ? src.value(j) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int j = j0 + u * step;
+            if (j < n) body(j, xs[u]);
+        }
+    }
+}
+
+// Largest key ``thr`` such that the weight of {key >= thr} reaches the target; ``above`` = weight of
 // {key > thr}, ``ties`` = weight of {key == thr}.  weight(i, key, x) is 0 for tokens outside the set.
-template <typename WFn>
-__device__ void radix_select(const Row& r, WFn weight, u64 target, Shared& sh, unsigned& thr, u64& above, u64& ties) {
+// The target is target_of(total weight), known after the first pass.  Three passes over the source
+// (12, 12 and 8 bits of the key); the bin that holds the target is found by all threads together.
+template <typename Src, typename WFn, typename TFn>
+__device__ void radix_select(const Src& src, WFn weight, TFn target_of, Shared& sh, unsigned& thr, u64& above,
+                             u64& ties, u64& total, u64& target) {
     unsigned prefix = 0, mask = 0;
     u64 acc_above = 0, sel = 0;
-    for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int b = threadIdx.x; b < 256; b += blockDim.x) sh.hist[b] = 0;
+    total = 0; target = 0;
+    for (int pass = 0; pass < 3; ++pass) {
+        const int shift = pass == 0 ? 20 : (pass == 1 ? 8 : 0);
+        const int bins = pass == 2 ? 256 : DIGIT_BINS;
+        for (int b = threadIdx.x; b < bins; b += blockDim.x) { sh.hist_lo[b] = 0; sh.hist_hi[b] = 0; }
         __syncthreads();
-        for (int i = threadIdx.x; i < r.V; i += blockDim.x) {
-            const float x = r.value(i);
+        for_each(src, [&](int j, float x) {
             const unsigned key = order_key(x);
-            if ((key & mask) != prefix) continue;
-            const u64 w = weight(i, key, x);
-            if (w) atomicAdd(&sh.hist[(key >> shift) & 255u], w);
+            if ((key & mask) != prefix) return;
+            const u64 w = weight(src.index(j), key, x);
+            if (w) bin_add(sh, (int)((key >> shift) & (unsigned)(bins - 1)), w);
+        });
+        __syncthreads();
+        // bins in descending order, a run of them per thread
+        const int per = (bins + blockDim.x - 1) / blockDim.x;
+        const int lo = min(bins, (int)threadIdx.x * per), hi = min(bins, lo + per);
+        u64 mine = 0;
+        for (int rb = lo; rb < hi; ++rb) mine += bin_sum(sh, bins - 1 - rb);
+        u64 all;
+        const u64 before = block_exclusive_scan(mine, sh.scan, &all);
+        if (pass == 0) { total = all; target = target_of(all); }
+        if (threadIdx.x == 0) {         // no bin reaches the target: the lowest bin, as a walk from the top ends
+            sh.bcast[0] = acc_above + all - bin_sum(sh, 0); sh.bcast[1] = 0; sh.bcast[2] = bin_sum(sh, 0);
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            u64 a = acc_above;
-            int b = 255;
-            for (; b > 0; --b) {
-                if (a + sh.hist[b] >= target) break;
-                a += sh.hist[b];
-            }
-            sh.bcast[0] = a; sh.bcast[1] = (u64)b; sh.bcast[2] = sh.hist[b];
+        u64 a = acc_above + before;
+        for (int rb = lo; rb < hi; ++rb) {
+            const int b = bins - 1 - rb;
+            const u64 h = bin_sum(sh, b);
+            if (b > 0 && a < target && a + h >= target) { sh.bcast[0] = a; sh.bcast[1] = (u64)b; sh.bcast[2] = h; }
+            a += h;
         }
         __syncthreads();
         acc_above = sh.bcast[0];
         prefix |= (unsigned)sh.bcast[1] << shift;
-        mask |= 255u << shift;
+        mask |= (unsigned)(bins - 1) << shift;
         sel = sh.bcast[2];
         __syncthreads();
     }
     thr = prefix; above = acc_above; ties = sel;
 }
 
-// Index of the ``need``-th (1-based) token in vocabulary order for which pred(i) holds.
-template <typename PFn>
-__device__ int nth_in_order(int V, PFn pred, u64 need, Shared& sh) {
-    const int per = (V + blockDim.x - 1) / blockDim.x;
-    const int lo = min(V, (int)threadIdx.x * per), hi = min(V, lo + per);
-    u64 cnt = 0;
-    for (int i = lo; i < hi; ++i) cnt += pred(i) ? 1 : 0;
-    u64 total;
-    const u64 before = block_exclusive_scan(cnt, sh.scan, &total);
+// Position j of the source, in its order, at which the running sum of f first exceeds the target
+// (INT_MAX if it never does).  The target is target_of(sum of f over the source).  The source is cut
+// into one run per warp, the run that holds the target into runs again, until a thread holds one
+// position: every level reads coalesced, and all levels together read little more than the source once.
+template <typename Src, typename F, typename TFn>
+__device__ int locate(const Src& src, F f, TFn target_of, Shared& sh, u64& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    int lo = 0, hi = src.size();
+    u64 target = 0;
+    bool have = false;
+    while (hi - lo > (int)blockDim.x) {
+        const int per = (((hi - lo + nwarp - 1) / nwarp) + 31) & ~31;
+        const int clo = min(hi, lo + warp * per), chi = min(hi, clo + per);
+        u64 s = 0;
+        for (int j0 = clo + lane; j0 < chi; j0 += 128) {
+            float xs[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) xs[u] = j0 + 32 * u < chi ? src.value(j0 + 32 * u) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) if (j0 + 32 * u < chi) s += f(j0 + 32 * u, xs[u]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        __syncthreads();
+        if (lane == 0) sh.scan[warp] = s;
+        __syncthreads();
+        if (!have) {
+            u64 all = 0;
+            for (int w = 0; w < nwarp; ++w) all += sh.scan[w];
+            total = all; target = target_of(all); have = true;
+        }
+        u64 a = 0;
+        int c = -1;
+        for (int w = 0; w < nwarp; ++w) {
+            const u64 sw = sh.scan[w];
+            if (c < 0) { if (a + sw > target) c = w; else a += sw; }
+        }
+        __syncthreads();
+        if (c < 0) return INT_MAX;
+        target -= a;
+        lo = min(hi, lo + c * per);
+        hi = min(hi, lo + per);
+    }
+    const int j = lo + (int)threadIdx.x;
+    const u64 v = j < hi ? f(j, src.value(j)) : 0ull;
+    u64 all;
+    const u64 before = block_exclusive_scan(v, sh.scan, &all);
+    if (!have) { total = all; target = target_of(all); }
     if (threadIdx.x == 0) sh.result = INT_MAX;
     __syncthreads();
-    if (cnt && before < need && need <= before + cnt) {
-        u64 seen = before;
-        for (int i = lo; i < hi; ++i)
-            if (pred(i) && ++seen == need) { sh.result = i; break; }
-    }
+    if (v && before <= target && target < before + v) sh.result = j;
     __syncthreads();
-    return sh.result;
+    const int found = sh.result;
+    __syncthreads();
+    return found;
 }
 
 // (value, index) pairs: the larger value wins, the lower index among equals; INT_MAX marks "none yet".
@@ -223,6 +323,48 @@ __global__ void __launch_bounds__(MAX_THREADS) sample_max_kernel(SampleArgs a) {
     }
 }
 
+// top_p over the tokens that ``k1`` keeps, then the draw in vocabulary order; INT_MAX if nothing has mass.
+template <typename Src>
+__device__ int top_p_and_draw(const Src& src, Keep k1, float x_max, float top_p, unsigned u24, Shared& sh) {
+    auto mass = [&](int i, unsigned key, float x) -> u64 {
+        return k1.has(key, i) ? __float2ull_rd(expf(x - x_max) * FIX_ONE) : 0ull;
+    };
+    Keep k2 = k1;                                                  // after top_p
+    if (top_p < 1.0f) {
+        unsigned thr; u64 above, ties, total, target;
+        radix_select(src, mass, [&](u64 all) -> u64 {
+            const u64 t = (u64)ceil((double)top_p * (double)all);
+            return t < 1 ? (all < 1 ? all : 1) : (t > all ? all : t);
+        }, sh, thr, above, ties, total, target);
+        if (total > 0) {
+            // every tie has the same mass q; keep the first ceil((target - above) / q) of them
+            const unsigned bits = (thr & 0x80000000u) ? (thr & 0x7fffffffu) : ~thr;
+            const u64 q = __float2ull_rd(expf(__uint_as_float(bits) - x_max) * FIX_ONE);
+            const u64 n_ties = q ? ties / q : 0;
+            const u64 need = q ? (target - above + q - 1) / q : 0;
+            k2.thr = thr;
+            k2.cut = k1.cut;
+            if (q && need < n_ties) {
+                u64 counted;
+                const int j = locate(src, [&](int j, float x) -> u64 {
+                    const unsigned key = order_key(x);
+                    return (key == thr && k1.has(key, src.index(j))) ? 1 : 0;
+                }, [&](u64) -> u64 { return need - 1; }, sh, counted);
+                k2.cut = j == INT_MAX ? INT_MAX : src.index(j);
+            }
+        }
+    }
+    // the draw: the first token, in vocabulary order, at which the running kept mass exceeds
+    // floor(u * total), u = u24 / 2^24 (from the 128-bit product)
+    u64 total;
+    const int j = locate(src, [&](int j, float x) -> u64 {
+        const unsigned key = order_key(x);
+        const int i = src.index(j);
+        return (k1.has(key, i) && k2.has(key, i)) ? __float2ull_rd(expf(x - x_max) * FIX_ONE) : 0ull;
+    }, [&](u64 all) -> u64 { return (__umul64hi(all, (u64)u24) << 40) | ((all * (u64)u24) >> 24); }, sh, total);
+    return j == INT_MAX ? INT_MAX : src.index(j);
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(SampleArgs a) {
     pdl_launch_dependents();
     pdl_wait();
@@ -270,66 +412,50 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(SampleArgs a) {
     if (token == INT_MAX) token = 0;
 
     if (!greedy) {
-        Keep k1; k1.thr = 0u; k1.cut = INT_MAX;                       // after top_k
         const int top_k = a.top_k[slot];
+        const float top_p = a.top_p[slot];
+        const unsigned u24 = uniform24((u64)a.seed[slot], (u64)a.sequence_id[slot], (u64)a.sample_step[slot]);
+        const WholeRow whole{r};
+        Keep k1; k1.thr = 0u; k1.cut = INT_MAX;                       // after top_k
         if (top_k > 0 && top_k < V) {
-            unsigned thr; u64 above, ties;
-            radix_select(r, [](int, unsigned, float) -> u64 { return 1; }, (u64)top_k, sh, thr, above, ties);
+            unsigned thr; u64 above, ties, total, target;
+            radix_select(whole, [](int, unsigned, float) -> u64 { return 1; }, [&](u64) -> u64 { return (u64)top_k; },
+                         sh, thr, above, ties, total, target);
             k1.thr = thr;
             const u64 need = (u64)top_k - above;
-            if (need < ties)
-                k1.cut = nth_in_order(V, [&](int i) { return order_key(r.value(i)) == thr; }, need, sh);
-        }
-        auto mass = [&](int i, unsigned key, float x) -> u64 {
-            return k1.has(key, i) ? __float2ull_rd(expf(x - x_max) * FIX_ONE) : 0ull;
-        };
-        Keep k2 = k1;                                                  // after top_p
-        const float top_p = a.top_p[slot];
-        if (top_p < 1.0f) {
-            u64 part = 0, total;
-            for (int i = tid; i < V; i += blockDim.x) { const float x = r.value(i); part += mass(i, order_key(x), x); }
-            block_exclusive_scan(part, sh.scan, &total);
-            u64 target = (u64)ceil((double)top_p * (double)total);
-            target = target < 1 ? 1 : (target > total ? total : target);
-            unsigned thr; u64 above, ties;
-            radix_select(r, mass, target, sh, thr, above, ties);
-            if (total > 0) {
-                // every tie has the same mass q; keep the first ceil((target - above) / q) of them
-                const float xt = [&]() { unsigned u = (thr & 0x80000000u) ? (thr & 0x7fffffffu) : ~thr; return __uint_as_float(u); }();
-                const u64 q = __float2ull_rd(expf(xt - x_max) * FIX_ONE);
-                const u64 n_ties = q ? ties / q : 0;
-                const u64 need = q ? (target - above + q - 1) / q : 0;
-                k2.thr = thr;
-                k2.cut = k1.cut;
-                if (q && need < n_ties)
-                    k2.cut = nth_in_order(V, [&](int i) { const unsigned key = order_key(r.value(i)); return key == thr && k1.has(key, i); }, need, sh);
+            if (need < ties) {
+                u64 n_ties;
+                k1.cut = locate(whole, [&](int, float x) -> u64 { return order_key(x) == thr ? 1 : 0; },
+                                [&](u64) -> u64 { return need - 1; }, sh, n_ties);
             }
         }
-        // ---- draw in vocabulary order
-        auto kept_mass = [&](int i) -> u64 {
-            const float x = r.value(i);
-            const unsigned key = order_key(x);
-            return (k1.has(key, i) && k2.has(key, i)) ? __float2ull_rd(expf(x - x_max) * FIX_ONE) : 0ull;
-        };
-        const int per = (V + blockDim.x - 1) / blockDim.x;
-        const int lo = min(V, tid * per), hi = min(V, lo + per);
-        u64 part = 0, total;
-        for (int i = lo; i < hi; ++i) part += kept_mass(i);
-        const u64 before = block_exclusive_scan(part, sh.scan, &total);
-        const unsigned u24 = uniform24((u64)a.seed[slot], (u64)a.sequence_id[slot], (u64)a.sample_step[slot]);
-        // target in [0, total): floor(u * total) with u = u24 / 2^24, from the 128-bit product
-        const u64 target = (__umul64hi(total, (u64)u24) << 40) | ((total * (u64)u24) >> 24);
-        if (tid == 0) sh.result = token;
-        __syncthreads();
-        if (total > 0 && part && before <= target && target < before + part) {
-            u64 run = before;
-            for (int i = lo; i < hi; ++i) {
-                run += kept_mass(i);
-                if (run > target) { sh.result = i; break; }
-            }
+        int drawn;
+        if (top_k > 0 && top_k < V && top_k <= LIST_MAX) {
+            // gather the kept tokens, put them in vocabulary order (a token's place is the number of
+            // kept tokens with a lower index), and finish on the list
+            if (tid == 0) sh.count = 0;
+            __syncthreads();
+            for_each(whole, [&](int j, float x) {
+                if (k1.has(order_key(x), j)) {
+                    const int at = atomicAdd(&sh.count, 1);
+                    if (at < LIST_MAX) { sh.list_idx[at] = j; sh.list_x[at] = x; }
+                }
+            });
+            __syncthreads();
+            const int n = min(sh.count, LIST_MAX);
+            const int my_i = tid < n ? sh.list_idx[tid] : INT_MAX;
+            const float my_x = tid < n ? sh.list_x[tid] : 0.f;
+            int place = 0;
+            for (int u = 0; u < n; ++u) place += sh.list_idx[u] < my_i ? 1 : 0;
+            __syncthreads();
+            if (tid < n) { sh.list_idx[place] = my_i; sh.list_x[place] = my_x; }
+            __syncthreads();
+            Keep all; all.thr = 0u; all.cut = INT_MAX;
+            drawn = top_p_and_draw(KeptList{sh.list_idx, sh.list_x, n}, all, x_max, top_p, u24, sh);
+        } else {
+            drawn = top_p_and_draw(whole, k1, x_max, top_p, u24, sh);
         }
-        __syncthreads();
-        token = sh.result;
+        if (drawn != INT_MAX) token = drawn;
     }
     if (tid == 0) {
         a.out[row] = token;
