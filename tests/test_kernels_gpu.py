@@ -387,8 +387,16 @@ def test_argmax_whole_vocabulary_lowest_index_on_ties(K, V):
     assert got[:3] == [V - 1, 77, 0] and got[3] == int(torch.argmax(torch.nan_to_num(logits[3], nan=-1e30)))
 
 
+@pytest.fixture(params=[0, 1, 2, 8], ids=lambda t: f"team{t}")
+def team(request, K):
+    """CTAs per row in the sampling kernel: by the vocabulary's size (0), one, or a cluster of 2 or 8."""
+    K.set_sample_team(request.param)
+    yield request.param
+    K.set_sample_team(0)
+
+
 @pytest.mark.parametrize("parts", [0, 7])       # the row's maximum by one block, and by seven blocks of uneven slices
-def test_sampling_matches_the_plain_sampler(K, parts):
+def test_sampling_matches_the_plain_sampler(K, parts, team):
     from titan_b200.sampling import SamplerParams
     V, B = 1000, 6
     g = torch.Generator().manual_seed(5)
@@ -420,8 +428,11 @@ def test_sampling_matches_the_plain_sampler(K, parts):
     assert all(got[s][4] in (10, 20) for s in range(steps))   # top_k = 2 of three tied: the two lowest indices
 
 
+_PLAIN_DRAWS = {}
+
+
 @pytest.mark.parametrize("V", [40000, 151936])
-def test_sampling_large_vocabulary_matches_the_plain_sampler(K, V):
+def test_sampling_large_vocabulary_matches_the_plain_sampler(K, V, team):
     """Vocabularies of several selection bins and several levels of the ordered search: top_k on the gathered
     list (up to 1,024 kept) and over the whole row (more), top_p alone, ties at both borders that lie far apart."""
     from titan_b200.sampling import SamplerParams
@@ -442,8 +453,11 @@ def test_sampling_large_vocabulary_matches_the_plain_sampler(K, V):
     for step in range(steps):
         for r in range(B):
             p = params[r]
-            want = P.sample(logits[r], seen[r], p.temperature, p.top_k, p.top_p, p.repetition_penalty,
-                            P.uniform_draw(p.seed_value(), 20 + r, step))
+            key = (V, r, step, tuple(sorted(seen[r])) if p.repetition_penalty > 1 else None)
+            if key not in _PLAIN_DRAWS:          # the plain sampler is slow at these sizes and does not depend on the team
+                _PLAIN_DRAWS[key] = P.sample(logits[r], seen[r], p.temperature, p.top_k, p.top_p, p.repetition_penalty,
+                                             P.uniform_draw(p.seed_value(), 20 + r, step))
+            want = _PLAIN_DRAWS[key]
             total += 1
             agree += int(want == got[step][r])
             seen[r].add(got[step][r])

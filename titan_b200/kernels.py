@@ -274,6 +274,12 @@ def sample(args: SampleArgs, stream: int) -> None:
     _check(lib().tb_sample(byref(args), stream))
 
 
+def set_sample_team(ctas: int) -> None:
+    """CTAs (a thread-block cluster) that share a row that is not greedy: 0 = by the size of the vocabulary
+    (8 from 65,536 tokens, 4 from 16,384, else 1), or 1, 2, 4, 8."""
+    lib().tb_sample_set_team(int(ctas))
+
+
 def mark_seen(tokens, seq_of, slot_of_seq, seen: torch.Tensor, T: int, stream: int) -> None:
     _check(lib().tb_mark_seen(tokens.data_ptr(), seq_of.data_ptr(), slot_of_seq.data_ptr(), seen.data_ptr(),
                               seen.shape[1], T, stream))
