@@ -319,6 +319,23 @@ def micro():
     for n, v in found.items():
         print(f"prompt of {M} tokens, {n}: " + ", ".join(f"{x:.1f}" for x in v) + " us (rows: " +
               ("2048, 2048, 1" if n == "rmsnorm" else "2048") + ")", flush=True)
+    # sampling alone: one call of the device sampler on float32 logits of the model's vocabulary
+    from titan_b200.cache import SlotState
+    from titan_b200.sampling import DeviceSampler, SamplerParams
+    V = QWEN3_8B["vocab_size"]
+    for B in (1, 8, 64):
+        state = SlotState(B, "cuda")
+        sampler = DeviceSampler(state, B, V, "cuda")
+        slots = list(range(B))
+        slot_t = torch.tensor(slots, dtype=torch.int32, device="cuda")
+        logits = torch.randn(B, V, device="cuda") * 3
+        line = []
+        for name, p in (("greedy", SamplerParams.greedy()), ("temperature", SamplerParams(0.8, 1.0, 0, 1.0, 3)),
+                        ("top_k 40", SamplerParams(0.8, 1.0, 40, 1.0, 3)), ("top_p 0.95", SamplerParams(0.8, 0.95, 0, 1.0, 3)),
+                        ("top_k 40 top_p 0.95 penalty 1.1", SamplerParams(0.8, 0.95, 40, 1.1, 3))):
+            sampler.configure(slots, [p] * B, slots)
+            line.append(f"{name} {timed(lambda: sampler.sample(logits, slot_t, st), 50):.1f}")
+        print(f"sampling, {B} rows of {V}: " + ", ".join(line) + " us", flush=True)
     print("wait errors:", K.gemm_tc_error(), K.attn_tc_error())
     return 0
 
