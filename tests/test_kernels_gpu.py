@@ -465,6 +465,59 @@ def test_sampling_large_vocabulary_matches_the_plain_sampler(K, V, team):
     assert all(got[s][2] in (5, V // 2) for s in range(steps))
 
 
+@pytest.mark.parametrize("case", range(12))
+def test_sampling_on_a_grid_of_tied_logits(K, case):
+    """Logits rounded to a coarse grid: both borders fall inside groups of equal values, zeros come with both signs
+    (one value: -0.0 == 0.0), and a top_k border that cuts a group must not cut the group at the top_p border."""
+    import random
+    from titan_b200.sampling import SamplerParams
+    r = random.Random(case)
+    V, B = r.choice([227, 803, 1446, 2819]), 4
+    g = torch.Generator().manual_seed(case)
+    logits = torch.round(torch.randn(B, V, generator=g) * r.choice([2.0, 6.0]) * 2) / 2
+    assert bool(((logits == 0) & torch.signbit(logits)).any()) and bool(((logits == 0) & ~torch.signbit(logits)).any())
+    params = [SamplerParams(r.choice([0.8, 1.0, 1.7]), r.choice([1.0, 0.9, 0.5, 0.01]), r.choice([V // 2, V // 3, 40, 0, 2000]),
+                            r.choice([1.0, 1.3]), r.randint(0, 99)) for _ in range(B)]
+    K.set_sample_team(r.choice([1, 2, 4]))
+    try:
+        context = [torch.randint(0, V, (10,), generator=g).tolist() for _ in range(B)]
+        got = SamplerBench(K, V, B, parts=r.choice([0, 3])).run(logits, params, list(range(B)), context, steps=3)
+    finally:
+        K.set_sample_team(0)
+    seen = [set(c) for c in context]
+    for step in range(3):
+        for row in range(B):
+            p = params[row]
+            want = P.sample(logits[row], seen[row], p.temperature, p.top_k, p.top_p, p.repetition_penalty,
+                            P.uniform_draw(p.seed_value(), row, step))
+            assert want == got[step][row], (case, row, step, p)
+            seen[row].add(want)
+
+
+def test_sampling_borders_built_by_hand(K, team):
+    """Row 0: the top_k border cuts a group of zeros whose low indices hold -0.0 and whose high indices hold +0.0
+    (one value; the low indices are kept).  Row 1: top_k cuts a group of ties at index 20, and the top_p border
+    needs ALL of a higher group that has a member beyond index 20."""
+    from titan_b200.sampling import SamplerParams
+    V = 64
+    logits = torch.full((2, V), -5.0)
+    logits[0, 0:10] = -0.0
+    logits[0, 10:20] = 0.0
+    logits[0, 20:25] = 1.0
+    logits[1, 50] = 3.0
+    logits[1, 5] = logits[1, 60] = 2.0
+    logits[1, 10] = logits[1, 20] = logits[1, 30] = logits[1, 40] = 1.0
+    params = [SamplerParams(1.0, 1.0, 15, 1.0, 1), SamplerParams(1.0, 0.8, 5, 1.0, 2)]
+    steps = 60
+    got = SamplerBench(K, V, 2).run(logits, params, [0, 1], None, steps=steps)
+    for step in range(steps):
+        for row, p in enumerate(params):
+            want = P.sample(logits[row], set(), p.temperature, p.top_k, p.top_p, 1.0, P.uniform_draw(p.seed_value(), row, step))
+            assert want == got[step][row], (row, step)
+    assert {g[0] for g in got} <= set(range(0, 10)) | set(range(20, 25)) and {g[0] for g in got} & set(range(0, 10))
+    assert {g[1] for g in got} == {50, 5, 60}
+
+
 def penalised(row, seen, pen):
     x = row.clone()
     for t in seen:

@@ -36,9 +36,9 @@ struct SampleArgs {
 
 typedef unsigned long long u64;
 
-__device__ __forceinline__ unsigned order_key(float x) {      // larger float -> larger key; NaN -> 0
+__device__ __forceinline__ unsigned order_key(float x) {      // larger float -> larger key; NaN -> 0; -0 and +0 share a key
     if (x != x) return 0u;
-    const unsigned u = __float_as_uint(x);
+    const unsigned u = x == 0.f ? 0u : __float_as_uint(x);
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
@@ -461,7 +461,7 @@ __device__ int top_p_and_draw(const Team& team, const Src& src, Keep k1, float x
             const u64 n_ties = q ? ties / q : 0;
             const u64 need = q ? (target - above + q - 1) / q : 0;
             k2.thr = thr;
-            k2.cut = k1.cut;
+            k2.cut = INT_MAX;              // (k1 still applies beside k2: its cut is about ties at ITS threshold)
             if (q && need < n_ties) {
                 u64 counted;
                 k2.cut = locate(team, src, [&](int j, float x) -> u64 {
