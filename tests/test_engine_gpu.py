@@ -299,3 +299,35 @@ def test_programmatic_dependent_launch_changes_no_result(worlds):
     finally:
         K.set_pdl(True)
     assert torch.equal(outs[0], outs[1])
+
+
+def test_capture_survives_dead_engines_waiting_for_the_cycle_collector(worlds, monkeypatch):
+    """An engine that is dropped while a reference cycle still holds it owns captured graphs and device memory
+    until Python's cycle collector runs.  If that happens while another engine's decode step is being captured,
+    the capture is invalidated; so the capture collects first and keeps the collector off meanwhile.  Here the
+    collector is held back between engines, and the first launcher of a captured step runs a collection."""
+    import gc
+    from titan_b200 import Engine, SamplerParams, kernels as K
+    w = worlds["A"]
+    prompts = [w.requests[0], w.requests[1]]
+    prepare = K.decode_prepare
+
+    def collect_then_prepare(*a, **k):
+        if torch.cuda.is_current_stream_capturing():
+            gc.collect()
+        return prepare(*a, **k)
+    monkeypatch.setattr(K, "decode_prepare", collect_then_prepare)
+    gc.collect()
+    gc.disable()
+    try:
+        want = None
+        for _ in range(3):
+            e = Engine.from_pretrained(w.folder, dtype="float32", max_tokens=512)
+            e.held_by_a_cycle = [e]                                   # only the cycle collector can free it
+            out = [r.tokens for r in e.generate(prompts, max_tokens=6, params=SamplerParams.greedy(), stop_tokens=[])]
+            assert want is None or out == want
+            want = out
+            del e
+    finally:
+        gc.enable()
+        gc.collect()

@@ -12,6 +12,8 @@ count is frozen at capture time from the then-current position (:2240), which is
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -24,7 +26,7 @@ class DecodeGraph:
     """Captured decode steps for exactly ``B`` sequences (which ones is data, not part of the graph)."""
 
     def __init__(self, engine, B: int):
-        self.engine, self.B = engine, B
+        self._engine, self.B = weakref.ref(engine), B      # no cycle: an engine that is dropped frees its graphs at once
         dev = engine.device
         i32 = lambda n: torch.zeros(n, dtype=torch.int32, device=dev)
         ar = lambda n: torch.arange(n, dtype=torch.int32, device=dev)
@@ -40,6 +42,10 @@ class DecodeGraph:
         self.launches = 0                      # launcher calls inside one replay
         self.host_tokens = torch.zeros(B, dtype=torch.int32).pin_memory()
         self.host_slots = torch.zeros(B, dtype=torch.int32).pin_memory()
+
+    @property
+    def engine(self):
+        return self._engine()
 
     def set_slots(self, slots: Sequence[int]) -> None:
         if self.slots != list(slots):
@@ -65,8 +71,18 @@ class DecodeGraph:
         key = (feed_last, self.engine.sampler.seen is not None)
         g = self.graphs.get(key)
         if g is None:
+            # Nothing may free device memory or destroy another graph while the stream is capturing (that
+            # invalidates the capture), and Python's cycle collector can do both at any allocation when dead
+            # objects that hold tensors or graphs are around: collect them now, and keep it off meanwhile.
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self._body(feed_last)
+            gc.collect()
+            was_enabled = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(g):
+                    self._body(feed_last)
+            finally:
+                if was_enabled:
+                    gc.enable()
             self.graphs[key] = g
         g.replay()
