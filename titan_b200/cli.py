@@ -78,6 +78,20 @@ def _prompts(args) -> List[List[int]]:
 
 
 def main(argv=None) -> int:
+    """Errors of the library's own kinds (configuration, weights, a step's input, a kernel's refusal) end the
+    program with one line and status 1, not a traceback."""
+    from .config import ConfigError
+    from .engine.engine import StepError
+    from .kernels import KernelError
+    from .weights import WeightError
+    try:
+        return _main(argv)
+    except (ConfigError, WeightError, StepError, KernelError, FileNotFoundError) as err:
+        print(f"titan_b200: {type(err).__name__}: {err}", file=sys.stderr)
+        return 1
+
+
+def _main(argv=None) -> int:
     ap = build_parser()
     args = ap.parse_args(argv)
     if args.command in (None, "help"):
