@@ -98,10 +98,16 @@ struct TcArgs {
 // TMA ring depth.  Decode tiles (BN <= 64) take as many stages as still let two CTAs share an SM: the
 // ring is filled before the wait on the previous kernel, so its depth is what bridges kernel boundaries.
 template <int BN> constexpr int stages_for() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 4 : (BN >= 32 ? 5 : 6))); }
+// Swap mode with 65..128 rows of activations: three stages, so that two CTAs share an SM here too and the
+// 192 tiles of the gate-and-up product are resident at once (measured at 96 rows: 59.8 -> 44.0 us).  The
+// bfloat16 store (a short prompt's Q|K|V: 48 tiles, no K slices) keeps the deeper ring of one CTA per SM.
+template <int BN, int EPI, bool SWAP> constexpr int stages_of() {
+    return (SWAP && BN == 128 && EPI != TB_EPI_STORE) ? 3 : stages_for<BN>();
+}
 template <int BN> constexpr int tmem_cols_for() { return BN < 32 ? 32 : BN; }
 constexpr int EPI_TILE_FLOATS = 32 * 33;      // one warp's 32 x 32 transposition tile, padded against bank conflicts
-template <int BN, bool SWAP> constexpr size_t smem_for() {
-    return 1024 /*alignment slack*/ + (size_t)stages_for<BN>() * (BM * BK * 2 + BN * BK * 2) + 256 +
+template <int BN, bool SWAP, int STAGES = stages_for<BN>()> constexpr size_t smem_for() {
+    return 1024 /*alignment slack*/ + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 256 +
            (SWAP ? 0 : 4 * EPI_TILE_FLOATS * sizeof(float));
 }
 
@@ -242,7 +248,7 @@ __device__ __forceinline__ void epilogue_rows(const float* val, float* tile, con
 template <int BN, int EPI, bool SWAP>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs a) {
-    constexpr int STAGES = stages_for<BN>();
+    constexpr int STAGES = stages_of<BN, EPI, SWAP>();
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     constexpr uint32_t TMEM_COLS = tmem_cols_for<BN>();
     extern __shared__ uint8_t smem_raw[];
@@ -664,7 +670,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <int BN, int EPI, bool SWAP>
 int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t stream) {
     static bool configured = false;
-    constexpr size_t smem = smem_for<BN, SWAP>();
+    constexpr size_t smem = smem_for<BN, SWAP, stages_of<BN, EPI, SWAP>()>();
     if (!configured) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, SWAP>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // room for several CTAs per SM
@@ -762,6 +768,8 @@ int launch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const TcAr
 // Reads and clears the error word of the tensor-core kernels (0: none; 1, 2, 3: a wait of the
 // producer, the MMA issuer or the epilogue ran out).  Synchronises the device.
 int g_plain_tile = 0;
+int g_swap_below = 128;
+extern "C" void tb_gemm_tc_set_swap_below(int m) { g_swap_below = m; }
 // Prompt products: 0 chooses the tile shape, 1 forces CTA pairs (256 x 256), 2 single CTAs with 128 x 256, 3 with 128 x 128.
 extern "C" void tb_gemm_tc_set_plain_tile(int which) { g_plain_tile = which; }
 
@@ -799,7 +807,7 @@ extern "C" int tb_gemm_tc_check(int M, int N, int K, int ldx, int ldo, int epi, 
 extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N, int K, int ldx, int ldo, int epi,
                           int splits, cudaStream_t stream) {
     if (tb_gemm_tc_check(M, N, K, ldx, ldo, epi, X, W, out)) return 1;
-    const bool swap = M < 128;
+    const bool swap = M < g_swap_below;
     const int kb = (K + BK - 1) / BK;
     CUtensorMap ma, mb;
     TcArgs a;
@@ -874,8 +882,8 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         const int tiles = (N + BM - 1) / BM;
         int s = 1;
         if (epi == TB_EPI_ADD) {
-            // as many K slices as fill the machine once: two CTAs fit an SM up to BN = 64, one above
-            const int room = (bn <= 64 ? 2 : 1) * sm_count;
+            // as many K slices as fill the machine once
+            const int room = 2 * sm_count;                        // two CTAs fit an SM at every width
             s = splits > 0 ? splits : room / tiles;
             const int max_s = kb / 4 > 0 ? kb / 4 : 1;              // at least four 64-wide blocks per slice
             s = s < 1 ? 1 : (s > max_s ? max_s : s);

@@ -320,6 +320,11 @@ def set_gemm_pair(on: bool) -> None:
     tlib().tb_gemm_tc_set_pair(int(bool(on)))
 
 
+def set_gemm_swap_below(m: int) -> None:
+    """Products with fewer rows than this run in swap mode (weights on the 128-row side): 128 by default, at most 129."""
+    tlib().tb_gemm_tc_set_swap_below(int(m))
+
+
 def set_gemm_plain_tile(which: int) -> None:
     """Prompt products: 0 lets the launcher choose the tile shape (default), 1 forces CTA pairs with 256 x 256 tiles
     (from 256 x 256 outputs on), 2 single CTAs with 128 x 256 tiles, 3 single CTAs with 128 x 128 tiles."""
