@@ -584,6 +584,22 @@ def test_attention_decode_on_tensor_cores(K, nh, nkv, hd, window, ring):
         assert rel_l2(outs[1], want) < 8e-3, chunk
         assert rel_l2(outs[0], outs[2]) < 8e-3, chunk
         assert rel_l2(outs[0], outs[1]) < 1e-5, chunk     # the two merges add the same parts in the same order
+        # lengths named as final before the step: the same numbers by sequence (1), or committed lengths by slot (2);
+        # pages of older positions are then requested before the dependency wait, and nothing else changes
+        committed = torch.zeros(max(slots) + 1, dtype=torch.int32)
+        for sl, n in zip(slots, lens):
+            committed[sl] = n - 1
+        committed = committed.cuda()
+        for early, mode in ((lay.kv_len, 1), (committed, 2)):
+            out = torch.full((B, Q), float("nan"), dtype=torch.bfloat16, device="cuda")
+            d.out, d.early_len, d.early_mode = out.data_ptr(), early.data_ptr(), mode
+            K.attn_decode_mma(d, stream())
+            assert K.attn_mma_error() == 0
+            assert torch.equal(out.float().cpu(), outs[0]), (chunk, mode)
+        committed -= 1                                    # an early length that is not the step's is reported
+        K.attn_decode_mma(d, stream())
+        assert K.attn_mma_error() == 7
+        d.early_len, d.early_mode = None, 0
     d.chunk = 100
     assert not K.attn_decode_mma_accepts(d, torch.bfloat16)
     d.chunk, d.hd = 64, 96

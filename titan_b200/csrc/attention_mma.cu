@@ -37,6 +37,7 @@ struct DecArgs {
     float* scratch;                          // [B][nh][n_splits][hd + 2]
     const int* table; int table_width; int ring_rows; int num_pages;
     const int* slot_of_seq; const int* kv_len;
+    const int* early_len; int early_mode;    // lengths that were final before the step's first kernel (see AttnArgs); 0: none
     int nh; int nkv; int window; float scale_log2;   // scale * log2(e)
     int chunk; int n_splits;
     __nv_bfloat16* out; int out_stride;      // [B][out_stride]: written by the kernel itself when its splits form a cluster
@@ -81,8 +82,12 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
     pdl_launch_dependents();
-    pdl_wait();                                         // lengths, queries and the newest cache row come from earlier kernels
-    const int len = a.kv_len[b];
+    // Queries and the newest cache row come from the kernels just before this one.  The length does too,
+    // unless the caller names a copy that was final before the step's first kernel: then the pages that hold
+    // only older positions are requested before the wait, while those kernels still run.
+    const bool early = a.early_mode != 0;
+    if (!early) pdl_wait();
+    const int len = a.early_mode == 2 ? a.early_len[a.slot_of_seq[b]] + 1 : (early ? a.early_len[b] : a.kv_len[b]);
     if (!CL && split * a.chunk >= len) return;          // uniform over the CTA; the merge skips these splits (in a cluster the CTA stays, with no pages, for the barrier)
     const int group = a.nh / a.nkv;
     const int wlo = a.window > 0 ? max(0, len - a.window) : 0;       // first visible key of position len - 1
@@ -101,7 +106,15 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
             const int* tab = a.table + (size_t)slot * a.table_width;
             const int v_rows = a.num_pages * a.nkv * PAGE;          // rows of the K half
             const uint64_t once = l2_evict_first_policy();          // a step reads every page once
+            // before the wait: the first pages of the ring, but never the page that holds position len - 1
+            // (the last page of the split that ends at len), whose newest row is still being written
+            const int old_pages = n_pages - (hi == len && n_pages > 0 ? 1 : 0);
+            const int ahead = early ? (old_pages < STAGES ? old_pages : STAGES) : 0;
             for (int i = 0; i < n_pages; ++i) {
+                if (early && i == ahead) {
+                    pdl_wait();
+                    if (a.kv_len[b] != len) atomicCAS(&g_attn_error, 0u, 7u);     // the early length was not the step's
+                }
                 const int s = i % STAGES, round = i / STAGES;
                 if (round > 0) mbar_wait(empty + s, (round - 1) & 1, &g_attn_error, 1);
                 const int pos0 = (page0 + i) * PAGE;
@@ -115,6 +128,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
                     tma_load_2d_hint(kd + TILE_BYTES + x * (PAGE * 128), &kv_map, full + s, x * 64, v_rows + row, once);
                 }
             }
+            if (early && ahead >= n_pages) {                // everything was requested ahead: check the length all the same
+                pdl_wait();
+                if (a.kv_len[b] != len) atomicCAS(&g_attn_error, 0u, 7u);
+            }
         }
         if (!CL) return;
     }
@@ -125,6 +142,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     if (warp < DEC_WARPS) {
     const int g = lane >> 2, t = lane & 3;
     uint32_t qf[KS][4];
+    if (early) pdl_wait();
     {
         const __nv_bfloat16* q0 = a.q + (size_t)b * a.q_stride + (size_t)(kh * group) * HD;
 #pragma unroll
@@ -528,6 +546,8 @@ extern "C" int tb_attn_decode_mma(const AttnArgs* args, cudaStream_t stream) {
     d.q = (const __nv_bfloat16*)a.q; d.q_stride = a.q_stride; d.scratch = a.scratch;
     d.table = a.cache.table; d.table_width = a.cache.table_width; d.ring_rows = a.cache.ring_rows; d.num_pages = a.cache.num_pages;
     d.slot_of_seq = a.batch.slot_of_seq; d.kv_len = a.batch.kv_len;
+    d.early_len = a.early_len; d.early_mode = a.early_len ? a.early_mode : 0;
+    TB_REQUIRE(d.early_mode >= 0 && d.early_mode <= 2, "attn_decode_mma: early_mode %d (0, 1 or 2)", d.early_mode);
     d.nh = a.nh; d.nkv = a.nkv; d.window = a.window; d.scale_log2 = a.scale * 1.4426950408889634f;
     d.chunk = a.chunk; d.n_splits = a.n_splits;
     d.out = (__nv_bfloat16*)a.out; d.out_stride = a.out_stride;

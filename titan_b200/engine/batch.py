@@ -73,6 +73,8 @@ class StepLayout:
         self.all_single = all(n == 1 for n in lens)       # a decode step: one token per sequence
         self.all_fresh = bool((starts == 0).all())        # every sequence starts at its first token
         self.h2d_bytes = host.nbytes
+        self.lengths_by_copy = True            # kv_len is final before the step's first kernel runs
+        self.committed_len = None
         self._c: Optional[K.Batch] = None
 
     @classmethod
@@ -88,6 +90,8 @@ class StepLayout:
         self.max_new, self.max_kv_len = max_new, max_kv_len
         self.all_single, self.all_fresh = all_single, all_fresh
         self.h2d_bytes = 0
+        self.lengths_by_copy = False           # a kernel of the step writes kv_len ...
+        self.committed_len = None              # ... as committed_len[slot] + 1, if the owner names that array (by slot)
         self._c = None
         return self
 

@@ -35,6 +35,7 @@ class DecodeGraph:
         self.layout = StepLayout.from_device_arrays(
             self.tokens, ar(B), self.pos_of, self.slot_of_seq, ar(B + 1), self.start_pos, self.kv_len, ar(B),
             max_new=1, max_kv_len=engine.max_context, all_single=True, all_fresh=False)
+        self.layout.committed_len = engine.cache.state.seq_len     # kv_len = committed length + 1, known before the step
         self.options = dict(engine.step_options, fixed_splits=True)
         self.scratch: Dict[str, torch.Tensor] = {}
         self.graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}

@@ -47,6 +47,7 @@ class EngineOptions:
     attention: str = "fast"           # "plain": the any-size attention kernels even where a tensor-core one fits
     qkv: str = "split"                # decode steps: "fused" runs projection + head norm + rotary + append as one kernel (cluster sums, deterministic; measured slower), "split" as three
     attn_chunk: int = 256             # keys per split of decode attention
+    early_pages: bool = True          # decode attention requests pages of older positions before it waits for the kernels before it
     decode_graphs: bool = True        # replay single-token steps as CUDA graphs once a batch size has run eagerly
     device: str = "cuda:0"
 
@@ -72,6 +73,7 @@ class Engine:
         self.sampler = DeviceSampler(self.cache.state, max_slots, self.spec.vocab_size, self.device)
         self.scratch: Dict[str, torch.Tensor] = {}
         self.step_options = {"gemm": options.gemm, "attention": options.attention, "qkv": options.qkv, "attn_chunk": options.attn_chunk,
+                             "early_pages": options.early_pages,
                              "max_context": self.cache.max_context,
                              "sm_count": torch.cuda.get_device_properties(self.device).multi_processor_count}
         self.h2d_bytes = 0

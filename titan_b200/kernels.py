@@ -48,7 +48,8 @@ class AttnArgs(Structure):
     _fields_ = [("q", c_void_p), ("q_stride", c_int), ("kv_new", c_void_p), ("kv_stride", c_int),
                 ("out", c_void_p), ("out_stride", c_int), ("cache", KvView), ("batch", Batch),
                 ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("window", c_int), ("scale", c_float),
-                ("chunk", c_int), ("n_splits", c_int), ("scratch", c_void_p)]
+                ("chunk", c_int), ("n_splits", c_int), ("scratch", c_void_p),
+                ("early_len", c_void_p), ("early_mode", c_int)]
 
 
 class SampleArgs(Structure):

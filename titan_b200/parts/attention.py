@@ -193,6 +193,11 @@ class AttentionMixer(Mixer):
                 scratch = ctx.scratch["attn_partials"] = torch.empty(need, dtype=torch.float32, device=ctx.device)
             aa.kv_new, aa.kv_stride = None, 0
             aa.chunk, aa.n_splits, aa.scratch = chunk, splits, scratch.data_ptr()
+            if ctx.options.get("early_pages", True):       # lengths the kernel may read before its predecessors end
+                if lay.lengths_by_copy:
+                    aa.early_len, aa.early_mode = lay.kv_len.data_ptr(), 1
+                elif lay.committed_len is not None:
+                    aa.early_len, aa.early_mode = lay.committed_len.data_ptr(), 2
             if fast and K.attn_decode_mma_accepts(aa, q_buf.dtype):
                 K.attn_decode_mma(aa, ctx.stream)
             else:
