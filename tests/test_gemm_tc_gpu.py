@@ -33,12 +33,12 @@ def cta_mode(request, K):
     K.set_gemm_plain_tile(0)
 
 
-@pytest.mark.parametrize("M,N,Kd", SHAPES + [(256, 256, 64), (300, 700, 136), (520, 264, 1032)])
+@pytest.mark.parametrize("M,N,Kd", SHAPES + [(256, 256, 64), (300, 700, 136), (520, 264, 1032), (130, 512, 128), (255, 1000, 264)])
 def test_all_epilogues(K, M, N, Kd, cta_mode):
     if cta_mode != "auto" and M < 128:
         pytest.skip("decode-sized products have one kernel")
-    if cta_mode == "pairs" and (M < 256 or N < 256):
-        pytest.skip("pairs are only used from 256 x 256 outputs on")
+    if cta_mode == "pairs" and (M <= 128 or N < 256):
+        pytest.skip("pairs are only used from 129 rows and 256 columns on")
     g = torch.Generator().manual_seed(M + N + Kd)
     x = torch.randn(M, Kd, generator=g).to(torch.bfloat16)
     w = (torch.randn(N, Kd, generator=g) * 0.1).to(torch.bfloat16)

@@ -7,12 +7,13 @@
 // so that in decode the 128-row side of the instruction is filled by weight rows and the batch is the
 // narrow side (BN = 16..128).
 //
-// Plain mode is persistent.  From 256 x 256 outputs on it runs on PAIRS of CTAs (gemm_tc_pair_kernel, a
+// Plain mode is persistent.  From 129 rows and 256 columns on it runs on PAIRS of CTAs (gemm_tc_pair_kernel, a
 // cluster of two, tcgen05.mma.cta_group::2 with M = 256: see the comment above that kernel); smaller
 // outputs run on single CTAs (gemm_tc_persistent_kernel: one CTA per SM walks over 128 x 256 tiles).
 // In both the accumulator is double buffered in tensor memory, so the epilogue of a tile overlaps the
 // MMAs of the next, and the tiles of a last, partly filled round can be cut along K for the ADD
-// epilogue (struct Segments).  Swap mode (gemm_tc_kernel) is one tile per CTA with two CTAs per SM; it
+// epilogue (struct Segments).  Swap mode (gemm_tc_kernel) is one tile per CTA with two CTAs per SM (the
+// ring is six to three stages deep, by the tile's width); it
 // can cut K into slices (grid.z), each CTA adding its partial sum into a float32 output with atomics, to
 // fill the machine once when N / 128 is small; its weights are loaded with the L2 evict-first hint.
 //
@@ -832,7 +833,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         }
         return best;
     };
-    int pairs_max = (!swap && g_pair && M >= 256 && N >= 256) ? pair_clusters_for(epi) : 0;
+    int pairs_max = (!swap && g_pair && M > 128 && N >= 256) ? pair_clusters_for(epi) : 0;
     int single_bn = N >= 256 ? 256 : 128;
     if (!swap && M < 1024) {
         // Which tile shape is fastest for this output (from 1,024 rows on: pairs).  Measured at M = 128 .. 1024: where rows are few, a CTA
@@ -852,7 +853,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         if (t_128 < t_pair && t_128 < t_256) { pairs_max = 0; single_bn = 128; }
         else if (t_256 < t_pair) pairs_max = 0;
     }
-    if (!swap && g_plain_tile == 1 && M >= 256 && N >= 256) pairs_max = pair_clusters_for(epi);
+    if (!swap && g_plain_tile == 1 && M > 128 && N >= 256) pairs_max = pair_clusters_for(epi);
     if (!swap && g_plain_tile == 2) { pairs_max = 0; single_bn = N >= 256 ? 256 : 128; }
     if (!swap && g_plain_tile == 3) { pairs_max = 0; single_bn = 128; }
     if (pairs_max > 0) {
