@@ -129,7 +129,7 @@ def replay_in_batches(e, requests, batch_size, prompt_part):
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_batches_of_unequal_lengths_with_slots_used_again(worlds, name, dtype):
     w = worlds[name]
-    e = w.engine(dtype, max_slots=2, max_tokens=512)
+    e = w.engine(dtype, max_slots=2, max_tokens=512, mark_freed_pages=True)     # a stale row of an earlier owner would show
     order = [3, 0, 2, 1]                               # long with short, so the short one leaves early
     reqs = [w.requests[i] for i in order]
     for part in (0.5, 1.0):

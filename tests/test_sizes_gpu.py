@@ -84,9 +84,9 @@ def test_long_prompts_and_decoding_fast_kernels_against_plain_kernels():
     from titan_b200 import Engine, StepEntry, kernels as K
     from titan_b200.config import config_from_dict
     w = random_weights(MID, 12, torch.bfloat16, std=0.03)
-    engines = {"fast": Engine.from_tensors(config_from_dict(MID), w, dtype="bfloat16", max_tokens=3 * 3072, max_context=3072),
-               "plain kernels": Engine.from_tensors(config_from_dict(MID), w, dtype="bfloat16", max_tokens=3 * 3072, max_context=3072,
-                                                    gemm="plain", attention="plain")}
+    kw = dict(dtype="bfloat16", max_tokens=3 * 3072, max_context=3072, mark_freed_pages=True)    # a stale row of the round before would show
+    engines = {"fast": Engine.from_tensors(config_from_dict(MID), w, **kw),
+               "plain kernels": Engine.from_tensors(config_from_dict(MID), w, gemm="plain", attention="plain", **kw)}
     got = {}
     for name, e in engines.items():
         rows = []

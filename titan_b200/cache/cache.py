@@ -46,10 +46,11 @@ class SlotState:
 
 class SequenceCache:
     def __init__(self, needs: Sequence[Optional[CacheNeed]], max_tokens: int, max_slots: int,
-                 max_context: int, dtype: torch.dtype, device, page_size: int = PAGE_SIZE):
+                 max_context: int, dtype: torch.dtype, device, page_size: int = PAGE_SIZE, mark_freed: bool = False):
         if max_tokens <= 0 or max_context <= 0:
             raise CacheError("max_tokens and max_context must be positive")
         self.page_size = page_size
+        self.mark_freed = mark_freed           # a debugging aid: freed pages are overwritten with a large value
         self.num_pages = -(-max_tokens // page_size)
         self.max_context = min(max_context, self.num_pages * page_size)
         self.max_slots = max_slots
@@ -93,7 +94,7 @@ class SequenceCache:
         del self.length[slot]
         for g in self.groups:
             if isinstance(g, KVGroup):
-                g.release(slot)
+                g.release(slot, self.mark_freed)
 
     def is_live(self, slot: int) -> bool:
         return self.slots.is_held(slot)

@@ -43,6 +43,9 @@ class CacheNeed:
         return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.state_shape, self.state_dtype)
 
 
+STALE_MARK = 3.0e4        # what a freed page holds when the cache is asked to mark freed pages
+
+
 class KVGroup:
     def __init__(self, need: CacheNeed, layers: List[int], num_pages: int, page_size: int,
                  max_slots: int, max_context: int, dtype: torch.dtype, device):
@@ -85,8 +88,15 @@ class KVGroup:
         self.table_host[slot, first:len(have)] = torch.tensor(have[first:], dtype=torch.int32)
         self.table[slot, first:len(have)].copy_(self.table_host[slot, first:len(have)], non_blocking=True)
 
-    def release(self, slot: int) -> None:
-        for p in self.pages_of.pop(slot, []):
+    def release(self, slot: int, mark: bool = False) -> None:
+        """Give the slot's pages back.  ``mark``: first overwrite them with a large finite value, so that a
+        later read of a row that its new owner never wrote shows in the result (not NaN or infinity: the
+        tensor-core kernels multiply rows past a sequence's end by a weight of zero)."""
+        pages = self.pages_of.pop(slot, [])
+        if mark and pages:
+            idx = torch.tensor(pages, dtype=torch.long, device=self.storage.device)
+            self.storage.index_fill_(2, idx, STALE_MARK)
+        for p in pages:
             self.pool.give_back(p)
 
     def layer_storage(self, index_in_group: int) -> torch.Tensor:

@@ -47,6 +47,7 @@ class EngineOptions:
     attention: str = "fast"           # "plain": the any-size attention kernels even where a tensor-core one fits
     qkv: str = "split"                # decode steps: "fused" runs projection + head norm + rotary + append as one kernel (cluster sums, deterministic; measured slower), "split" as three
     attn_chunk: int = 256             # keys per split of decode attention
+    mark_freed_pages: bool = False    # debugging: pages of a freed slot are overwritten with a large finite value, so a stale read shows
     early_pages: bool = True          # decode attention requests pages of older positions before it waits for the kernels before it
     decode_graphs: bool = True        # replay single-token steps as CUDA graphs once a batch size has run eagerly
     device: str = "cuda:0"
@@ -69,7 +70,7 @@ class Engine:
         max_context = min(options.max_context or num_pages * PAGE_SIZE, num_pages * PAGE_SIZE)
         max_slots = options.max_slots or max(1, min(num_pages, (16 << 20) // max(1, -(-max_context // PAGE_SIZE))))
         self.cache = SequenceCache(self.model.cache_needs(), options.max_tokens, max_slots, max_context,
-                                   self.dtype, self.device)
+                                   self.dtype, self.device, mark_freed=options.mark_freed_pages)
         self.sampler = DeviceSampler(self.cache.state, max_slots, self.spec.vocab_size, self.device)
         self.scratch: Dict[str, torch.Tensor] = {}
         self.step_options = {"gemm": options.gemm, "attention": options.attention, "qkv": options.qkv, "attn_chunk": options.attn_chunk,
