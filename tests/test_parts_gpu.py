@@ -380,3 +380,167 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding(dtype):
     for i in range(2):
         assert rel_l2(torch.cat(got[i]).cpu(), want[i]) < TOL[dtype]
         e.free_slot(slots[i])
+
+
+# --------------------------------------------------------------------------- #
+# A layer that reads another layer's cache: it has a query projection only and attends over the keys and
+# values that the named layer wrote.  The architecture is defined here; the package knows nothing of it.
+# --------------------------------------------------------------------------- #
+class SharedCacheConfig:
+    def __init__(self, d):
+        self.d = d
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d)
+
+    def to_dict(self):
+        return dict(self.d)
+
+    def to_model_spec(self):
+        from titan_b200.config import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec
+        d = self.d
+        H, nh, nkv, hd = d["width"], d["heads"], d["kv_heads"], d["head"]
+        layers = []
+        for i in range(3):
+            mixer = MixerSpec("attention", H, nh, nkv, hd, qk_norm=NormSpec("rmsnorm", hd, 1e-5, "{}_norm.weight"),
+                              position=PositionSpec("rope", hd, 1e4), cache_from=0 if i == 2 else None, prefix="attn.")
+            layers.append(LayerSpec(i, "pre_norm", mixer, FeedForwardSpec("gated_mlp", H, d["ff"], prefix="ff."),
+                                    NormSpec("rmsnorm", H, 1e-5, "n1.weight"), NormSpec("rmsnorm", H, 1e-5, "n2.weight"), f"blocks.{i}."))
+        return ModelSpec("SharedCacheForCausalLM", H, d["vocab"], tuple(layers), (0, 1, 2),
+                         NormSpec("rmsnorm", H, 1e-5, "final.weight"), embedding="embed.weight", lm_head=None)
+
+
+def shared_cache_plain(d, w, tokens):
+    nh, nkv, hd = d["heads"], d["kv_heads"], d["head"]
+    x = w["embed.weight"][torch.tensor(tokens)]
+    T, pos = len(tokens), torch.arange(len(tokens))
+    kept = {}
+    for i in range(3):
+        p = f"blocks.{i}."
+        h = P.rms_norm(x, w[p + "n1.weight"], 1e-5)
+        q = P.rope_neox(P.rms_norm(P.linear(h, w[p + "attn.q_proj.weight"]).view(T, nh, hd), w[p + "attn.q_norm.weight"], 1e-5), pos, 1e4)
+        if i == 2:
+            k, v = kept[0]                                   # layer 0's keys and values, as its cache holds them
+        else:
+            k = P.rope_neox(P.rms_norm(P.linear(h, w[p + "attn.k_proj.weight"]).view(T, nkv, hd), w[p + "attn.k_norm.weight"], 1e-5), pos, 1e4)
+            v = P.linear(h, w[p + "attn.v_proj.weight"]).view(T, nkv, hd)
+            kept[i] = (k, v)
+        x = x + P.linear(P.causal_attention(q, k, v).reshape(T, nh * hd), w[p + "attn.o_proj.weight"])
+        h = P.rms_norm(x, w[p + "n2.weight"], 1e-5)
+        x = x + P.mlp_part({k_.replace(p + "ff.", "mlp."): v_ for k_, v_ in w.items() if k_.startswith(p + "ff.")}, "", h)
+    return P.linear(P.rms_norm(x, w["final.weight"], 1e-5), w["embed.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("head", [16, 64])            # 64: the tensor-core attention kernels in bfloat16
+def test_a_layer_that_reads_another_layers_cache(dtype, head):
+    from titan_b200 import Engine, StepEntry, register_architecture
+    from titan_b200.parts import declare_weights
+    register_architecture("SharedCacheForCausalLM", SharedCacheConfig)
+    d = {"architectures": ["SharedCacheForCausalLM"], "width": 64, "heads": 4, "kv_heads": 2, "head": head, "ff": 96, "vocab": 150}
+    cfg = SharedCacheConfig(d)
+    g = torch.Generator().manual_seed(9)
+    w = {}
+    for s in declare_weights(cfg.to_model_spec()):
+        t = torch.randn(s.shape, generator=g) * (0.1 if s.role == "vector" else 0.1) + (1.0 if s.role == "vector" else 0.0)
+        w[s.name] = t.to(torch.bfloat16)
+    assert "blocks.2.attn.k_proj.weight" not in w and "blocks.2.attn.k_norm.weight" not in w and "blocks.2.attn.q_norm.weight" in w
+    e = Engine.from_tensors(cfg, w, dtype=dtype, max_tokens=1024, max_slots=2)
+    assert len(e.cache.groups) == 1 and sum(n is not None for n in e.model.cache_needs()) == 2     # two layers own a cache, one borrows
+    w32 = {k: v.float() for k, v in w.items()}
+    reqs = [random_tokens(150, 150, 1), random_tokens(40, 150, 2)]
+    want = [shared_cache_plain(d, w32, r) for r in reqs]
+    slots = [e.alloc_slot(), e.alloc_slot()]
+    cut = [100, 7]
+    out = e.step([StepEntry(slots[i], reqs[i][:cut[i]], list(range(cut[i]))) for i in range(2)])
+    got = [[out[:cut[0]]], [out[cut[0]:]]]
+    at = list(cut)
+    while any(a < len(r) for a, r in zip(at, reqs)):
+        live = [i for i in range(2) if at[i] < len(reqs[i])]
+        out = e.step([StepEntry(slots[i], [reqs[i][at[i]]], [0]) for i in live])
+        for k, i in enumerate(live):
+            got[i].append(out[k:k + 1])
+            at[i] += 1
+    for i in range(2):
+        assert rel_l2(torch.cat(got[i]).cpu(), want[i]) < TOL[dtype], i
+        e.free_slot(slots[i])
+
+
+# --------------------------------------------------------------------------- #
+# A toy norm (mean-centred, with a bias), defined and registered here only.
+# --------------------------------------------------------------------------- #
+def toy_norm_part():
+    from titan_b200.parts import NORMS, Norm
+    from titan_b200.weights import WeightSpec
+
+    class CentredNorm(Norm):
+        def __init__(self, spec):
+            self.spec = spec
+
+        def weight_specs(self, prefix):
+            name = prefix + self.spec.weight
+            return [WeightSpec(name, (self.spec.size,), "vector", ("one_plus_normal", 0.1)),
+                    WeightSpec(name.replace(".weight", ".bias"), (self.spec.size,), "vector", ("normal", 0.1))]
+
+        def bind(self, get):
+            self.weight, self.bias = get(self.spec.weight), get(self.spec.weight.replace(".weight", ".bias"))
+
+        def forward(self, x, ctx, rows=None):
+            if rows is not None:
+                x = x[rows.long()]
+            c = x - x.mean(dim=1, keepdim=True)                                   # float32 throughout
+            y = c * torch.rsqrt(c.pow(2).mean(dim=1, keepdim=True) + self.spec.eps) * self.weight + self.bias
+            return y.to(ctx.dtype)
+    NORMS.register("toy_centred", CentredNorm)
+
+
+class ToyNormConfig(SharedCacheConfig):
+    def to_model_spec(self):
+        from titan_b200.config import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec
+        d, H = self.d, self.d["width"]
+        norm = lambda name: NormSpec("toy_centred", H, 1e-4, name)
+        layers = [LayerSpec(i, "pre_norm", MixerSpec("attention", H, 2, 1, 32, position=PositionSpec("rope", 32, 1e4), prefix="attn."),
+                            FeedForwardSpec("gated_mlp", H, d["ff"], prefix="ff."), norm("n1.weight"), norm("n2.weight"), f"blocks.{i}.")
+                  for i in range(2)]
+        return ModelSpec("ToyNormForCausalLM", H, d["vocab"], tuple(layers), (0, 1), norm("final.weight"),
+                         embedding="embed.weight", lm_head=None)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_norm(dtype):
+    from titan_b200 import Engine, StepEntry, register_architecture
+    from titan_b200.parts import declare_weights
+    toy_norm_part()
+    register_architecture("ToyNormForCausalLM", ToyNormConfig)
+    d = {"architectures": ["ToyNormForCausalLM"], "width": 56, "ff": 72, "vocab": 90}
+    cfg = ToyNormConfig(d)
+    g = torch.Generator().manual_seed(3)
+    w = {}
+    for s in declare_weights(cfg.to_model_spec()):
+        one = 1.0 if s.name.endswith("weight") and s.role == "vector" else 0.0
+        w[s.name] = (torch.randn(s.shape, generator=g) * 0.1 + one).to(torch.bfloat16)
+
+    def norm(x, name):
+        c = x - x.mean(dim=1, keepdim=True)
+        return c * torch.rsqrt(c.pow(2).mean(dim=1, keepdim=True) + 1e-4) * w32[name] + w32[name.replace(".weight", ".bias")]
+
+    def plain(tokens):
+        x = w32["embed.weight"][torch.tensor(tokens)]
+        T, pos = len(tokens), torch.arange(len(tokens))
+        for i in range(2):
+            p = f"blocks.{i}."
+            h = norm(x, p + "n1.weight")
+            q = P.rope_neox(P.linear(h, w32[p + "attn.q_proj.weight"]).view(T, 2, 32), pos, 1e4)
+            k = P.rope_neox(P.linear(h, w32[p + "attn.k_proj.weight"]).view(T, 1, 32), pos, 1e4)
+            v = P.linear(h, w32[p + "attn.v_proj.weight"]).view(T, 1, 32)
+            x = x + P.linear(P.causal_attention(q, k, v).reshape(T, 64), w32[p + "attn.o_proj.weight"])
+            x = x + P.mlp_part({k_.replace(p + "ff.", "mlp."): v_ for k_, v_ in w32.items() if k_.startswith(p + "ff.")}, "", norm(x, p + "n2.weight"))
+        return P.linear(norm(x, "final.weight"), w32["embed.weight"])
+    e = Engine.from_tensors(cfg, w, dtype=dtype, max_tokens=256, max_slots=1)
+    w32 = {k: v.float() for k, v in w.items()}
+    toks = random_tokens(40, 90, 5)
+    s = e.alloc_slot()
+    rows = [e.step([StepEntry(s, toks[:25], list(range(25)))])] + [e.step([StepEntry(s, [t], [0])]) for t in toks[25:]]
+    e.free_slot(s)
+    assert rel_l2(torch.cat(rows).cpu(), plain(toks)) < TOL[dtype]
