@@ -544,3 +544,73 @@ def test_a_toy_norm(dtype):
     rows = [e.step([StepEntry(s, toks[:25], list(range(25)))])] + [e.step([StepEntry(s, [t], [0])]) for t in toks[25:]]
     e.free_slot(s)
     assert rel_l2(torch.cat(rows).cpu(), plain(toks)) < TOL[dtype]
+
+
+# --------------------------------------------------------------------------- #
+# A toy arrangement: mixer and feed-forward read the same normed input and both add to the stream.
+# --------------------------------------------------------------------------- #
+def toy_parallel_block():
+    from titan_b200.parts import BLOCKS
+    from titan_b200.parts.block import PreNormBlock
+
+    class ParallelBlock(PreNormBlock):
+        def parts(self):
+            return (self.mixer_norm, self.mixer, self.feed_forward)          # one norm: no weights for a second
+
+        def forward(self, x, ctx, cache):
+            h = self.mixer_norm.forward(x, ctx)
+            self.mixer.forward(h, ctx, cache, x)
+            self.feed_forward.forward(h, ctx, x)
+    BLOCKS.register("toy_parallel", ParallelBlock)
+
+
+class ToyParallelConfig(SharedCacheConfig):
+    def to_model_spec(self):
+        from titan_b200.config import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec
+        d, H = self.d, self.d["width"]
+        layers = [LayerSpec(i, "toy_parallel" if i == 0 else "pre_norm",
+                            MixerSpec("attention", H, 2, 2, 16, position=PositionSpec("rope", 16, 1e4), prefix="attn."),
+                            FeedForwardSpec("gated_mlp", H, d["ff"], prefix="ff."), NormSpec("rmsnorm", H, 1e-5, "n1.weight"),
+                            NormSpec("rmsnorm", H, 1e-5, "n2.weight"), f"blocks.{i}.") for i in range(2)]
+        return ModelSpec("ToyParallelForCausalLM", H, d["vocab"], tuple(layers), (0, 1), NormSpec("rmsnorm", H, 1e-5, "final.weight"),
+                         embedding="embed.weight", lm_head=None)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_arrangement_of_a_block(dtype):
+    from titan_b200 import Engine, StepEntry, register_architecture
+    from titan_b200.parts import declare_weights
+    toy_parallel_block()
+    register_architecture("ToyParallelForCausalLM", ToyParallelConfig)
+    d = {"architectures": ["ToyParallelForCausalLM"], "width": 40, "ff": 64, "vocab": 70}
+    cfg = ToyParallelConfig(d)
+    g = torch.Generator().manual_seed(6)
+    w = {}
+    for s in declare_weights(cfg.to_model_spec()):
+        w[s.name] = (torch.randn(s.shape, generator=g) * 0.1 + (1.0 if s.role == "vector" else 0.0)).to(torch.bfloat16)
+    assert "blocks.0.n2.weight" not in w and "blocks.1.n2.weight" in w
+    w32 = {k: v.float() for k, v in w.items()}
+
+    def plain(tokens):
+        x = w32["embed.weight"][torch.tensor(tokens)]
+        T, pos = len(tokens), torch.arange(len(tokens))
+        for i in range(2):
+            p = f"blocks.{i}."
+            mlp = {k_.replace(p + "ff.", "mlp."): v_ for k_, v_ in w32.items() if k_.startswith(p + "ff.")}
+            h = P.rms_norm(x, w32[p + "n1.weight"], 1e-5)
+            q = P.rope_neox(P.linear(h, w32[p + "attn.q_proj.weight"]).view(T, 2, 16), pos, 1e4)
+            k = P.rope_neox(P.linear(h, w32[p + "attn.k_proj.weight"]).view(T, 2, 16), pos, 1e4)
+            v = P.linear(h, w32[p + "attn.v_proj.weight"]).view(T, 2, 16)
+            a = P.linear(P.causal_attention(q, k, v).reshape(T, 32), w32[p + "attn.o_proj.weight"])
+            if i == 0:
+                x = x + a + P.mlp_part(mlp, "", h)
+            else:
+                x = x + a
+                x = x + P.mlp_part(mlp, "", P.rms_norm(x, w32[p + "n2.weight"], 1e-5))
+        return P.linear(P.rms_norm(x, w32["final.weight"], 1e-5), w32["embed.weight"])
+    e = Engine.from_tensors(cfg, w, dtype=dtype, max_tokens=256, max_slots=1)
+    toks = random_tokens(30, 70, 8)
+    s = e.alloc_slot()
+    rows = [e.step([StepEntry(s, toks[:20], list(range(20)))])] + [e.step([StepEntry(s, [t], [0])]) for t in toks[20:]]
+    e.free_slot(s)
+    assert rel_l2(torch.cat(rows).cpu(), plain(toks)) < TOL[dtype]
