@@ -3,12 +3,15 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
-Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 with every sequence near the
-benchmark context length (device time, CUDA events around K decode steps); ``e2e`` is the same steps
-through the Python entry point with host tokens in and out; ``prefill`` is one 2,048-token prompt;
-``roofline`` divides the bytes a decode step has to read (every weight once, the live cache) by its
-time; ``points`` holds decode at batch 1 and 64.  The step reads far more than the 126 MB L2, so no
-flush is needed between iterations (``config.l2``).
+Prints ONE JSON line.  The workload is the benchmark configuration's: sequences that hold 2,048-token
+prompts in a context of 8,192, decoded one token each per step.  ``value`` is decoded tokens per second at
+batch 8 (device time, CUDA events around K decode steps that start with 2,048 tokens in the cache);
+``e2e`` is the same steps through the Python entry point with host tokens in and out; ``prefill`` is one
+2,048-token prompt; ``roofline`` divides the bytes a decode step has to read (every weight once, the
+live cache) by its time.  ``points`` holds the whole stated run, 256 steps from 2,048 cached tokens, at
+batch 1, 8 and 64 (tokens per second, with ``_ms`` per step and ``_frac`` of the copy bandwidth beside
+each), and batch 8 at the end of the context.  The prompts are really run (no cache is filled by hand).
+The step reads far more than the 126 MB L2, so no flush is needed between iterations (``config.l2``).
 """
 from __future__ import annotations
 
@@ -83,8 +86,8 @@ class ClockSampler:
 
 
 def fill_cache_random(engine, slots, length):
-    """Benchmark set-up: give every slot ``length`` tokens of random keys and values without running
-    the prompts (the timed steps only read them)."""
+    """Set-up of the small profiling case only: give every slot ``length`` tokens of random keys and values
+    without running the prompts."""
     engine.cache.reserve({s: length for s in slots})
     for s in slots:
         engine.cache.commit(s, length)
@@ -92,6 +95,15 @@ def fill_cache_random(engine, slots, length):
     for g in engine.cache.groups:
         if hasattr(g, "pool"):
             g.storage.normal_(0.0, 1.0)
+
+
+def run_prompts(engine, slots, length):
+    """Every slot gets a prompt of ``length`` tokens of its own, eight prompts to a step."""
+    from titan_b200 import StepEntry
+    V = engine.vocab_size
+    for at in range(0, len(slots), 8):
+        part = slots[at:at + 8]
+        engine.step([StepEntry(s, [(13 * i + 977 * s + 5) % V for i in range(length)], []) for s in part])
 
 
 def decode_flops_and_bytes(engine, batch, kv_len):
@@ -111,14 +123,16 @@ def prefill_flops(cfg, layers, T):
     return linear + attn + 2 * H * V                 # LM head on the last row
 
 
-def time_decode(engine, torch, K, batch, kv_start, steps, warmup, e2e: bool):
-    """K timed decode steps at ``batch`` sequences that hold ``kv_start`` tokens at the start.
-    Returns (ms per step by CUDA events, ms per step by wall clock incl. host copies, launcher calls)."""
+def time_decode(engine, torch, K, batch, kv_timed, steps, warmup):
+    """``steps`` timed decode steps of ``batch`` sequences whose caches hold ``kv_timed`` tokens when the first
+    timed step begins: prompts of ``kv_timed - warmup`` tokens are run, then ``warmup`` untimed steps.
+    Returns (ms per step by CUDA events, ms per step by wall clock incl. host copies, launcher calls, bytes
+    copied to and from the device per step)."""
     from titan_b200 import SamplerParams
     slots = [engine.alloc_slot() for _ in range(batch)]
     try:
-        fill_cache_random(engine, slots, kv_start)
         engine.sampler.configure(slots, [SamplerParams.greedy()] * batch, list(range(batch)))
+        run_prompts(engine, slots, kv_timed - warmup)
         tokens = [(7 * i + 1) % engine.vocab_size for i in range(batch)]
         for _ in range(warmup):
             tokens = engine.advance(slots, tokens)
@@ -167,51 +181,65 @@ def run_ours(args):
     pk = peaks()
     cfg = dict(QWEN3_8B)
     cfg["num_hidden_layers"] = args.layers
-    context, B = args.context, args.batch
-    big = max(B, 64 if not args.skip_points else B)
-    engine = Engine.from_random(config_from_dict(cfg), seed=2, dtype="bfloat16", max_tokens=big * context,
-                                max_context=context, max_slots=big, max_batch=big)
-    kv_start = context - (args.steps + args.warmup) - 1
+    context, B, kv0 = args.context, args.batch, args.prompt_tokens
+    point_steps = 0 if args.skip_points else args.point_steps
+    biggest = max(B, 1 if args.skip_points else 64)
+    room = max(biggest * (kv0 + max(args.steps, point_steps) + 64), 8 * context if not args.skip_points else 0)
+    engine = Engine.from_random(config_from_dict(cfg), seed=2, dtype="bfloat16", max_tokens=room,
+                                max_context=context, max_slots=biggest, max_batch=biggest)
+    hbm = pk["hbm_gbs"]
+
+    def measured(batch, kv_timed, steps):
+        ms, wall, launches, h2d, d2h = time_decode(engine, torch, K, batch, kv_timed, steps, args.warmup)
+        gbs = decode_flops_and_bytes(engine, batch, kv_timed + steps // 2) / (ms * 1e-3) / 1e9
+        return ms, wall, launches, h2d, d2h, gbs
+
     clocks = ClockSampler()
     clocks.start()
-    dev_ms, wall_ms, launches, h2d, d2h = time_decode(engine, torch, K, B, kv_start, args.steps, args.warmup, True)
+    dev_ms, wall_ms, launches, h2d, d2h, achieved = measured(B, kv0, args.steps)
     clock_rec = clocks.stop()
     value = B * 1e3 / dev_ms
     e2e = B * 1e3 / wall_ms
-    kv_mid = kv_start + args.warmup + args.steps // 2
-    step_bytes = decode_flops_and_bytes(engine, B, kv_mid)
-    achieved = step_bytes / (dev_ms * 1e-3) / 1e9
     points = {}
-    if not args.skip_points:
-        for b in (1, 64):
-            ms = time_decode(engine, torch, K, b, kv_start, max(4, args.steps // 2), args.warmup, False)[0]
+    if point_steps:
+        for b in (1, 8, 64):                                   # the stated run: 256 steps after 2,048-token prompts
+            ms, _, _, _, _, gbs = measured(b, kv0, point_steps)
             points[f"decode_b{b}"] = round(b * 1e3 / ms, 1)
+            points[f"decode_b{b}_ms"] = round(ms, 4)
+            points[f"decode_b{b}_frac"] = round(gbs / hbm, 4)
+        tail = context - 20 - 1                                # and batch 8 at the end of the context
+        ms, _, _, _, _, gbs = measured(8, tail, 20)
+        points["decode_b8_context_end"] = round(8e3 / ms, 1)
+        points["decode_b8_context_end_ms"] = round(ms, 4)
+        points["decode_b8_context_end_frac"] = round(gbs / hbm, 4)
+        points["steps"] = point_steps
+        points["kv_len_at_context_end"] = tail
     T = args.prefill_tokens
     pre_clocks = ClockSampler()
     pre_clocks.start()
     pre_ms, pre_best = time_prefill(engine, torch, T, 3, 12)       # ~0.4 s back to back: the power cap is reached
     pre_rec = pre_clocks.stop()
     flops = prefill_flops(cfg, args.layers, T)
-    err = max(K.gemm_tc_error(), K.attn_tc_error(), K.attn_mma_error())      # a bounded wait that gave up anywhere (0: none)
+    engine.check_kernels()                                        # raises if a bounded wait gave up anywhere
     line = {
-        "metric": "decode tok/s (Qwen3-8B layer sizes, bf16, batch 8)", "value": round(value, 1), "unit": "tok/s",
+        "metric": "decode tok/s (Qwen3-8B layer sizes, bf16, batch 8, after 2,048-token prompts)", "value": round(value, 1), "unit": "tok/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic: random weights (seed 2), token ids from a fixed pattern, cache of random keys and values",
+        "data": "synthetic: random weights (seed 2), prompts of token ids from a fixed pattern, run through the engine",
         "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_of_model": 36, "hidden": 4096, "heads": 32,
                    "kv_heads": 8, "head_dim": 128, "intermediate": 12288, "vocab": 151936, "global_batch": B,
-                   "seq_len": context, "kv_len_at_first_timed_step": kv_start + args.warmup, "prefill_tokens": T,
-                   "parallelism": "single_gpu", "l2": "inputs_larger_than_l2", "cache_fill": "random",
-                   "peaks": pk["source"]},
+                   "seq_len": context, "kv_len_at_first_timed_step": kv0, "prefill_tokens": T,
+                   "parallelism": "single_gpu", "l2": "inputs_larger_than_l2", "cache_fill": "prompts_run",
+                   "peaks": pk["source"], "points_steps": point_steps},
         "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "prefill": {"value": round(T * 1e3 / pre_ms, 1), "tokens": T, "ms": round(pre_ms, 3),
                     "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
                     "frac_of_sustained_peak": round(flops / (pre_ms * 1e-3) / (pk.get("bf16_tflops_sustained", pk["bf16_tflops"]) * 1e12), 4),
                     "best_ms": round(pre_best, 3), "sm_mhz": pre_rec.get("sm_mhz"), "reasons": pre_rec.get("reasons")},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points, "clocks": clock_rec, "kernel_error": err,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm, "unit": "GB/s",
+                     "frac": round(achieved / hbm, 4)},
+        "points": points, "clocks": clock_rec, "kernel_error": 0,
     }
     print(json.dumps(line))
     return 0
@@ -267,8 +295,6 @@ def micro():
         torch.cuda.synchronize()
         return a.elapsed_time(b) / n * 1e3           # microseconds
 
-    for n in (16, 32, 64, 128, 192, 256):
-        print(f"tcgen05.mma 128 x {n:3d} x 16: {K.mma_probe(n):6.1f} clocks each, back to back on every SM", flush=True)
     H, F = QWEN3_8B["hidden_size"], QWEN3_8B["intermediate_size"]
     QKV = (QWEN3_8B["num_attention_heads"] + 2 * QWEN3_8B["num_key_value_heads"]) * QWEN3_8B["head_dim"]
     shapes = [("qkv", QKV, H, K.EPI_ADD, K.EPI_STORE), ("o", H, H, K.EPI_ADD, K.EPI_ADD),
@@ -343,12 +369,14 @@ def micro():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=36, help="fewer than 36 only where time needs it; both numbers are reported")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--prompt-tokens", type=int, default=2048, help="tokens every sequence holds when the first timed step begins")
+    ap.add_argument("--point-steps", type=int, default=256, help="decode steps of each entry of 'points'")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--profile-case", action="store_true", help="run the small one-layer case used for ncu captures and exit")

@@ -80,3 +80,26 @@ def rel_l2(a, b):
 # implementation by summation order only.  bfloat16: activations are rounded to 8 bits of mantissa
 # (2^-9 relative) at every part's output.
 TOL = {"float32": 5e-5, "bfloat16": 3e-2}
+
+
+def rows_close(got, want, dtype, what="", row_factor=4.0):
+    """The whole tensor within the bound, and every row within ``row_factor`` times the bound: one wrong row
+    among a thousand right ones does not hide in the tensor's norm."""
+    got, want = got.float().cpu(), want.float().cpu()
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} instead of {tuple(want.shape)}"
+    err = rel_l2(got, want)
+    assert err < TOL[dtype], f"{what}: relative error {err:.3e} over the bound {TOL[dtype]:.0e}"
+    g, w = got.double().reshape(-1, got.shape[-1]), want.double().reshape(-1, want.shape[-1])
+    per_row = (g - w).norm(dim=1) / w.norm(dim=1).clamp_min(1e-30)
+    worst = int(per_row.argmax())
+    assert float(per_row[worst]) < row_factor * TOL[dtype], \
+        f"{what}: row {worst} of {g.shape[0]} is off by {float(per_row[worst]):.3e} (bound {row_factor * TOL[dtype]:.0e})"
+
+
+# Mid-size models whose head sizes take the tensor-core attention kernels (the kernels that serving runs).
+MID = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=1024,
+           num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=2816, vocab_size=5000,
+           rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
+MID64 = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=512,
+             num_attention_heads=16, num_key_value_heads=8, head_dim=64, intermediate_size=1408, vocab_size=3000,
+             rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=2048)

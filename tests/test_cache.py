@@ -68,7 +68,7 @@ def test_ring_group_stops_growing():
     s = c.alloc_slot()
     c.reserve({s: 500})
     assert len(c.groups[0].pages_of[s]) == 8 and len(c.groups[1].pages_of[s]) == 2
-    assert c.groups[0].table_host[s, :8].tolist() == c.groups[0].pages_of[s]
+    assert c.groups[0].table[s, :8].tolist() == c.groups[0].pages_of[s]
 
 
 def test_state_is_zeroed_on_alloc():

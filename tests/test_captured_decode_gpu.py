@@ -1,0 +1,114 @@
+"""The path that serving and the benchmark run, against the plain implementation: bfloat16, decode steps
+replayed as CUDA graphs, decode attention on tensor cores (head sizes 128 and 64) with its splits merged
+inside a thread-block cluster, lengths read from the committed per-slot state before the step's earlier
+kernels have ended, K slices of the decode products summed in float32.
+
+Teacher-forced: the tokens fed are the request's own, so every step's logits have a plain counterpart,
+and they are compared row by row.  berniehans/titan checks its captured decode pass the same way, graph
+against stream and token by token (engine/engine-cuda/tests/cuda_graphs_test.rs:143-148,
+engine/engine-core/tests/driver_graph_parity.rs:54-78)."""
+import pytest
+import torch
+
+from helpers import MID, MID64, TOL, random_tokens, random_weights, rel_l2, rows_close
+from plain import qwen3_plain as P
+
+pytestmark = pytest.mark.gpu
+
+STEPS = 100
+PROMPTS = {1: [100], 3: [1, 63, 250], 8: [30, 60, 64, 65, 120, 127, 200, 600]}     # lengths that cross pages (64) and splits (128) on the way
+MODELS = {"hd128": (MID, 21), "hd64": (MID64, 22)}
+
+
+@pytest.fixture(scope="module")
+def models():
+    out = {}
+    for name, (cfg, seed) in MODELS.items():
+        w = random_weights(cfg, seed, torch.bfloat16, std=0.03)
+        out[name] = (cfg, w, {k: v.float() for k, v in w.items()})
+    return out
+
+
+def teacher_forced(engine, reqs, prompt_lens, steps):
+    """Prompts in one step, then ``steps`` single-token steps through Engine.advance (captured from the third
+    step of a batch size on); the logits of every step, per request."""
+    from titan_b200 import SamplerParams
+    B = len(reqs)
+    slots, _ = engine.start([r[:n] for r, n in zip(reqs, prompt_lens)], [SamplerParams.greedy()] * B, list(range(B)))
+    rows = [[engine.last_logits[i:i + 1].clone()] for i in range(B)]
+    for d in range(steps):
+        engine.advance(slots, [r[n + d] for r, n in zip(reqs, prompt_lens)])
+        for i in range(B):
+            rows[i].append(engine.last_logits[i:i + 1].clone())
+    for s in slots:
+        engine.finish(s)
+    engine.check_kernels()
+    return [torch.cat(r).float().cpu() for r in rows]
+
+
+@pytest.mark.parametrize("variant", ["default", "lengths after the wait", "merge through scratch"])
+@pytest.mark.parametrize("B", [1, 3, 8])
+@pytest.mark.parametrize("model", ["hd128", "hd64"])
+def test_captured_decode_steps_against_the_plain_implementation(models, model, B, variant):
+    from titan_b200 import Engine, kernels as K
+    from titan_b200.config import config_from_dict
+    cfg, w, w32 = models[model]
+    lens = PROMPTS[B]
+    reqs = [random_tokens(n + STEPS, cfg["vocab_size"], 300 + 7 * n + B) for n in lens]
+    want = [P.forward_logits(cfg, w32, r)[n - 1:] for r, n in zip(reqs, lens)]
+    kw = dict(dtype="bfloat16", max_tokens=B * 768, max_context=768, mark_freed_pages=True)
+    if variant == "lengths after the wait":
+        kw["early_pages"] = False
+    K.set_attn_decode_cluster(variant != "merge through scratch")
+    try:
+        graph = Engine.from_tensors(config_from_dict(cfg), w, decode_graphs=True, **kw)
+        got = teacher_forced(graph, reqs, lens, STEPS)
+        assert graph.graph_launches > 0
+        for i in range(B):
+            rows_close(got[i], want[i], "bfloat16", f"{model}, batch {B}, {variant}, request {i} (captured)")
+        if variant == "default":
+            eager = Engine.from_tensors(config_from_dict(cfg), w, decode_graphs=False, **kw)
+            plain_steps = teacher_forced(eager, reqs, lens, STEPS)
+            assert eager.graph_launches == 0
+            for i in range(B):
+                rows_close(plain_steps[i], want[i], "bfloat16", f"{model}, batch {B}, request {i} (eager)")
+                rows_close(got[i], plain_steps[i], "bfloat16", f"{model}, batch {B}, request {i} (captured against eager)")
+    finally:
+        K.set_attn_decode_cluster(True)
+
+
+@pytest.mark.parametrize("model", ["hd128", "hd64"])
+def test_decoding_on_the_device_against_the_plain_implementation(models, model):
+    """64 steps with the host out of the loop (every step feeds the token the step before sampled, from the
+    slot's state), one replay at a time so that every token can be read: each must be the plain
+    implementation's greedy choice for the sequence so far, or lose a near-tie to rounding."""
+    from titan_b200 import Engine, SamplerParams
+    from titan_b200.config import config_from_dict
+    cfg, w, w32 = models[model]
+    prompts = [random_tokens(n, cfg["vocab_size"], 900 + n) for n in (70, 3, 129)]
+    e = Engine.from_tensors(config_from_dict(cfg), w, dtype="bfloat16", max_tokens=3 * 256, max_context=256)
+    slots, first = e.start(prompts, [SamplerParams.greedy()] * 3, [0, 1, 2])
+    second = e.advance(slots, first)
+    made = [[a, b] for a, b in zip(first, second)]
+    for _ in range(64):
+        for i, t in enumerate(e.decode_on_device(slots, 1).cpu().tolist()):
+            made[i].append(t)
+    for s in slots:
+        e.finish(s)
+    e.check_kernels()
+    e.cache.check()
+    for p, toks in zip(prompts, made):
+        logits = P.forward_logits(cfg, w32, list(p) + toks)
+        for j, tok in enumerate(toks):
+            row = logits[len(p) - 1 + j]
+            best = int(torch.argmax(row))
+            if tok != best:
+                assert float(row[best] - row[tok]) < 0.05 * float(row.abs().max()), (model, j, tok, best)
+    # and many steps in one call end where one step at a time ends
+    slots, first = e.start(prompts, [SamplerParams.greedy()] * 3, [0, 1, 2])
+    e.advance(slots, first)
+    last = e.decode_on_device(slots, 64).cpu().tolist()
+    for s in slots:
+        e.finish(s)
+    agree = sum(int(a == m[-1]) for a, m in zip(last, made))
+    assert agree >= 2, (last, [m[-1] for m in made])      # float32 sums of K slices add in any order: a near-tie may fall the other way once

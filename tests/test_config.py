@@ -85,6 +85,48 @@ def test_order_and_cache_sharing_are_checked():
     dataclasses.replace(spec, order=(0, 1, 1, 0)).validate()      # a layer may run twice
 
 
+def test_a_reader_must_fit_the_cache_it_reads():
+    """A layer that reads another layer's cache must see exactly what the owner keeps: same kind of mixer, same
+    window (a full-attention reader over a ring would read rows that were overwritten), same head size, a
+    number of query heads that the owner's kv heads divide; and it must run, after its owner."""
+    import dataclasses
+    spec = config_from_dict(TINY_A).to_model_spec()
+    l0, l1 = spec.layers
+    reader = lambda **kw: dataclasses.replace(l1, mixer=dataclasses.replace(l1.mixer, cache_from=0, **kw))
+    dataclasses.replace(spec, layers=(l0, reader())).validate()
+    windowed = dataclasses.replace(l0, mixer=dataclasses.replace(l0.mixer, window=8))
+    with pytest.raises(ConfigError, match="window"):
+        dataclasses.replace(spec, layers=(windowed, reader())).validate()
+    with pytest.raises(ConfigError, match="heads of"):
+        dataclasses.replace(spec, layers=(l0, reader(head_dim=32))).validate()
+    with pytest.raises(ConfigError, match="query heads"):
+        dataclasses.replace(spec, layers=(l0, reader(num_heads=3))).validate()
+    with pytest.raises(ConfigError, match="another kind"):
+        dataclasses.replace(spec, layers=(dataclasses.replace(l0, mixer=dataclasses.replace(l0.mixer, kind="something_else")), reader())).validate()
+    with pytest.raises(ConfigError, match="never runs"):
+        dataclasses.replace(spec, layers=(l0, reader()), order=(0,)).validate()
+    with pytest.raises(ConfigError, match="owns none"):
+        dataclasses.replace(spec, layers=(dataclasses.replace(l0, mixer=dataclasses.replace(l0.mixer, cache_from=1)), reader())).validate()
+
+
+def test_tensor_names_come_from_the_spec():
+    """Which tensors a part binds is its spec's business: the defaults are this architecture's names, another
+    checkpoint layout (a fused q|k|v tensor, a fused gate|up tensor, other names) is a matter of the spec."""
+    import dataclasses
+    from titan_b200.parts import declare_weights
+    spec = config_from_dict(TINY_A).to_model_spec()
+    names = [w.name for w in declare_weights(spec)]
+    assert "model.layers.0.self_attn.q_proj.weight" in names and "model.layers.1.mlp.gate_proj.weight" in names
+    l0 = spec.layers[0]
+    fused = dataclasses.replace(l0, mixer=dataclasses.replace(l0.mixer, names=(("qkv", "wqkv.weight"), ("o", "wo.weight"))),
+                                feed_forward=dataclasses.replace(l0.feed_forward, names=(("gate_up", "w13.weight"), ("down", "w2.weight"))))
+    by_name = {w.name: w.shape for w in declare_weights(dataclasses.replace(spec, layers=(fused, spec.layers[1])))}
+    assert by_name["model.layers.0.self_attn.wqkv.weight"] == ((4 + 2 * 2) * 16, 64)
+    assert by_name["model.layers.0.self_attn.wo.weight"] == (64, 64)
+    assert by_name["model.layers.0.mlp.w13.weight"] == (256, 64) and by_name["model.layers.0.mlp.w2.weight"] == (64, 128)
+    assert not any("layers.0.self_attn.q_proj" in n or "layers.0.mlp.up_proj" in n for n in by_name)
+
+
 def test_load_config_from_folder(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(TINY_B))
     assert load_config(str(tmp_path)).vocab_size == 509

@@ -5,7 +5,7 @@ import os
 import pytest
 import torch
 
-from helpers import TINY, TOL, random_tokens, random_weights, rel_l2, write_folder
+from helpers import TINY, TOL, random_tokens, random_weights, rel_l2, rows_close, write_folder
 from plain import qwen3_plain as P
 
 pytestmark = pytest.mark.gpu
@@ -47,8 +47,7 @@ def worlds(tmp_path_factory):
 
 
 def close(got, want, dtype, what=""):
-    err = rel_l2(got.float().cpu(), want)
-    assert err < TOL[dtype], f"{what}: relative error {err:.3e} over the bound {TOL[dtype]:.0e}"
+    rows_close(got, want, dtype, what)          # the tensor within the bound and every row within four times the bound
 
 
 @pytest.mark.parametrize("name,dtype", CASES)
@@ -221,10 +220,11 @@ def test_greedy_generation_through_the_entry_point(worlds, name, dtype):
     assert e.cache.slots.held_count == 0
 
 
-def test_generation_stops_and_samples_reproducibly(worlds):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_stops_and_samples_reproducibly(worlds, dtype):
     from titan_b200 import SamplerParams
     w = worlds["B"]
-    e = w.engine("float32", max_batch=4)
+    e = w.engine(dtype, max_batch=4)
     params = SamplerParams(temperature=0.8, top_k=0, top_p=1.0, repetition_penalty=1.0, seed=11)
     a = e.generate(w.requests, max_tokens=12, params=params, stop_tokens=[])
     b = e.generate(list(reversed(w.requests)), max_tokens=12, params=params, stop_tokens=[])
@@ -234,12 +234,13 @@ def test_generation_stops_and_samples_reproducibly(worlds):
     assert c[0].tokens == a[0].tokens
     assert [r.tokens for r in e.generate(w.requests, max_tokens=12, params=params, stop_tokens=[])] == [r.tokens for r in a]
     assert all(len(r.tokens) == 12 for r in b)
-    stop = a[1].tokens[3]
-    d = e.generate(w.requests[1:2], max_tokens=12, params=SamplerParams(temperature=0.8, top_k=0, top_p=1.0, repetition_penalty=1.0, seed=11), stop_tokens=[stop])
-    # request 1 now has sequence id 0, so compare against a fresh run with the same id
+    # a stop token: taken from the very run that the stopped run is compared with (request 1 alone has sequence id 0)
     ref = e.generate(w.requests[1:2], max_tokens=12, params=params, stop_tokens=[])[0].tokens
-    if stop in ref:
-        assert d[0].finish_reason == "stop" and d[0].tokens == ref[:ref.index(stop)]
+    stop = ref[5]
+    d = e.generate(w.requests[1:2], max_tokens=12, params=params, stop_tokens=[stop])
+    assert d[0].finish_reason == "stop" and d[0].tokens == ref[:ref.index(stop)]
+    kept = e.generate(w.requests[1:2], max_tokens=12, params=params, stop_tokens=[stop], include_stop=True)
+    assert kept[0].finish_reason == "stop" and kept[0].tokens == ref[:ref.index(stop) + 1]
 
 
 def test_step_errors_leave_the_cache_alone(worlds):

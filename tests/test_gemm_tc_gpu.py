@@ -97,16 +97,6 @@ def test_pairs_are_available(K):
         assert K.gemm_pair_clusters(epi) >= 32
 
 
-def test_mma_probe_runs(K):
-    """The measurement that tile shapes rest on: a 128 x 256 x 16 MMA occupies the tensor pipe for about 128
-    clocks (4,096 multiply-adds per clock and SM); narrow ones cost the issuing thread about as much."""
-    wide, narrow = K.mma_probe(256, 1024), K.mma_probe(16, 1024)
-    assert 100 < wide < 170
-    assert 10 < narrow < wide
-    with pytest.raises(K.KernelError, match="multiple of 16"):
-        K.mma_probe(24)
-
-
 def test_strided_input_rows(K):
     g = torch.Generator().manual_seed(1)
     big = torch.randn(150, 400, generator=g).to(torch.bfloat16).cuda()

@@ -154,8 +154,9 @@ def test_qk_norm_rope_in_place_and_append(K, dtype, nh, nkv, hd, rot):
         a.inp, a.in_stride, a.q_out, a.q_stride = buf.data_ptr(), Q + 2 * KV, buf.data_ptr(), Q + 2 * KV
         a.k_out, a.k_stride = buf.data_ptr() + Q * esz, Q + 2 * KV
         keep = (dev(qw), dev(kw), dev(inv))
-        a.q_w, a.k_w, a.inv_freq = keep[0].data_ptr(), keep[1].data_ptr(), keep[2].data_ptr()
-        a.eps, a.rot, a.nh, a.nkv, a.hd = 1e-5, rot, nh, nkv, hd
+        a.q_w, a.k_w = keep[0].data_ptr(), keep[1].data_ptr()
+        a.rope = K.RotaryArgs(keep[2].data_ptr(), rot, 0.0, 1.0)
+        a.eps, a.nh, a.nkv, a.hd = 1e-5, nh, nkv, hd
         a.pos_of, a.seq_of, a.slot_of_seq = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr()
         a.cache, a.append, a.T = cache.view, append, T
         K.qk_norm_rope(a, DT[dtype], DT[dtype], stream())
@@ -167,57 +168,8 @@ def test_qk_norm_rope_in_place_and_append(K, dtype, nh, nkv, hd, rot):
         ck, cv = cache.get(s, p)
         assert torch.equal(ck, got[t, Q:Q + KV].view(nkv, hd)) and torch.equal(cv, got[t, Q + KV:].view(nkv, hd))
     with pytest.raises(K.KernelError, match="rotary_dim"):
-        a.rot = hd + 2
+        a.rope.rot = hd + 2
         K.qk_norm_rope(a, DT[dtype], DT[dtype], stream())
-
-
-@pytest.mark.parametrize("M,nh,nkv,Kd,ring", [(1, 4, 2, 256, 0), (8, 32, 8, 1024, 0), (13, 3, 1, 520, 0), (16, 6, 3, 4096, 128)])
-def test_fused_qkv_projection_norm_rotary_append(K, M, nh, nkv, Kd, ring):
-    """Projection, head norm, rotation and cache append in one kernel (K slices of a head summed inside a
-    thread-block cluster) against the plain functions: single tokens of M sequences at scattered
-    positions, ragged K, a ring cache; the cache rows of other tokens must stay as they were."""
-    hd, theta, eps = 128, 1e4, 1e-6
-    g = torch.Generator().manual_seed(M * 7 + nh)
-    N = (nh + 2 * nkv) * hd
-    x = torch.randn(M, Kd, generator=g).to(torch.bfloat16)
-    w = (torch.randn(N, Kd, generator=g) * 0.05).to(torch.bfloat16)
-    qw, kw = 1 + 0.1 * torch.randn(hd, generator=g), 1 + 0.1 * torch.randn(hd, generator=g)
-    lens = [int(v) for v in torch.randint(1, 300, (M,), generator=g)]          # after the step; the new token sits at len - 1
-    slots = torch.randperm(M + 2, generator=g)[:M].tolist()
-    pos = torch.tensor([n - 1 for n in lens])
-    full = P.linear(x.float(), w.float())
-    want_q = P.rope_neox(P.rms_norm(full[:, :nh * hd].view(M, nh, hd), qw, eps), pos, theta)
-    want_k = P.rope_neox(P.rms_norm(full[:, nh * hd:(nh + nkv) * hd].view(M, nkv, hd), kw, eps), pos, theta)
-    want_v = full[:, (nh + nkv) * hd:].view(M, nkv, hd)
-    cache = Paged(K, slots, lens, nkv, hd, torch.bfloat16, ring_rows=ring)
-    before = cache.storage.clone()
-    lay = layout_for(slots, [n - 1 for n in lens], [1] * M)
-    k_ = torch.arange(hd // 2, dtype=torch.float64)
-    inv = (torch.tensor(theta, dtype=torch.float64) ** (-2 * k_ / hd)).float()
-    keep = (qw.cuda(), kw.cuda(), inv.cuda(), x.cuda(), w.cuda())
-    q_out = torch.full((M, nh * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
-    a = K.QkArgs()
-    a.inp, a.in_stride, a.q_out, a.q_stride, a.k_out, a.k_stride = None, 0, q_out.data_ptr(), nh * hd, None, 0
-    a.q_w, a.k_w, a.inv_freq = keep[0].data_ptr(), keep[1].data_ptr(), keep[2].data_ptr()
-    a.eps, a.rot, a.nh, a.nkv, a.hd = eps, hd, nh, nkv, hd
-    a.pos_of, a.seq_of, a.slot_of_seq, a.kv_len = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr(), lay.kv_len.data_ptr()
-    a.cache, a.append, a.T, a.zero_in = cache.view, 1, M, 0
-    assert K.gemm_qkv_accepts(keep[3], keep[4], a, torch.bfloat16)
-    K.gemm_qkv(keep[3], keep[4], a, stream())
-    assert K.gemm_qkv_error() == 0
-    assert rel_l2(q_out.float().cpu(), want_q.reshape(M, -1)) < 6e-3
-    changed = torch.zeros_like(before, dtype=torch.bool)
-    for i, (s, p) in enumerate(zip(slots, pos.tolist())):
-        ck, cv = cache.get(s, p)
-        assert rel_l2(ck, want_k[i]) < 6e-3 and rel_l2(cv, want_v[i]) < 6e-3
-        row = p % ring if ring else p
-        page = int(cache.table[s, row // 64])
-        changed[:, page, :, row % 64] = True
-    assert torch.equal(cache.storage[~changed], before[~changed])             # nothing else was written
-    a.hd = 64
-    assert not K.gemm_qkv_accepts(keep[3], keep[4], a, torch.bfloat16)
-    a.hd, a.T = 128, M + 1
-    assert not K.gemm_qkv_accepts(keep[3], keep[4], a, torch.bfloat16)
 
 
 def test_attention_prefill_tensor_cores_long_prompt_many_times(K):
@@ -330,9 +282,12 @@ def test_attention_prefill_over_cache_and_new_keys(K, dtype, nh, nkv, hd, window
         K.attn_decode(d, DT[dtype], stream())
         want1 = torch.stack([reference_attention(q1[i].float(), full_k[i].float(), full_v[i].float(), lens[i] - 1, window, scale) for i in range(3)])
         assert rel_l2(o1.float().cpu(), want1.reshape(3, Q)) < KTOL[dtype], chunk
-    with pytest.raises(K.KernelError, match="cover"):
-        d.n_splits = 1
+    # fewer splits than the chunk covers: every sequence is cut into that many equal parts of its own length
+    for splits in (1, 3):
+        d.chunk, d.n_splits = 32, splits
+        o1.fill_(float("nan"))
         K.attn_decode(d, DT[dtype], stream())
+        assert rel_l2(o1.float().cpu(), want1.reshape(3, Q)) < KTOL[dtype], splits
 
 
 def test_attention_refuses_bad_heads(K):
@@ -557,8 +512,9 @@ def test_attention_decode_on_tensor_cores(K, nh, nkv, hd, window, ring):
     lay = layout_for(slots, [n - 1 for n in lens], [1] * B)
     qb = q.reshape(B, Q).cuda()
     want = torch.stack([reference_attention(q[i].float(), ks[i].float(), vs[i].float(), lens[i] - 1, window, scale) for i in range(B)]).reshape(B, Q)
-    for chunk in (64, 128, 256, 1024):              # 24 splits (scratch), 12 (a cluster beyond the portable 8), 6, 2
-        splits = -(-max(lens) // chunk)
+    # splits of ``chunk`` keys: 24 (through scratch), 12 (a cluster beyond the portable 8), 6, 2; then fewer splits
+    # than the chunk covers, which cut every sequence into equal parts of its own length (4, 16 and 1 parts)
+    for chunk, splits in ((64, 24), (128, 12), (256, 6), (1024, 2), (128, 4), (64, 16), (128, 1)):
         outs = []
         for mode in ("mma", "mma through scratch", "plain"):     # up to 16 splits merge inside a cluster unless told otherwise
             fast = mode != "plain"

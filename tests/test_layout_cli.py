@@ -33,5 +33,7 @@ def test_command_line_keeps_the_references_options():
     for alias in ("--temp", "--temperature"):
         assert ap.parse_args(["run", alias, "1.5"]).temperature == 1.5
     assert ap.parse_args(["bench", "--random", "cfg.json"]).random == "cfg.json"
+    c = ap.parse_args(["run", "-m", "dir", "--max-context", "300", "--max-batch", "2"])
+    assert (c.max_context, c.max_batch) == (300, 2) and (a.max_context, a.max_batch) == (None, 64)
     with pytest.raises(SystemExit):
         ap.parse_args(["serve"])                               # servers are outside this library

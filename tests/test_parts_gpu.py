@@ -121,6 +121,8 @@ def toy_parts():
     class DecayMixer(Mixer):
         """state_t = decay * state_{t-1} + x_t . W^T ; output = state_t (per sequence, fixed size)."""
 
+        capturable = False          # forward reads the layout on the host: steps with this mixer are not captured as graphs
+
         def __init__(self, spec):
             self.spec, self.decay = spec, spec.option("decay", 0.5)
 
@@ -231,6 +233,15 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(dtype):
         for i in range(2):
             assert rel_l2(torch.cat(got[i]).cpu(), want[i]) < TOL[dtype]
             e.free_slot(slots[i])
+    # through the generation loop: the mixer says that it cannot be captured, so every step runs eagerly
+    from titan_b200 import SamplerParams
+    prompt = reqs[0][:12]
+    made = e.generate([prompt], max_tokens=6, params=SamplerParams.greedy(), stop_tokens=[])[0].tokens
+    assert len(made) == 6 and e.graph_launches == 0
+    logits = toy_plain(d, w32, prompt + made)
+    for j, tok in enumerate(made):
+        row = logits[len(prompt) - 1 + j]
+        assert tok == int(row.argmax()) or float(row.max() - row[tok]) < 0.05 * float(row.abs().max())
 
 
 # --------------------------------------------------------------------------- #
@@ -614,3 +625,229 @@ def test_a_toy_arrangement_of_a_block(dtype):
     rows = [e.step([StepEntry(s, toks[:20], list(range(20)))])] + [e.step([StepEntry(s, [t], [0])]) for t in toks[20:]]
     e.free_slot(s)
     assert rel_l2(torch.cat(rows).cpu(), plain(toks)) < TOL[dtype]
+
+
+# --------------------------------------------------------------------------- #
+# A third kind of cache, an arrangement with four norms (and one layer without a feed-forward), an embedding
+# multiplier and a logit scale, a checkpoint with fused q|k|v and gate|up tensors under other names, and a
+# position encoding with an offset and a factor: all described by specs and registered here.
+# --------------------------------------------------------------------------- #
+def latent_parts():
+    from titan_b200.cache import CacheGroup, CacheNeed, register_cache_group
+    from titan_b200.cache.slots import CacheError
+    from titan_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Mixer, Part, PositionEncoding
+    from titan_b200.weights import WeightSpec
+
+    class LatentGroup(CacheGroup):
+        """One vector of ``width`` numbers per token and layer (no heads, no pages): [layers, slots, context, width]."""
+
+        def __init__(self, need, layers, geometry):
+            self.need, self.layers = need, list(layers)
+            self.limit = geometry.max_context
+            self.storage = torch.zeros((len(layers), geometry.max_slots, geometry.max_context, need.option("width")), device=geometry.device)
+            self.held = {}
+
+        def room_error(self, wanted):
+            over = [s for s, n in wanted.items() if n > self.limit]
+            return f"slots {over} would hold more than {self.limit} latent rows" if over else None
+
+        def extend(self, slot, new_length):
+            self.held[slot] = max(self.held.get(slot, 0), new_length)
+
+        def release(self, slot, mark=False):
+            if self.held.pop(slot, None) is not None and mark:
+                self.storage[:, slot] = 3.0e4
+
+        def check(self, is_live):
+            for slot in self.held:
+                if not is_live(slot):
+                    raise CacheError(f"latent rows are held by slot {slot}, which is not live")
+
+        def layer_storage(self, index_in_group):
+            return self.storage[index_in_group]
+
+        def bytes(self):
+            return self.storage.numel() * 4
+    register_cache_group("toy_latent", LatentGroup)
+
+    class CausalMean(Mixer):
+        """c_t = x_t . Wc^T is kept for every token; output_t = mean_{s <= t} c_s . Wo^T."""
+
+        def __init__(self, spec):
+            self.spec, self.width = spec, spec.option("latent", 8)
+
+        def cache_need(self):
+            return CacheNeed("toy_latent", extra=(("width", self.width),))
+
+        def weight_specs(self, prefix):
+            p = prefix + self.spec.prefix
+            return [WeightSpec(p + "down.weight", (self.width, self.spec.hidden_size)), WeightSpec(p + "up.weight", (self.spec.hidden_size, self.width))]
+
+        def bind(self, get):
+            self.wc, self.wo = get(self.spec.prefix + "down.weight"), get(self.spec.prefix + "up.weight")
+
+        def forward(self, h, ctx, cache, out):
+            group, index = cache
+            rows = group.layer_storage(index)                       # [slots, context, width]
+            lay = ctx.layout
+            c = (h.float() @ self.wc.float().t())
+            starts, slots, first = lay.q_start.tolist(), lay.slot_of_seq.tolist(), lay.start_pos.tolist()
+            for b, slot in enumerate(slots):
+                n = starts[b + 1] - starts[b]
+                rows[slot, first[b]:first[b] + n] = c[starts[b]:starts[b + 1]]
+                sums = rows[slot, :first[b] + n].cumsum(0)[first[b]:]
+                mean = sums / torch.arange(first[b] + 1, first[b] + n + 1, device=h.device)[:, None]
+                out[starts[b]:starts[b + 1]] += mean.to(h.dtype).float() @ self.wo.float().t()
+    MIXERS.register("toy_causal_mean", CausalMean)
+
+    class Sandwich(Part):
+        """x += norm_b(mixer(norm_a(x))); x += norm_d(feed_forward(norm_c(x))): a norm after each part as well as
+        before it (the two after come from ``LayerSpec.norms``); a layer may have no feed-forward at all."""
+
+        def __init__(self, spec):
+            self.spec = spec
+            self.pre_mixer, self.mixer = NORMS.build(spec.mixer_norm), MIXERS.build(spec.mixer)
+            self.post_mixer = NORMS.build(spec.norms[0])
+            self.has_ff = spec.feed_forward is not None
+            if self.has_ff:
+                self.pre_ff, self.feed_forward = NORMS.build(spec.feed_forward_norm), FEED_FORWARDS.build(spec.feed_forward)
+                self.post_ff = NORMS.build(spec.norms[1])
+
+        def parts(self):
+            return (self.pre_mixer, self.mixer, self.post_mixer) + ((self.pre_ff, self.feed_forward, self.post_ff) if self.has_ff else ())
+
+        def weight_specs(self, prefix=""):
+            return [w for part in self.parts() for w in part.weight_specs(self.spec.prefix)]
+
+        def bind(self, get):
+            for part in self.parts():
+                part.bind(lambda name: get(self.spec.prefix + name))
+
+        def forward(self, x, ctx, cache):
+            y = torch.zeros_like(x)
+            self.mixer.forward(self.pre_mixer.forward(x, ctx), ctx, cache, y)
+            x += self.post_mixer.forward(y, ctx).float()
+            if self.has_ff:
+                y = torch.zeros_like(x)
+                self.feed_forward.forward(self.pre_ff.forward(x, ctx), ctx, y)
+                x += self.post_ff.forward(y, ctx).float()
+    BLOCKS.register("toy_sandwich", Sandwich)
+
+    class ShiftedRotary(PositionEncoding):
+        """Rotary angles of (position + shift), cosines and sines scaled by ``factor``: the mixer hands the block
+        to its kernels as it is."""
+
+        def __init__(self, spec):
+            self.spec = spec
+            self._inv = None
+
+        @property
+        def rotary_dim(self):
+            return self.spec.rotary_dim
+
+        def kernel_args(self, device):
+            from titan_b200 import kernels as K
+            if self._inv is None:
+                k = torch.arange(self.spec.rotary_dim // 2, dtype=torch.float64)
+                self._inv = (torch.tensor(self.spec.theta, dtype=torch.float64) ** (-2.0 * k / self.spec.rotary_dim)).float().to(device)
+            return K.RotaryArgs(self._inv.data_ptr(), self.spec.rotary_dim, 3.0, 1.25)
+    POSITIONS.register("toy_shifted_rope", ShiftedRotary)
+
+
+class LatentConfig:
+    def __init__(self, d):
+        self.d = d
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(d)
+
+    def to_dict(self):
+        return dict(self.d)
+
+    def to_model_spec(self):
+        from titan_b200.config import FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec
+        d, H = self.d, self.d["width"]
+        norm = lambda name: NormSpec("rmsnorm", H, 1e-5, name)
+        layers = []
+        for i in range(3):
+            if i == 1:
+                mixer = MixerSpec("attention", H, 4, 2, 16, position=PositionSpec("toy_shifted_rope", 16, 100.0), prefix="att.",
+                                  names=(("qkv", "wqkv.weight"), ("o", "wo.weight")))
+            else:
+                mixer = MixerSpec("toy_causal_mean", H, prefix="mean.", extra=(("latent", d["latent"]),))
+            ff = None if i == 2 else FeedForwardSpec("gated_mlp", H, d["ff"], prefix="ff.", names=(("gate_up", "w13.weight"), ("down", "w2.weight")))
+            layers.append(LayerSpec(i, "toy_sandwich", mixer, ff, norm("a.weight"), None if ff is None else norm("c.weight"), f"blocks.{i}.",
+                                    norms=(norm("b.weight"),) if ff is None else (norm("b.weight"), norm("d.weight"))))
+        return ModelSpec("LatentForCausalLM", H, d["vocab"], tuple(layers), (0, 1, 2), norm("final.weight"), embedding="embed.weight",
+                         lm_head=None, embedding_scale=d["embedding_scale"], logit_scale=d["logit_scale"])
+
+
+def latent_plain(d, w, tokens):
+    H, T = d["width"], len(tokens)
+    x = w["embed.weight"][torch.tensor(tokens)] * d["embedding_scale"]
+    pos = torch.arange(T)
+    for i in range(3):
+        p = f"blocks.{i}."
+        h = P.rms_norm(x, w[p + "a.weight"], 1e-5)
+        if i == 1:
+            qkv = P.linear(h, w[p + "att.wqkv.weight"])
+            q, k, v = qkv[:, :64].view(T, 4, 16), qkv[:, 64:96].view(T, 2, 16), qkv[:, 96:].view(T, 2, 16)
+            q, k = 1.25 * P.rope_neox(q, pos + 3, 100.0), 1.25 * P.rope_neox(k, pos + 3, 100.0)
+            y = P.linear(P.causal_attention(q, k, v).reshape(T, 64), w[p + "att.wo.weight"])
+        else:
+            c = P.linear(h, w[p + "mean.down.weight"])
+            y = P.linear(c.cumsum(0) / torch.arange(1, T + 1)[:, None], w[p + "mean.up.weight"])
+        x = x + P.rms_norm(y, w[p + "b.weight"], 1e-5)
+        if i != 2:
+            h = P.rms_norm(x, w[p + "c.weight"], 1e-5)
+            both = w[p + "ff.w13.weight"]
+            F = both.shape[0] // 2
+            y = P.linear(P.swiglu(P.linear(h, both[:F]), P.linear(h, both[F:])), w[p + "ff.w2.weight"])
+            x = x + P.rms_norm(y, w[p + "d.weight"], 1e-5)
+    return P.linear(P.rms_norm(x, w["final.weight"], 1e-5), w["embed.weight"]) * d["logit_scale"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_third_cache_kind_four_norms_scales_and_other_tensor_names(dtype):
+    from titan_b200 import Engine, StepEntry, StepError, register_architecture
+    from titan_b200.parts import declare_weights
+    latent_parts()
+    register_architecture("LatentForCausalLM", LatentConfig)
+    d = {"architectures": ["LatentForCausalLM"], "width": 64, "latent": 24, "ff": 96, "vocab": 130, "embedding_scale": 8.0, "logit_scale": 0.25}
+    cfg = LatentConfig(d)
+    g = torch.Generator().manual_seed(14)
+    w = {}
+    for s in declare_weights(cfg.to_model_spec()):
+        t = torch.randn(s.shape, generator=g) * (0.1 if s.role == "vector" else 0.12) + (1.0 if s.role == "vector" else 0.0)
+        w[s.name] = t.to(torch.bfloat16)
+    assert "blocks.1.att.wqkv.weight" in w and "blocks.0.ff.w13.weight" in w and not any("q_proj" in n or "gate_proj" in n for n in w)
+    assert not any(n.startswith("blocks.2.ff") or n.startswith("blocks.2.c.") for n in w)              # the last layer has no feed-forward
+    e = Engine.from_tensors(cfg, w, dtype=dtype, max_tokens=256, max_context=128, max_slots=2, mark_freed_pages=True)
+    assert sorted(type(g_).__name__ for g_ in e.cache.groups) == ["KVGroup", "LatentGroup"]
+    w32 = {k: v.float() for k, v in w.items()}
+    reqs = [random_tokens(90, 130, 1), random_tokens(33, 130, 2)]
+    want = [latent_plain(d, w32, r) for r in reqs]
+    for round_ in range(2):                                                  # slots, pages and latent rows are used again
+        slots = [e.alloc_slot(), e.alloc_slot()]
+        cut = [50, 4]
+        out = e.step([StepEntry(slots[i], reqs[i][:cut[i]], list(range(cut[i]))) for i in range(2)])
+        got, at = [[out[:cut[0]]], [out[cut[0]:]]], list(cut)
+        out = e.step([StepEntry(slots[0], reqs[0][50:70], list(range(20)))])  # a continuation chunk
+        got[0].append(out)
+        at[0] = 70
+        while any(a < len(r) for a, r in zip(at, reqs)):
+            live = [i for i in range(2) if at[i] < len(reqs[i])]
+            out = e.step([StepEntry(slots[i], [reqs[i][at[i]]], [0]) for i in live])
+            for k, i in enumerate(live):
+                got[i].append(out[k:k + 1])
+                at[i] += 1
+        for i in range(2):
+            assert rel_l2(torch.cat(got[i]).cpu(), want[i]) < TOL[dtype], (round_, i)
+        with pytest.raises(StepError, match="context"):
+            e.step([StepEntry(slots[0], [1] * 39, [])])                        # 90 + 39 > 128
+        e.cache.check()
+        for s in slots:
+            e.free_slot(s)
+    e.cache.check()
+    assert [g_.held for g_ in e.cache.groups if type(g_).__name__ == "LatentGroup"] == [{}]

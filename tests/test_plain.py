@@ -58,8 +58,15 @@ def test_against_the_references_numpy_functions():
     i = {k: torch.from_numpy(v) for k, v in op_inputs().items()}
     assert np.allclose(P.rms_norm(i["x"], i["w"], GOLD["rms_norm_eps"]).numpy(), GOLD["rms_norm"], rtol=2e-7, atol=0)
     assert np.allclose(P.linear(i["x"][None], i["m"])[0].numpy(), GOLD["matmul_q"], rtol=0, atol=2e-6)
-    s = i["s"].double()
-    assert np.allclose(torch.softmax(s, 0).numpy(), GOLD["softmax_1"], rtol=1e-6)
+    # softmax: the plain implementation's own max-subtract / exp / normalise code, inside its attention.  One query
+    # over 17 keys whose scores are the golden inputs (q = 5 e_0, k_t = s_t e_0, head_dim 25 so that the scale is
+    # 1/5), values one-hot: the output row is the softmax itself.
+    T, hd = 17, 25
+    q, k, v = torch.zeros(T, 1, hd), torch.zeros(T, 1, hd), torch.zeros(T, 1, hd)
+    q[:, 0, 0] = 5.0
+    k[:, 0, 0] = i["s"]
+    v[torch.arange(T), 0, torch.arange(T)] = 1.0
+    assert np.allclose(P.causal_attention(q, k, v)[T - 1, 0, :T].numpy(), GOLD["softmax_1"], rtol=2e-6, atol=1e-9)
     ref, mine = np.array(GOLD["whole_forward_reference_logits"]), np.array(GOLD["whole_forward_plain_logits"])
     assert np.abs(ref - mine).max() < 1e-6 * np.abs(ref).max()
 

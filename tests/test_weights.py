@@ -115,3 +115,18 @@ def test_random_weights_mode_writes_a_loadable_folder(tmp_path):
     assert abs(float(fa.tensor(n).float().std()) - 0.02) < 0.004
     assert abs(float(fa.tensor("model.norm.weight").float().mean()) - 1.0) < 0.1
     FolderWeights(a, declared, torch.bfloat16, "cpu")
+
+
+def test_random_values_are_a_function_of_seed_name_and_index():
+    """Counter based: any slice of a tensor can be made alone, a tensor does not depend on its neighbours, and
+    the stream is standard normal (the device kernel gives the same bits; that is checked on a GPU)."""
+    import numpy as np
+    from titan_b200.weights.random_init import standard_normal, tensor_key, values
+    key = tensor_key(5, "model.layers.1.mlp.up_proj.weight")
+    whole = values(key, 0, 5000, 0.02, 0.0)
+    assert np.array_equal(whole[1234:1300], values(key, 1234, 66, 0.02, 0.0))
+    assert not np.array_equal(whole[:50], values(tensor_key(5, "model.layers.2.mlp.up_proj.weight"), 0, 50, 0.02, 0.0))
+    assert not np.array_equal(whole[:50], values(tensor_key(6, "model.layers.1.mlp.up_proj.weight"), 0, 50, 0.02, 0.0))
+    x = standard_normal(key, 0, 400000)
+    assert abs(x.mean()) < 0.005 and abs(x.std() - 1) < 0.005 and abs((x ** 4).mean() - 3) < 0.05 and 4 < np.abs(x).max() < 6
+    assert abs(np.mean(x[:-1] * x[1:])) < 0.005                       # neighbours are uncorrelated

@@ -26,6 +26,7 @@ def build_case(K, seed, lens, nh, nkv, hd, dtype):
     order = torch.randperm(num_pages, generator=g).tolist()
     table = torch.zeros((B, max(per)), dtype=torch.int32)
     storage = (torch.randn(2, num_pages, nkv, page, hd, generator=g) * 30).to(dtype)
+    keys, vals = [], []
     for s in range(B):
         for j in range(per[s]):
             table[s, j] = order.pop()
@@ -34,10 +35,19 @@ def build_case(K, seed, lens, nh, nkv, hd, dtype):
         for p in range(lens[s]):
             storage[0, int(table[s, p // page]), :, p % page] = k[p]
             storage[1, int(table[s, p // page]), :, p % page] = v[p]
+        keys.append(k)
+        vals.append(v)
     q = torch.randn(B, nh * hd, generator=g).to(dtype)
     dev = dict(table=table.cuda(), storage=storage.cuda(), q=q.cuda(),
                slots=torch.arange(B, dtype=torch.int32).cuda(), kv_len=torch.tensor(lens, dtype=torch.int32).cuda())
-    return dev
+    # what the attention must give, in float64, from the keys and values themselves (not from the paged copy)
+    want = torch.zeros(B, nh, hd, dtype=torch.float64)
+    for s in range(B):
+        for h in range(nh):
+            kh = h // (nh // nkv)
+            score = (keys[s][:, kh].double() @ q[s].view(nh, hd)[h].double()) / math.sqrt(hd)
+            want[s, h] = torch.softmax(score, 0) @ vals[s][:, kh].double()
+    return dev, want.reshape(B, nh * hd).float()
 
 
 def make_args(K, dev, lens, nh, nkv, hd, chunk, out, scratch_ptr):
@@ -63,18 +73,28 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row(dtype):
     code = K.dtype_code(dtype)
     # two calls in a row with different shapes: the second finds the first one's leftovers in the array
     for seed, lens, nh, nkv, hd, chunk in [(1, [300, 17, 129], 6, 2, 48, 64), (2, [64, 500], 4, 4, 32, 128)]:
-        dev = build_case(K, seed, lens, nh, nkv, hd, dtype)
+        dev, exact = build_case(K, seed, lens, nh, nkv, hd, dtype)
         B = len(lens)
         want = torch.empty(B, nh * hd, dtype=dtype, device="cuda")
         scratch = torch.empty(B * nh * -(-max(lens) // chunk) * (hd + 2), device="cuda")
         K.attn_decode(make_args(K, dev, lens, nh, nkv, hd, chunk, want, scratch.data_ptr()), dtype, stream)
         got = torch.full((B, nh * hd), float("nan"), dtype=dtype, device="cuda")
+        # The first call on a device looks up the scratch array's address (and may load the module that holds it):
+        # make it, then watch the driver's own count of free device memory around a second call.  That count moves
+        # with any cudaMalloc or cudaFree in the process, by torch's allocator or by the library itself.
+        args = make_args(K, dev, lens, nh, nkv, hd, chunk, got, None)
+        assert entry(ctypes.byref(args), code, stream) == 0, lib.tb_last_error().decode()
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
-        rc = entry(ctypes.byref(make_args(K, dev, lens, nh, nkv, hd, chunk, got, None)), code, stream)
+        got.fill_(float("nan"))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        rc = entry(ctypes.byref(args), code, stream)
         assert rc == 0, lib.tb_last_error().decode()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before
+        # against float64 from the keys and values themselves: the bound of the other kernel tests
+        exact_err = float((got.float().cpu() - exact).norm() / exact.norm())
+        assert exact_err < (2e-6 if dtype == torch.float32 else 6e-3), exact_err
         # the same kernels on another scratch: the bound of the other kernel tests (2e-6 float32, 6e-3 bfloat16)
         err = float((got.float() - want.float()).norm() / want.float().norm())
         assert err < (2e-6 if dtype == torch.float32 else 6e-3), err

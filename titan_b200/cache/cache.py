@@ -4,8 +4,9 @@
 ``CacheNeed`` or ``None`` per layer).  It owns
 
 * the slot allocator and each sequence's length (host and device copies);
-* one ``KVGroup`` / ``StateGroup`` per distinct need, and the map from a layer
-  to (group, index within the group);
+* one group of storage per distinct need, built from the registry of kinds
+  (``groups.register_cache_group``: ``kv``, ``state``, and what else is
+  registered), and the map from a layer to (group, index within the group);
 * ``SlotState``: per-sequence state of fixed size that no layer owns (length,
   last token, sampling counters), the same place where a mixer's fixed-size
   state lies (a ``StateGroup``).
@@ -20,7 +21,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from .groups import CacheNeed, KVGroup, StateGroup
+from .groups import CacheGeometry, CacheGroup, CacheNeed, build_cache_group
 from .slots import CacheError, CacheFull, SlotAllocator
 
 PAGE_SIZE = 64
@@ -58,7 +59,8 @@ class SequenceCache:
         self.slots = SlotAllocator(max_slots)
         self.length: Dict[int, int] = {}
         self.state = SlotState(max_slots, device)
-        self.groups: List[object] = []
+        self.groups: List[CacheGroup] = []
+        geometry = CacheGeometry(self.num_pages, page_size, max_slots, self.max_context, dtype, device)
         self.layer_place: List[Optional[Tuple[int, int]]] = []
         by_key: Dict[tuple, List[int]] = {}
         for i, need in enumerate(needs):
@@ -68,12 +70,7 @@ class SequenceCache:
         place: Dict[int, Tuple[int, int]] = {}
         for key, layers in by_key.items():
             need = need_of[key]
-            if need.kind == "kv":
-                g = KVGroup(need, layers, self.num_pages, page_size, max_slots, self.max_context, dtype, device)
-            elif need.kind == "state":
-                g = StateGroup(need, layers, max_slots, device)
-            else:
-                raise CacheError(f"unknown cache need '{need.kind}'")
+            g = build_cache_group(need, layers, geometry)
             for j, layer in enumerate(layers):
                 place[layer] = (len(self.groups), j)
             self.groups.append(g)
@@ -85,16 +82,14 @@ class SequenceCache:
         self.length[slot] = 0
         self.state.seq_len[slot] = 0
         for g in self.groups:
-            if isinstance(g, StateGroup):
-                g.reset(slot)
+            g.on_alloc(slot)
         return slot
 
     def free_slot(self, slot: int) -> None:
         self.slots.give_back(slot)          # raises on unknown / double free
         del self.length[slot]
         for g in self.groups:
-            if isinstance(g, KVGroup):
-                g.release(slot, self.mark_freed)
+            g.release(slot, self.mark_freed)
 
     def is_live(self, slot: int) -> bool:
         return self.slots.is_held(slot)
@@ -109,15 +104,12 @@ class SequenceCache:
             if n > self.max_context:
                 raise CacheFull(f"slot {slot} would hold {n} tokens; the context holds {self.max_context}")
         for g in self.groups:
-            if isinstance(g, KVGroup):
-                short = sum(g.shortfall(slot, n) for slot, n in wanted.items())
-                if short > g.pool.free_count:
-                    raise CacheFull(f"{short} more pages of {self.page_size} tokens wanted, "
-                                    f"{g.pool.free_count} of {g.pool.count} free")
+            why = g.room_error(wanted)
+            if why:
+                raise CacheFull(why)
         for g in self.groups:
-            if isinstance(g, KVGroup):
-                for slot, n in wanted.items():
-                    g.extend(slot, n)
+            for slot, n in wanted.items():
+                g.extend(slot, n)
 
     def commit(self, slot: int, new_length: int) -> None:
         """Host copy of the length after a step; the device copy is advanced by the step itself."""
@@ -143,13 +135,4 @@ class SequenceCache:
         if sorted(self.length) != [i for i in range(self.max_slots) if self.slots.is_held(i)]:
             raise CacheError("lengths are kept for slots that are not held")
         for g in self.groups:
-            if isinstance(g, KVGroup):
-                g.pool.check()
-                held = [p for pages in g.pages_of.values() for p in pages]
-                if len(set(held)) != len(held):
-                    raise CacheError("a page belongs to two sequences")
-                if len(held) != g.pool.held_count:
-                    raise CacheError("a page is held by no sequence")
-                for slot in g.pages_of:
-                    if not self.is_live(slot):
-                        raise CacheError(f"pages are held by slot {slot}, which is not live")
+            g.check(self.is_live)

@@ -10,7 +10,9 @@ Kept from the reference, with their names, meanings and defaults:
 Added, because this library takes token ids, not text, and has options the reference reads from its
 HTTP request (engine/engine-core/src/sampler.rs:13-24): --prompt-ids, --prompts-file, --max-tokens
 (default 512, main.rs:515), --top-k (40), --repetition-penalty (1.1), --seed (42), --stop-ids,
---dtype, --random <config.json> (random weights from a configuration and --weights-seed).
+--dtype, --random <config.json> (random weights from a configuration and --weights-seed),
+--max-context (longest sequence; default: the model's position limit or what the cache holds) and
+--max-batch (sequences per generation batch, default 64).
 Not kept: ``serve``, ``agent``, -e/--engine, -s/--speculative, --system, -p/--port: servers,
 streaming, speculative decoding and text are outside this library.
 """
@@ -48,6 +50,8 @@ def build_parser() -> argparse.ArgumentParser:
         p.add_argument("--prompt-ids", type=_ids, action="append", default=None, help="one prompt: 1,2,3 (repeatable)")
         p.add_argument("--prompts-file", default=None, help="one prompt per line: token ids, or a JSON list")
         p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+        p.add_argument("--max-context", type=int, default=None, help="longest sequence (prompt + generated); default: the model's limit or the cache's size")
+        p.add_argument("--max-batch", type=int, default=64, help="sequences that generate together; more prompts run one batch after another")
     sub.add_parser("help", help="print this help")
     return ap
 
@@ -56,12 +60,13 @@ def _engine(args):
     from . import Engine
     from .config import config_from_dict
     model = args.model or args.model_pos
+    kw = dict(dtype=args.dtype, max_tokens=args.kv_capacity, max_context=args.max_context, max_batch=args.max_batch)
     if args.random:
         with open(args.random) as f:
-            return Engine.from_random(config_from_dict(json.load(f)), args.weights_seed, dtype=args.dtype, max_tokens=args.kv_capacity)
+            return Engine.from_random(config_from_dict(json.load(f)), args.weights_seed, **kw)
     if not model:
         raise SystemExit("give a model folder (-m/--model) or --random <config.json>")
-    return Engine.from_pretrained(model, dtype=args.dtype, max_tokens=args.kv_capacity)
+    return Engine.from_pretrained(model, **kw)
 
 
 def _prompts(args) -> List[List[int]]:

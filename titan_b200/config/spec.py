@@ -37,6 +37,13 @@ class PositionSpec:
     pairing: str = "half"     # (k, k + rotary_dim/2)
 
 
+def _lookup(pairs, key, default):
+    for k, v in pairs:
+        if k == key:
+            return v
+    return default
+
+
 @dataclass(frozen=True)
 class MixerSpec:
     kind: str                 # "attention"
@@ -50,10 +57,17 @@ class MixerSpec:
     softmax_scale: Optional[float] = None  # None: 1/sqrt(head_dim)
     cache_from: Optional[int] = None      # read (and do not write) this layer's cache
     prefix: str = "self_attn."
+    # Tensor names by role, relative to ``prefix``; roles a part knows and that are not listed keep the
+    # part's default.  Attention: "q", "k", "v", "o" (defaults q_proj.weight ...), or "qkv" for a checkpoint
+    # that stores the three projections as one [Q + 2 KV, H] tensor.
+    names: Tuple[Tuple[str, str], ...] = ()
     extra: Tuple[Tuple[str, Any], ...] = ()   # for mixers defined outside the package
 
     def option(self, key: str, default: Any = None) -> Any:
-        return dict(self.extra).get(key, default)
+        return _lookup(self.extra, key, default)
+
+    def name(self, role: str, default: Optional[str] = None) -> Optional[str]:
+        return _lookup(self.names, role, default)
 
 
 @dataclass(frozen=True)
@@ -63,22 +77,36 @@ class FeedForwardSpec:
     intermediate_size: int = 0
     activation: str = "silu"
     prefix: str = "mlp."
+    # Tensor names by role: "gate", "up", "down" (defaults gate_proj.weight ...), or "gate_up" for a
+    # checkpoint that stores gate and up as one [2 F, H] tensor (gate rows first).
+    names: Tuple[Tuple[str, str], ...] = ()
     extra: Tuple[Tuple[str, Any], ...] = ()
 
     def option(self, key: str, default: Any = None) -> Any:
-        return dict(self.extra).get(key, default)
+        return _lookup(self.extra, key, default)
+
+    def name(self, role: str, default: Optional[str] = None) -> Optional[str]:
+        return _lookup(self.names, role, default)
 
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block: which mixer, which feed-forward, which norms, how arranged."""
+    """One block: which mixer, which feed-forward, which norms, how arranged.  The arrangement gives the
+    fields their meaning: ``pre_norm`` needs all four parts; another arrangement may do without a
+    feed-forward (None), or take more norms than two from ``norms`` (a norm after each part as well as
+    before it, say) and its own constants from ``extra``."""
     index: int
     arrangement: str          # "pre_norm"
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
-    mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    feed_forward: Optional[FeedForwardSpec]
+    mixer_norm: Optional[NormSpec]
+    feed_forward_norm: Optional[NormSpec]
     prefix: str               # "model.layers.3."
+    norms: Tuple[NormSpec, ...] = ()          # further norms, in the order the arrangement defines
+    extra: Tuple[Tuple[str, Any], ...] = ()
+
+    def option(self, key: str, default: Any = None) -> Any:
+        return _lookup(self.extra, key, default)
 
 
 @dataclass(frozen=True)
@@ -93,6 +121,8 @@ class ModelSpec:
     lm_head: Optional[str] = "lm_head.weight"   # None: tied to the embedding
     max_positions: int = 4096
     stop_token_ids: Tuple[int, ...] = ()
+    embedding_scale: Optional[float] = None   # the embedded rows are multiplied by this (None: as stored)
+    logit_scale: Optional[float] = None       # the logits are multiplied by this (None: as computed)
 
     def validate(self) -> None:
         if not self.layers:
@@ -102,8 +132,23 @@ class ModelSpec:
                 raise ConfigError(f"layer order names layer {i}, but there are {len(self.layers)} layers")
         for layer in self.layers:
             src = layer.mixer.cache_from
-            if src is not None:
-                if not 0 <= src < len(self.layers) or self.layers[src].mixer.cache_from is not None:
-                    raise ConfigError(f"layer {layer.index} reads the cache of layer {src}, which owns none")
-                if src not in self.order or self.order.index(src) > self.order.index(layer.index):
-                    raise ConfigError(f"layer {layer.index} reads the cache of layer {src} before it is written")
+            if src is None:
+                continue
+            me = layer.mixer
+            if not 0 <= src < len(self.layers) or self.layers[src].mixer.cache_from is not None:
+                raise ConfigError(f"layer {layer.index} reads the cache of layer {src}, which owns none")
+            if layer.index not in self.order:
+                raise ConfigError(f"layer {layer.index} reads the cache of layer {src} but never runs (it is not in the order)")
+            if src not in self.order or self.order.index(src) > self.order.index(layer.index):
+                raise ConfigError(f"layer {layer.index} reads the cache of layer {src} before it is written")
+            owner = self.layers[src].mixer
+            if owner.kind != me.kind:
+                raise ConfigError(f"layer {layer.index} ({me.kind}) reads the cache of layer {src}, whose mixer is of another kind ({owner.kind})")
+            if owner.window != me.window:
+                raise ConfigError(f"layer {layer.index} reads the cache of layer {src}, which keeps a window of {owner.window} keys, "
+                                  f"with a window of {me.window}: a reader must see exactly what the owner keeps")
+            if owner.head_dim != me.head_dim:
+                raise ConfigError(f"layer {layer.index} has heads of {me.head_dim}, the cache of layer {src} holds heads of {owner.head_dim}")
+            if owner.num_kv_heads <= 0 or me.num_heads % owner.num_kv_heads:
+                raise ConfigError(f"layer {layer.index} has {me.num_heads} query heads, not a multiple of the {owner.num_kv_heads} "
+                                  f"kv heads in the cache of layer {src}")

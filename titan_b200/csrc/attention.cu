@@ -3,8 +3,8 @@
 //   tb_attn_prefill  queries of a ragged step; keys before the step come from the cache, keys of
 //                    the step itself from the step's own K | V rows (so a ring cache can be
 //                    written after attention)
-//   tb_attn_decode   one query per sequence over its cached keys, cut into chunks of fixed
-//                    length ("split-KV"), each chunk giving (max, sum, unnormalised output)
+//   tb_attn_decode   one query per sequence over its cached keys, cut into splits by the sequence's
+//                    own length (tb_split_keys), each giving (max, sum, unnormalised output)
 //   tb_attn_merge    log-sum-exp merge of the chunks in chunk order
 //
 // One warp per (query, head): a lane scores one key per round with the whole query in shared
@@ -150,11 +150,12 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(AttnArgs a)
     const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
     const int hd = a.hd, group = a.nh / a.nkv;
     const int len = a.batch.kv_len[b];
-    if (split * a.chunk >= len) return;             // the merge reads ceil(len / chunk) splits only
+    const int keys = tb_split_keys(len, a.chunk, a.n_splits);
+    if ((long long)split * keys >= len) return;     // the merge reads ceil(len / keys) splits only
     const int pos = len - 1;
     const int slot = a.batch.slot_of_seq[b];
     const int wlo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-    const int lo = max(wlo, split * a.chunk), hi = min(len, (split + 1) * a.chunk);
+    const int lo = max(wlo, split * keys), hi = min(len, (split + 1) * keys);
     float* qs = q_smem + warp * hd;
     for (int g = warp; g < group; g += ATT_WARPS) {
         const int h = kh * group + g;
@@ -186,7 +187,8 @@ __global__ void attn_merge_kernel(AttnArgs a) {
     pdl_wait();
     const int b = blockIdx.x, h = blockIdx.y, lane = threadIdx.x, hd = a.hd, stride = hd + 2;
     const float* part = a.scratch + (size_t)(b * a.nh + h) * a.n_splits * stride;
-    const int used = min(a.n_splits, (a.batch.kv_len[b] + a.chunk - 1) / a.chunk);
+    const int len = a.batch.kv_len[b], keys = tb_split_keys(len, a.chunk, a.n_splits);
+    const int used = min(a.n_splits, (len + keys - 1) / keys);
     float m = -FLT_MAX;
     for (int s = lane; s < used; s += 32)
         if (part[s * stride + hd + 1] > 0.f) m = fmaxf(m, part[s * stride + hd]);
@@ -260,7 +262,6 @@ extern "C" int tb_attn_decode(const AttnArgs* args, int dtype, cudaStream_t stre
     if (check_common(a, "attn_decode")) return 1;
     TB_REQUIRE(a.batch.B > 0 && a.cache.storage && a.scratch, "attn_decode: needs sequences, a cache and scratch");
     TB_REQUIRE(a.chunk > 0 && a.n_splits > 0 && a.n_splits <= 65535, "attn_decode: bad split (chunk=%d splits=%d)", a.chunk, a.n_splits);
-    TB_REQUIRE((long long)a.chunk * a.n_splits >= a.batch.max_kv_len, "attn_decode: %d splits of %d keys do not cover %d keys", a.n_splits, a.chunk, a.batch.max_kv_len);
     TB_REQUIRE(a.nkv <= 65535, "attn_decode: too many kv heads");
     dim3 grid(a.batch.B, a.nkv, a.n_splits), mgrid(a.batch.B, a.nh);
     const size_t smem = (size_t)ATT_WARPS * a.hd * sizeof(float);

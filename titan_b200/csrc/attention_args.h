@@ -12,8 +12,8 @@ struct AttnArgs {
     int nh; int nkv; int hd;
     int window;                             // 0: all keys
     float scale;
-    int chunk;                              // decode: keys per split
-    int n_splits;                           // decode: grid.z
+    int chunk;                              // decode: fewest keys per split (see tb_split_keys)
+    int n_splits;                           // decode: grid.z, the most splits a sequence is cut into
     float* scratch;                         // decode: [B][nh][n_splits][hd + 2]
     // decode, optional: lengths that were final before the step's first kernel ran, so that a kernel may read
     // them without waiting for its predecessors.  early_mode 1: early_len[b] = batch.kv_len[b] (the same numbers,
@@ -21,3 +21,14 @@ struct AttnArgs {
     // length of the slot, for steps whose kv_len a kernel of the step computes); 0 or a null pointer: none.
     const int* early_len; int early_mode;
 };
+
+// How decode attention cuts the keys of ONE sequence into splits: ``chunk`` keys each while ``n_splits`` of
+// them cover the sequence, else ``n_splits`` equal parts of whole 64-key pages.  Split s takes keys
+// [s * keys, (s + 1) * keys) below the length; splits that start at or beyond the length are empty.  The
+// borders depend on the sequence's own length and on the launch's two numbers, never on the other sequences
+// of the batch, on the longest context the engine allows or on where the sequence lies in the cache.
+// (berniehans/titan: num_splits = min(32, ceil(S / 256)), engine/engine-cuda/src/paged_attention.rs:368-370.)
+__host__ __device__ __forceinline__ int tb_split_keys(int len, int chunk, int n_splits) {
+    if ((long long)chunk * n_splits >= len) return chunk;
+    return (((len + n_splits - 1) / n_splits) + 63) & ~63;
+}

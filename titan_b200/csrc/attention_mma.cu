@@ -8,8 +8,8 @@
 //                        read from HBM once for the group.  Partials go through the same
 //                        (max, sum, unnormalised output) format as the plain kernel and the same merge.
 //
-// The chunk borders are multiples of the page size and depend on the launch (batch size, context
-// limit), not on the other sequences of the batch.
+// A sequence's keys are cut into splits by its own length (tb_split_keys): the borders are multiples of
+// the page size and depend on that length and on the launch's (fewest keys per split, most splits) only.
 //
 // Keys and values arrive 128-byte swizzled (tensor map of 64 x 64 boxes), which makes the ldmatrix
 // reads conflict-free.  All waits are bounded (tma.cuh); tb_attn_mma_error() reads the error word.
@@ -88,10 +88,11 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     const bool early = a.early_mode != 0;
     if (!early) pdl_wait();
     const int len = a.early_mode == 2 ? a.early_len[a.slot_of_seq[b]] + 1 : (early ? a.early_len[b] : a.kv_len[b]);
-    if (!CL && split * a.chunk >= len) return;          // uniform over the CTA; the merge skips these splits (in a cluster the CTA stays, with no pages, for the barrier)
+    const int keys = tb_split_keys(len, a.chunk, a.n_splits);
+    if (!CL && (long long)split * keys >= len) return;  // uniform over the CTA; the merge skips these splits (in a cluster the CTA stays, with no pages, for the barrier)
     const int group = a.nh / a.nkv;
     const int wlo = a.window > 0 ? max(0, len - a.window) : 0;       // first visible key of position len - 1
-    const int lo = max(wlo, split * a.chunk), hi = min(len, (split + 1) * a.chunk);
+    const int lo = max(wlo, (int)min((long long)len, (long long)split * keys)), hi = (int)min((long long)len, (long long)(split + 1) * keys);
     const int page0 = lo / PAGE, n_pages = lo < hi ? (hi - 1) / PAGE - page0 + 1 : 0;
 
     if (threadIdx.x == 0) {
@@ -537,7 +538,6 @@ extern "C" int tb_attn_decode_mma(const AttnArgs* args, cudaStream_t stream) {
     const bool may_cluster = g_decode_cluster && a.out != nullptr;
     TB_REQUIRE(a.batch.B > 0 && a.cache.storage, "attn_decode_mma: needs sequences and a cache");
     TB_REQUIRE(a.n_splits > 0 && a.n_splits <= 65535 && a.nkv <= 65535, "attn_decode_mma: bad grid");
-    TB_REQUIRE((long long)a.chunk * a.n_splits >= a.batch.max_kv_len, "attn_decode_mma: %d splits of %d keys do not cover %d keys", a.n_splits, a.chunk, a.batch.max_kv_len);
     TB_REQUIRE(a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv, "attn_decode_mma: the cache view does not match the heads");
     CUtensorMap map;
     const long long rows = 2LL * a.cache.num_pages * a.nkv * PAGE;

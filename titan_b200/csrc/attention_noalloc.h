@@ -12,8 +12,8 @@
 // engine) allocates; here it is a fixed array inside the library image.
 //
 // tb_attn_decode_noalloc computes exactly what tb_attn_decode computes (attention.cu): one query per
-// sequence over its cached keys, cut into ``n_splits`` chunks of ``chunk`` keys, then the merge of
-// the chunks.  The caller passes the same argument block, inputs and outputs as for tb_attn_decode;
+// sequence over its cached keys, cut into at most ``n_splits`` splits of ``chunk`` keys or more
+// (tb_split_keys in attention_args.h), then the merge of the splits.  The caller passes the same argument block, inputs and outputs as for tb_attn_decode;
 // the ``scratch`` field is ignored.
 //
 // Limits and rules

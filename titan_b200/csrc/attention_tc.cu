@@ -27,9 +27,7 @@
 // fastest, so the heaviest query blocks of all heads start first and the lightest make the tail.
 // Tensor memory: S (then P) 4 x 64 columns, O 2 x 128 columns (all 512).
 //
-// All waits are bounded (tma.cuh); tb_attn_tc_error() reads the error word.  Built with -DTB_TC_TIMING
-// (TITAN_B200_NVCC_FLAGS), one warp of the first CTA adds up clock64() per phase of the softmax loop
-// (tb_attn_tc_clocks); that build is for experiments only.
+// All waits are bounded (tma.cuh); tb_attn_tc_error() reads the error word.
 //
 // berniehans/titan: flash_attention_2_kernel, one warp per (head, query), one key per iteration,
 // scalar FMA (engine/engine-cuda/kernels/flash_attention_2.cu:22-106).
@@ -46,12 +44,6 @@ using namespace tbtma;
 using namespace tbtc;
 
 __device__ unsigned int g_attn_tc_error = 0;
-#ifdef TB_TC_TIMING
-__device__ unsigned long long g_tc_clk[16];
-#define TCLK(i) do { if (timing) { const long long now_ = clock64(); atomicAdd(&g_tc_clk[i], (unsigned long long)(now_ - tprev)); tprev = now_; } } while (0)
-#else
-#define TCLK(i) do {} while (0)
-#endif
 
 constexpr int HD = 128, BQ = 128, BKEY = 64;
 constexpr int THREADS = 384;                           // producer, S issuer (even tiles), eight softmax warps, P.V issuer, S issuer (odd tiles)
@@ -140,9 +132,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 
     pdl_launch_dependents();
     pdl_wait();
-#ifdef TB_TC_TIMING
-    const long long t_entry = clock64();
-#endif
     // blockIdx.y: which sequence and which block of 128 queries (a sequence's blocks from the heaviest,
     // the last, down); blockIdx.x, which runs fastest in the dispatch order: the head
     int rem = blockIdx.y, seq = -1, blk = 0, tok0 = 0, n = 0;
@@ -208,17 +197,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         if (lane == 0) {
             const uint64_t q_desc = desc_k_major(smem_u32(q_smem));
             wait(q_full, 0, 3);
-#ifdef TB_TC_TIMING
-            const bool timing = blockIdx.x == 0 && blockIdx.y == 0 && warp == 1;
-            long long tprev = clock64();
-#endif
             for (int i = warp == 1 ? 0 : 1; i < n_tiles; i += 2) {
                 const int s = i % KV_STAGES;
-                TCLK(8);
                 if (i >= 4) wait(pv_done + (i & 3), ((i >> 2) - 1) & 1, 9);       // the buffer held S, then P, of tile i - 4
-                TCLK(9);
                 wait(k_full + s, (i / KV_STAGES) & 1, 2);
-                TCLK(10);
                 tc_fence_after();
                 const uint64_t k_desc = desc_k_major(smem_u32(kv_smem + s * 2 * KV_TILE));
                 const uint32_t d = tmem_s + (i & 3) * BKEY;
@@ -232,17 +214,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     } else if (warp == 10) {
         // ---- P.V issuer: O_g += P_j . V_j for the group g = j % 2
         if (lane == 0) {
-#ifdef TB_TC_TIMING
-            const bool timing = blockIdx.x == 0 && blockIdx.y == 0;
-            long long tprev = clock64();
-#endif
             for (int j = 0; j < n_tiles; ++j) {
                 const int g = j & 1, s = j % KV_STAGES;
-                TCLK(11);
                 wait(v_full + s, (j / KV_STAGES) & 1, 5);
-                TCLK(12);
                 wait(p_full + g, (j >> 1) & 1, 4);          // the group has rescaled O if it had to and written P_j
-                TCLK(13);
                 tc_fence_after();
                 const uint64_t v_desc = desc_mn_major(smem_u32(kv_smem + s * 2 * KV_TILE + KV_TILE));
                 const uint32_t p_tmem = tmem_s + (j & 3) * BKEY;      // P_j lies over the first half of S_j
@@ -261,23 +236,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         const int lo = a.window > 0 ? qpos - a.window + 1 : 0;
         float m_run = -1e30f, l_run = 0.f;                       // the maximum P is taken against (may lag), the sum
         int mine = 0;                                            // tiles of this group so far
-#ifdef TB_TC_TIMING
-        const bool timing = blockIdx.x == 0 && blockIdx.y == 0 && warp == 2 && lane == 0;
-        long long tprev = clock64();
-        if (timing) atomicAdd(&g_tc_clk[14], (unsigned long long)(tprev - t_entry));     // entry to the first tile
-#endif
         for (int j = g; j < n_tiles; j += 2, ++mine) {
             const int key0 = (kt0 + j) * BKEY;
             const bool tile_visible = key0 + BKEY - 1 <= qpos && key0 >= lo;       // no mask needed in this tile
-            TCLK(0);
             wait(s_done + (j & 3), (j >> 2) & 1, 6);
             tc_fence_after();
-            TCLK(1);
             float v[64];
             tmem_ld32_nowait(tmem_s + (j & 3) * BKEY + lane_addr, v);
             tmem_ld32_nowait(tmem_s + (j & 3) * BKEY + lane_addr + 32, v + 32);
             tmem_wait_ld<64>(v);
-            TCLK(2);
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (!tile_visible) {
 #pragma unroll
@@ -293,7 +260,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             const bool raise = cand > m_run + RESCALE_LOG2;
             const float m_new = raise ? cand : m_run;
             const float f = raise ? ex2(m_run - m_new) : 1.f;
-            TCLK(3);
             // Only a rescale touches O, and only then must the group's earlier P.V be complete (P itself goes
             // into this tile's own S buffer).  f = 1 for the rows of the warp that keep their maximum.
             if (mine >= 1 && __any_sync(0xffffffffu, raise)) {
@@ -308,7 +274,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     tmem_st32(tmem_o + g * HD + lane_addr + c, o);
                 }
             }
-            TCLK(4);
             // two scores per instruction where the hardware has one (packed float32 FMA and add on sm_100):
             // the softmax warps are short of issue slots, not only of special-function units
             const float2 scale2 = make_float2(a.scale_log2, a.scale_log2), shift2 = make_float2(-m_new, -m_new);
@@ -327,7 +292,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 #pragma unroll
             for (int i = 0; i < 32; ++i) pk[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
             tmem_st32_bits(tmem_s + (j & 3) * BKEY + lane_addr, pk);
-            TCLK(5);
             // The P.V issuer must have seen this group's previous arrival before the next one, or the
             // barrier would run two phases ahead of it and its parity wait would never end.  P.V of that
             // tile complete implies it; by now (a whole tile later) this wait is almost always over.
@@ -335,7 +299,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full + g);
-            TCLK(6);
         }
         if (mine >= 1) {                                         // the group's last P.V
             const int last = g + 2 * (mine - 1);
@@ -383,9 +346,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
-#ifdef TB_TC_TIMING
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64) atomicAdd(&g_tc_clk[15], (unsigned long long)(clock64() - t_entry));
-#endif
 }
 
 }  // namespace
@@ -430,14 +390,6 @@ extern "C" int tb_attn_prefill_tc(const AttnArgs* args, int all_fresh, cudaStrea
     return 0;
 }
 
-#ifdef TB_TC_TIMING
-extern "C" int tb_attn_tc_clocks(unsigned long long* out16) {
-    unsigned long long zero[16] = {};
-    if (cudaMemcpyFromSymbol(out16, g_tc_clk, sizeof(zero)) != cudaSuccess) return 1;
-    cudaMemcpyToSymbol(g_tc_clk, zero, sizeof(zero));
-    return 0;
-}
-#endif
 
 // Reads and clears the error word of this file's kernel (0: none).  Synchronises the device.
 extern "C" int tb_attn_tc_error() {

@@ -31,7 +31,7 @@ from typing import List, Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIBS = {"core": "libtitan_b200.so", "tensor": "libtitan_b200_tensor.so"}
-TENSOR_SOURCES = ("gemm_tc.cu", "gemm_qkv.cu", "attention_mma.cu", "attention_tc.cu", "tma_host.cu", "mma_probe.cu")
+TENSOR_SOURCES = ("gemm_tc.cu", "attention_mma.cu", "attention_tc.cu", "tma_host.cu")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
               "-Xcompiler", "-fvisibility=default"]

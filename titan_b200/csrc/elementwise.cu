@@ -37,6 +37,22 @@ extern "C" int tb_embed(const void* table, int dtype, const int* tokens, float* 
     return 0;
 }
 
+// x *= factor (float32, in place): an embedding multiplier or a logit scale of the model's description.
+__global__ void scale_f32_kernel(float* __restrict__ x, long long n, float factor) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] *= factor;
+}
+
+extern "C" int tb_scale_f32(float* x, long long n, float factor, cudaStream_t stream) {
+    TB_REQUIRE(x && n > 0, "scale_f32: nothing to scale");
+    const int threads = 256;
+    const long long blocks = (n + threads - 1) / threads;
+    tb_launch(scale_f32_kernel, (int)(blocks < 4096 ? blocks : 4096), threads, 0, stream, x, n, factor);
+    TB_CHECK_LAUNCH("scale_f32");
+    return 0;
+}
+
 // ------------------------------------------------------------------ RMSNorm
 // y[r] = x[rows ? rows[r] : r] * 1/sqrt(mean(x^2) + eps) * w      (x float32, y in the compute dtype)
 template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
@@ -116,7 +132,8 @@ extern "C" int tb_rmsnorm(const float* x, const float* w, void* y, int dtype, co
 // One warp per (token, head).  Heads 0..nh-1 are Q, nh..nh+nkv-1 are K, and, when the cache is
 // written here, nh+nkv.. are V (copied unchanged).  Per head: RMSNorm over head_dim with a shared
 // weight (skipped when the weight pointer is null), then the half-split rotation of the first
-// ``rot`` dims: for k < rot/2, angle = pos * inv_freq[k], (y_k, y_{k+rot/2}) rotated
+// ``rot`` dims: for k < rot/2, angle = (pos + offset) * inv_freq[k], (y_k, y_{k+rot/2}) rotated and
+// scaled by ``magnitude`` (offset 0 and magnitude 1 for plain rotary; TbRotary in qk_args.h)
 // (kernels/norm_rope.cu:226-245 and :83-117 in berniehans/titan).
 #define QK_MAXE 8   // head_dim <= 32 * QK_MAXE
 
@@ -131,10 +148,14 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
     const int n_heads = a.nh + a.nkv + (a.append ? a.nkv : 0);
     // cosine and sine of this token's angles, once per block: [rot/2] each, behind the warps' rows
     float* cs = head_smem + nwarp * a.hd;
-    float* sn = cs + (a.rot >> 1);
-    if (a.inv_freq) {
-        const float p = (float)a.pos_of[t];
-        for (int k = threadIdx.x; k < (a.rot >> 1); k += blockDim.x) sincosf(p * a.inv_freq[k], &sn[k], &cs[k]);
+    float* sn = cs + (a.rope.rot >> 1);
+    if (a.rope.inv_freq) {
+        const float p = (float)a.pos_of[t] + a.rope.offset;
+        for (int k = threadIdx.x; k < (a.rope.rot >> 1); k += blockDim.x) {
+            float sv, cv;
+            sincosf(p * a.rope.inv_freq[k], &sv, &cv);
+            sn[k] = sv * a.rope.magnitude; cs[k] = cv * a.rope.magnitude;
+        }
     }
     __syncthreads();
     if (head >= n_heads) return;
@@ -179,7 +200,7 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
         if (e < hd) y[e] = w ? v[j] * scale * w[e] : v[j];
     }
     __syncwarp();
-    const int half = a.rot >> 1;
+    const int half = a.rope.rot >> 1;
     TOut* out = is_q ? (TOut*)a.q_out + (size_t)t * a.q_stride + head * hd
                      : (a.k_out ? (TOut*)a.k_out + (size_t)t * a.k_stride + (head - a.nh) * hd : nullptr);
     TOut* cdst = (is_k && to_cache)
@@ -189,7 +210,7 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
         const int e = lane + 32 * j;
         if (e >= hd) continue;
         float r = y[e];
-        if (a.inv_freq && e < a.rot) {
+        if (a.rope.inv_freq && e < a.rope.rot) {
             const bool first = e < half;
             const int k = first ? e : e - half;
             const float s = sn[k], c = cs[k];
@@ -275,10 +296,12 @@ __global__ void qk_norm_rope_vec_kernel(QkArgs a) {
         const bool to_cache = a.append && !(a.cache.ring_rows && a.kv_len && pos < a.kv_len[seq] - a.cache.ring_rows);
         row_off[threadIdx.x] = to_cache ? (long long)kv_row_offset(a.cache, a.slot_of_seq[seq], pos, 0) : -1;
     }
-    if (a.inv_freq) {
+    if (a.rope.inv_freq) {
         for (int i = threadIdx.x; i < n_tok * HALF; i += blockDim.x) {
             const int j = i / HALF, k = i - j * HALF;
-            sincosf((float)a.pos_of[t0 + j] * a.inv_freq[k], &sn[i], &cs[i]);
+            float sv, cv;
+            sincosf(((float)a.pos_of[t0 + j] + a.rope.offset) * a.rope.inv_freq[k], &sv, &cv);
+            sn[i] = sv * a.rope.magnitude; cs[i] = cv * a.rope.magnitude;
         }
     }
     __syncthreads();
@@ -314,7 +337,7 @@ __global__ void qk_norm_rope_vec_kernel(QkArgs a) {
             wlo[i] = w ? w[l * HV + i] : 1.f;
             whi[i] = w ? w[HALF + l * HV + i] : 1.f;
         }
-        const bool rotate = a.inv_freq && (is_q || is_k);
+        const bool rotate = a.rope.inv_freq && (is_q || is_k);
         // No early exit from this loop: its TOK bodies are independent, and the compiler interleaves
         // them; a token beyond the end computes on zeros and stores nothing.
 #pragma unroll
@@ -385,7 +408,7 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     QkArgs a = *args;
     TB_REQUIRE(a.T > 0 && a.nh > 0 && a.nkv >= 0, "qk_norm_rope: sizes must be positive");
     TB_REQUIRE(a.hd > 0 && a.hd <= 32 * QK_MAXE, "qk_norm_rope: head_dim %d is not in 1..%d", a.hd, 32 * QK_MAXE);
-    TB_REQUIRE(a.rot >= 0 && a.rot <= a.hd && a.rot % 2 == 0, "qk_norm_rope: rotary_dim %d must be even and <= head_dim %d", a.rot, a.hd);
+    TB_REQUIRE(a.rope.rot >= 0 && a.rope.rot <= a.hd && a.rope.rot % 2 == 0, "qk_norm_rope: rotary_dim %d must be even and <= head_dim %d", a.rope.rot, a.hd);
     TB_REQUIRE(!a.zero_in || (a.append && a.in != a.q_out && a.k_out == nullptr),
                "qk_norm_rope: zeroing the input needs every head to be read (append) and outputs elsewhere");
     TB_REQUIRE(!a.append || (a.cache.storage && a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv),
@@ -393,14 +416,14 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     const int warps = 4;
     const int n_heads = a.nh + a.nkv + (a.append ? a.nkv : 0);
     dim3 grid(a.T, (n_heads + warps - 1) / warps);
-    const size_t smem = ((size_t)warps * a.hd + a.rot) * sizeof(float);
+    const size_t smem = ((size_t)warps * a.hd + a.rope.rot) * sizeof(float);
     const int in_bytes = in_dtype == TB_F32 ? 4 : 2, out_bytes = out_dtype == TB_F32 ? 4 : 2;
     const int hv = a.hd == 256 ? 4 : a.hd / 32;        // consecutive elements per lane and half of the fast path
     auto aligned = [&](const void* p, long long stride_elems, int esz) {
         const int unit = hv * esz < 16 ? hv * esz : 16;   // read and written in pieces of at most 16 bytes
         return p == nullptr || (((uintptr_t)p % (size_t)unit) == 0 && (stride_elems * esz) % unit == 0);
     };
-    const bool vec = (a.hd == 64 || a.hd == 128 || a.hd == 256) && (a.rot == a.hd || !a.inv_freq) &&
+    const bool vec = (a.hd == 64 || a.hd == 128 || a.hd == 256) && (a.rope.rot == a.hd || !a.rope.inv_freq) &&
                      aligned(a.in, a.in_stride, in_bytes) && aligned(a.q_out, a.q_stride, out_bytes) &&
                      aligned(a.k_out, a.k_stride, out_bytes) && aligned(a.cache.storage, a.hd, out_bytes);
     if (in_dtype == TB_F32 && out_dtype == TB_F32) {

@@ -1,16 +1,25 @@
-// Argument block of the Q/K head norm + rotary (+ cache append) step, shared by its own kernel
-// (elementwise.cu) and by the matrix product that does the same in its epilogue (gemm_tc.cu); mirrors
+// Argument block of the Q/K head norm + rotary (+ cache append) kernel (elementwise.cu); mirrors
 // titan_b200.kernels.QkArgs.
 #pragma once
 #include "common.cuh"
+
+// What a position encoding hands to the kernels (titan_b200.kernels.RotaryArgs): the mixer passes it on
+// without looking inside.  angle_k(position) = (position + offset) * inv_freq[k]; the pair
+// (k, k + rot/2) of a head is rotated by that angle and scaled by ``magnitude``.
+struct TbRotary {
+    const float* inv_freq;                  // [rot/2] or null (no rotation)
+    int rot;                                // leading dims of a head that are rotated
+    float offset;                           // added to every position (0 for plain rotary)
+    float magnitude;                        // factor on cosines and sines (1 for plain rotary)
+};
 
 struct QkArgs {
     const void* in; int in_stride;          // [T][in_stride]: Q | K | V
     void* q_out; int q_stride;              // [T][q_stride]
     void* k_out; int k_stride;              // [T][k_stride] (null: K goes to the cache only)
     const float* q_w; const float* k_w;     // [hd] or null
-    const float* inv_freq;                  // [rot/2] or null (no rotation)
-    float eps; int rot; int nh; int nkv; int hd;
+    TbRotary rope;
+    float eps; int nh; int nkv; int hd;
     const int* pos_of; const int* seq_of; const int* slot_of_seq;
     TbKvView cache; int append; int T;
     int zero_in;                            // after reading a head, write zeros over it (an accumulation buffer is left clean)

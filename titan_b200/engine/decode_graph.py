@@ -41,6 +41,7 @@ class DecodeGraph:
         self.graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
         self.slots: Optional[List[int]] = None
         self.launches = 0                      # launcher calls inside one replay
+        self.logits: Dict[tuple, torch.Tensor] = {}    # per captured graph: the step's logits [B, vocab], valid until its next replay
         self.host_tokens = torch.zeros(B, dtype=torch.int32).pin_memory()
         self.host_slots = torch.zeros(B, dtype=torch.int32).pin_memory()
 
@@ -54,7 +55,7 @@ class DecodeGraph:
             self.slot_of_seq.copy_(self.host_slots, non_blocking=True)
             self.slots = list(slots)
 
-    def _body(self, feed_last: bool) -> None:
+    def _body(self, feed_last: bool) -> torch.Tensor:
         e = self.engine
         stream = K.current_stream()
         st = e.cache.state
@@ -67,8 +68,10 @@ class DecodeGraph:
         logits = e.model.logits(x, ctx, self.layout.want)
         e.sampler.sample(logits, self.slot_of_seq, stream, out=self.out_tokens)
         K.commit_lengths(self.slot_of_seq, self.kv_len, st.seq_len, stream)
+        return logits
 
-    def replay(self, feed_last: bool) -> None:
+    def replay(self, feed_last: bool) -> torch.Tensor:
+        """Run the step; returns its logits (memory of the graph: read them before the next replay)."""
         key = (feed_last, self.engine.sampler.seen is not None)
         g = self.graphs.get(key)
         if g is None:
@@ -81,9 +84,10 @@ class DecodeGraph:
             gc.disable()
             try:
                 with torch.cuda.graph(g):
-                    self._body(feed_last)
+                    self.logits[key] = self._body(feed_last)
             finally:
                 if was_enabled:
                     gc.enable()
             self.graphs[key] = g
         g.replay()
+        return self.logits[key]

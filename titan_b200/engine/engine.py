@@ -7,9 +7,11 @@ float32 logits at the wanted places.  berniehans/titan's counterpart is
 ``ForwardDriver::prefill_chunked`` / ``decode`` for one sequence
 (engine/engine-core/src/forward_driver.rs:939-1242, 3035-3070).
 
-Nothing is committed if a step is refused: validation and page reservation
+No length is committed if a step is refused: validation and page reservation
 happen before the first kernel (the reference's InvalidSize guards,
-forward_driver.rs:947-953, 3037-3043).
+forward_driver.rs:947-953, 3037-3043).  Pages reserved for a step that then
+failed inside a kernel stay with their slot (they are room, not content) and
+go back when the slot is freed.
 """
 from __future__ import annotations
 
@@ -40,12 +42,11 @@ class StepError(ValueError):
 class EngineOptions:
     dtype: object = "bfloat16"
     max_tokens: int = 8192            # tokens the cache holds over all live sequences (pages of 64)
-    max_context: Optional[int] = None  # longest sequence; default: what the cache and the model allow
+    max_context: Optional[int] = None  # longest sequence; default: what the cache and the model's position limit allow (more than that limit is refused)
     max_slots: Optional[int] = None
     max_batch: int = 64               # sequences per generation batch
     gemm: str = "fast"                # "plain": CUDA-core matrix products even in bfloat16
     attention: str = "fast"           # "plain": the any-size attention kernels even where a tensor-core one fits
-    qkv: str = "split"                # decode steps: "fused" runs projection + head norm + rotary + append as one kernel (cluster sums, deterministic; measured slower), "split" as three
     attn_chunk: int = 256             # keys per split of decode attention
     mark_freed_pages: bool = False    # debugging: pages of a freed slot are overwritten with a large finite value, so a stale read shows
     early_pages: bool = True          # decode attention requests pages of older positions before it waits for the kernels before it
@@ -67,13 +68,16 @@ class Engine:
         self.model = DecoderModel(self.spec)
         self.model.load(source_factory(self.model.declared_weights(), self.dtype, self.device))
         num_pages = -(-options.max_tokens // PAGE_SIZE)
-        max_context = min(options.max_context or num_pages * PAGE_SIZE, num_pages * PAGE_SIZE)
+        limit = int(self.spec.max_positions)           # the model's own limit (max_position_embeddings)
+        if options.max_context is not None and options.max_context > limit:
+            raise StepError(f"max_context {options.max_context} is beyond the model's {limit} positions")
+        max_context = min(options.max_context or limit, limit, num_pages * PAGE_SIZE)
         max_slots = options.max_slots or max(1, min(num_pages, (16 << 20) // max(1, -(-max_context // PAGE_SIZE))))
         self.cache = SequenceCache(self.model.cache_needs(), options.max_tokens, max_slots, max_context,
                                    self.dtype, self.device, mark_freed=options.mark_freed_pages)
         self.sampler = DeviceSampler(self.cache.state, max_slots, self.spec.vocab_size, self.device)
         self.scratch: Dict[str, torch.Tensor] = {}
-        self.step_options = {"gemm": options.gemm, "attention": options.attention, "qkv": options.qkv, "attn_chunk": options.attn_chunk,
+        self.step_options = {"gemm": options.gemm, "attention": options.attention, "attn_chunk": options.attn_chunk,
                              "early_pages": options.early_pages,
                              "max_context": self.cache.max_context,
                              "sm_count": torch.cuda.get_device_properties(self.device).multi_processor_count}
@@ -81,8 +85,11 @@ class Engine:
         self.d2h_bytes = 0
         self.steps_run = 0
         self.graph_launches = 0                   # launcher calls replayed through graphs
+        self.last_logits: Optional[torch.Tensor] = None    # logits of the latest generation step, on the device; valid until the next step
         self._graphs: Dict[int, DecodeGraph] = {}
         self._ran_eagerly = set()
+        # captured decode steps only if every part of the model allows it (Part.capturable)
+        self._capturable = all(getattr(part, "capturable", True) for b in self.model.blocks for part in b.parts())
 
     # -- construction ------------------------------------------------------- #
     @classmethod
@@ -161,9 +168,13 @@ class Engine:
         self.h2d_bytes += layout.h2d_bytes
         self.steps_run += 1
         ctx = self._context(layout)
-        self.sampler.observe(layout, ctx.stream)
-        x = self.model.forward_hidden(ctx, self.cache)
-        K.commit_lengths(layout.slot_of_seq, layout.kv_len, self.cache.state.seq_len, ctx.stream)
+        try:
+            self.sampler.observe(layout, ctx.stream)
+            x = self.model.forward_hidden(ctx, self.cache)
+            K.commit_lengths(layout.slot_of_seq, layout.kv_len, self.cache.state.seq_len, ctx.stream)
+        except Exception:
+            self.reset_accumulators()             # a kernel between a product and its consumer was refused
+            raise
         for e, s in zip(entries, starts):
             self.cache.commit(e.slot, s + len(e.tokens))
         return x, layout, ctx
@@ -197,7 +208,7 @@ class Engine:
     def advance(self, slots, tokens):
         """One token for each sequence: host token ids in, sampled host token ids out."""
         B = len(slots)
-        if not self.options.decode_graphs or B not in self._ran_eagerly:
+        if not self.options.decode_graphs or not self._capturable or B not in self._ran_eagerly:
             self._ran_eagerly.add(B)              # the first step of a batch size runs eagerly (lazy set-up happens there)
             return self._step_and_sample([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)])
         g = self._prepare_graph_step(slots, 1)
@@ -220,6 +231,8 @@ class Engine:
         """``steps`` decode steps without the host in the loop: every step feeds each sequence the
         token it sampled in the step before (``last_token`` of its slot).  Returns the last step's
         tokens as a device tensor; nothing is copied back."""
+        if not self._capturable:
+            raise StepError("a part of this model cannot run in a captured step; decode with advance()")
         g = self._prepare_graph_step(slots, steps)
         for _ in range(steps):
             self._replay(g, True)
@@ -245,9 +258,23 @@ class Engine:
         g.set_slots(slots)
         return g
 
+    def reset_accumulators(self) -> None:
+        """Zero the float32 buffers that decode products add into (``acc_*`` entries of the scratch).  Their
+        consumers leave them zeroed after every use; a step that ended between a product and its consumer (a
+        refused launch, a bounded wait that gave up) does not, and every later step of that shape would add
+        onto stale sums.  Called after any failed step; in place, because captured graphs hold the addresses."""
+        for scratch in [self.scratch] + [g.scratch for g in self._graphs.values()]:
+            for key, t in scratch.items():
+                if key.startswith("acc_"):
+                    t.zero_()
+
     def _replay(self, g: "DecodeGraph", feed_last: bool) -> None:
         before = K.launch_count
-        g.replay(feed_last)
+        try:
+            self.last_logits = g.replay(feed_last)
+        except Exception:
+            self.reset_accumulators()
+            raise
         captured = K.launch_count - before
         if captured:                              # this call captured the graph: remember its size
             g.launches = captured
@@ -261,11 +288,12 @@ class Engine:
         are invalid).  Synchronises the device; the generation loop calls it once per batch."""
         bad = K.wait_errors()
         if bad:
+            self.reset_accumulators()
             raise StepError("a kernel's bounded wait gave up, results are invalid: " + ", ".join(f"{k} (code {v})" for k, v in bad.items()))
 
     def _step_and_sample(self, entries) -> List[int]:
         x, layout, ctx = self.forward(entries)
-        logits = self.model.logits(x, ctx, layout.want)
+        logits = self.last_logits = self.model.logits(x, ctx, layout.want)
         tokens = self.sampler.sample(logits, layout.slot_of_seq, ctx.stream)
         host = tokens.cpu()
         self.d2h_bytes += host.numel() * 4

@@ -73,6 +73,8 @@ class DecoderModel:
         lay = ctx.layout
         x = torch.empty((lay.T, self.spec.hidden_size), dtype=torch.float32, device=ctx.device)
         K.embed(self.embedding, lay.tokens, x, ctx.stream)
+        if self.spec.embedding_scale is not None:
+            K.scale_f32(x, float(self.spec.embedding_scale), ctx.stream)
         for run, i in enumerate(self.spec.order):
             self.blocks[i].forward(x, ctx, cache.view_for_layer(self.cache_run_of(run)))
         return x
@@ -82,4 +84,6 @@ class DecoderModel:
         hn = self.final_norm.forward(x, ctx, rows)
         out = torch.empty((rows.numel(), self.spec.vocab_size), dtype=torch.float32, device=ctx.device)
         linear.matmul(hn, self.lm_head, out, linear.EPI_F32, ctx)
+        if self.spec.logit_scale is not None:
+            K.scale_f32(out, float(self.spec.logit_scale), ctx.stream)
         return out

@@ -36,10 +36,16 @@ class Batch(Structure):
                 ("T", c_int), ("B", c_int), ("max_new", c_int), ("max_kv_len", c_int)]
 
 
+class RotaryArgs(Structure):
+    """What a position encoding hands to the kernels; a mixer passes it on without looking inside.
+    angle_k(position) = (position + offset) * inv_freq[k]; cosines and sines are scaled by ``magnitude``."""
+    _fields_ = [("inv_freq", c_void_p), ("rot", c_int), ("offset", c_float), ("magnitude", c_float)]
+
+
 class QkArgs(Structure):
     _fields_ = [("inp", c_void_p), ("in_stride", c_int), ("q_out", c_void_p), ("q_stride", c_int),
                 ("k_out", c_void_p), ("k_stride", c_int), ("q_w", c_void_p), ("k_w", c_void_p),
-                ("inv_freq", c_void_p), ("eps", c_float), ("rot", c_int), ("nh", c_int), ("nkv", c_int),
+                ("rope", RotaryArgs), ("eps", c_float), ("nh", c_int), ("nkv", c_int),
                 ("hd", c_int), ("pos_of", c_void_p), ("seq_of", c_void_p), ("slot_of_seq", c_void_p),
                 ("cache", KvView), ("append", c_int), ("T", c_int), ("zero_in", c_int), ("kv_len", c_void_p)]
 
@@ -72,6 +78,8 @@ def lib():
         l.tb_uniform24.restype = ctypes.c_uint
         l.tb_uniform24.argtypes = [c_longlong, c_longlong, c_longlong]
         l.tb_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        l.tb_fill_random.argtypes = [c_void_p, c_int, c_longlong, ctypes.c_ulonglong, c_float, c_float, c_void_p]
+        l.tb_scale_f32.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
         l.tb_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
         l.tb_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
         l.tb_qk_norm_rope.argtypes = [POINTER(QkArgs), c_int, c_int, c_void_p]
@@ -103,9 +111,6 @@ def tlib():
         l.tb_attn_prefill_mma_check.argtypes = [POINTER(AttnArgs), c_int, c_int]
         l.tb_attn_prefill_tc.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
         l.tb_attn_prefill_tc_check.argtypes = [POINTER(AttnArgs), c_int, c_int]
-        l.tb_mma_probe.argtypes = [c_int, c_int, POINTER(ctypes.c_double)]
-        l.tb_gemm_qkv.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, POINTER(QkArgs), c_int, c_void_p]
-        l.tb_gemm_qkv_check.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_void_p, POINTER(QkArgs), c_int]
         _tlib = l
     return _tlib
 
@@ -144,6 +149,24 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, stream: 
     _need_cuda(table, tokens, out)
     _check(lib().tb_embed(table.data_ptr(), dtype_code(table.dtype), tokens.data_ptr(), out.data_ptr(),
                           tokens.numel(), table.shape[1], table.shape[0], stream))
+
+
+def fill_random(out: torch.Tensor, key: int, std: float, mean: float) -> None:
+    """out[i] = normal(key, i) * std + mean (float32 or bfloat16), or 15-bit integers (int32): the counter-based
+    generator of titan_b200.weights.random_init, on the device."""
+    _need_cuda(out)
+    if not out.is_contiguous():
+        raise KernelError("fill_random: a contiguous tensor is wanted")
+    code = -1 if out.dtype == torch.int32 else dtype_code(out.dtype)
+    _check(lib().tb_fill_random(out.data_ptr(), code, out.numel(), key & ((1 << 64) - 1), std, mean, current_stream()))
+
+
+def scale_f32(x: torch.Tensor, factor: float, stream: int) -> None:
+    """x *= factor in place (float32, contiguous)."""
+    _need_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("scale_f32: a contiguous float32 tensor is wanted")
+    _check(lib().tb_scale_f32(x.data_ptr(), x.numel(), factor, stream))
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, eps: float, stream: int,
@@ -189,24 +212,6 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, strea
         raise KernelError(f"gemm_tc: shapes do not fit: x {tuple(x.shape)} w {tuple(w.shape)}")
     _check(tlib().tb_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K_, x.stride(0), out.stride(0), epi,
                             splits, stream))
-
-
-def gemm_qkv_accepts(x: torch.Tensor, w: torch.Tensor, args: QkArgs, out_dtype: torch.dtype) -> bool:
-    """Can the Q | K | V projection run fused with head norm, rotation and cache append (tb_gemm_qkv)?"""
-    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out_dtype != torch.bfloat16 or x.stride(1) != 1 or not w.is_contiguous():
-        return False
-    return tlib().tb_gemm_qkv_check(x.shape[0], w.shape[0], x.shape[1], x.stride(0), x.data_ptr(), w.data_ptr(), byref(args), BF16) == 0
-
-
-def gemm_qkv(x: torch.Tensor, w: torch.Tensor, args: QkArgs, stream: int) -> None:
-    """Q | K | V = x . w^T per head, head norm, rotation, Q rows out and K, V rows into the cache: one kernel
-    (a decode step of at most 16 tokens, heads of 128, bfloat16)."""
-    _need_cuda(x, w)
-    _check(tlib().tb_gemm_qkv(x.data_ptr(), w.data_ptr(), x.shape[0], w.shape[0], x.shape[1], x.stride(0), byref(args), BF16, stream))
-
-
-def gemm_qkv_error() -> int:
-    return int(tlib().tb_gemm_qkv_error())
 
 
 def gemm_tc_error() -> int:
@@ -302,7 +307,7 @@ def wait_errors() -> dict:
     if the tensor-core library was never loaded."""
     if _tlib is None:
         return {}
-    found = {"gemm_tc": gemm_tc_error(), "gemm_qkv": gemm_qkv_error(), "attn_prefill_tc": attn_tc_error(), "attn_mma": attn_mma_error()}
+    found = {"gemm_tc": gemm_tc_error(), "attn_prefill_tc": attn_tc_error(), "attn_mma": attn_mma_error()}
     return {k: v for k, v in found.items() if v}
 
 
@@ -335,13 +340,6 @@ def set_gemm_plain_tile(which: int) -> None:
 def gemm_pair_clusters(epi: int) -> int:
     """CTA pairs the device holds at once for the pair kernel of this epilogue (0: it cannot run)."""
     return int(tlib().tb_gemm_tc_pair_clusters(int(epi)))
-
-
-def mma_probe(n: int, iters: int = 4096) -> float:
-    """Clocks one tcgen05.mma of 128 x n x 16 takes, issued back to back on every SM (a measurement, used by no step)."""
-    out = ctypes.c_double(0.0)
-    _check(tlib().tb_mma_probe(int(n), int(iters), byref(out)))
-    return float(out.value)
 
 
 def uniform24(seed: int, sequence: int, step: int) -> int:

@@ -8,7 +8,10 @@ scale) v over the keys the query may see (all earlier ones, or the last
 berniehans/titan: engine/engine-core/src/forward_cpu.rs:300-366 and 440-507;
 driver steps forward_driver.rs:1010-1133 (prompt) and 2168-2259 (one token).
 Q, K and V are three launches there; here their weights are concatenated at
-bind time into one [Q + 2 KV, H] matrix.
+bind time into one [Q + 2 KV, H] matrix.  Which tensors those are is the spec's
+business (``MixerSpec.names``): by default q_proj / k_proj / v_proj / o_proj
+``.weight`` under the prefix; a checkpoint that stores one fused tensor names
+it under the role "qkv".
 
 A step of single tokens writes K and V into the cache inside the norm/rotary
 kernel and attends over the cache.  A step with longer runs of tokens keeps the
@@ -33,26 +36,26 @@ from .base import MIXERS, POSITIONS, Mixer
 
 
 def decode_split(lay, kv_heads: int, options, fast: bool):
-    """(keys per split, number of splits) of decode attention.  Both depend on the batch size and on the
-    context limit only, so a sequence's result is the same whatever the other sequences hold, and a
-    captured step (whose grid is fixed) and an eager one cut the keys at the same places."""
-    bound = int(options.get("max_context", 0)) or lay.max_kv_len
+    """(fewest keys per split, most splits) of decode attention; the kernels cut every sequence by its own
+    length from these two numbers (``tb_split_keys``).  Neither depends on what the sequences hold or on the
+    longest context the engine allows, so a sequence's borders are the same in any cache and beside any
+    neighbours, and a captured step and an eager one cut the keys at the same places.
+
+    The any-size kernel takes splits of ``attn_chunk`` keys, as many as the longest sequence needs (an eager
+    step) or as the context limit needs (a captured one, whose grid is fixed; the spare ones leave at once):
+    the borders are multiples of ``attn_chunk`` either way.  The tensor-core kernel takes a number of splits
+    that fills the machine at this batch size: two of its CTAs fit an SM, one round of CTAs on about 0.6 of
+    those places was fastest over batch sizes 1 to 8, and at most 16 splits merge inside a thread-block
+    cluster (no scratch, no merge kernel)."""
     if not fast:
         chunk = int(options.get("attn_chunk", 256))
-    else:
-        # Two CTAs of the tensor-core kernel fit an SM.  Measured over batch sizes 1 to 8 at 8,192 keys: one
-        # round of CTAs on about 0.6 of those places is fastest (a second round costs a whole chunk, more
-        # splits a longer merge), chunks under 512 keys never pay, and at most 16 splits: up to 16 merge
-        # inside a thread-block cluster (no scratch, no merge kernel), which at batch 1 beats more, smaller
-        # chunks through scratch.
-        places = 2 * int(options.get("sm_count", 148))
-        pairs = lay.B * kv_heads
-        want = min(16, max(1, (3 * places // 5 + pairs // 2) // pairs))
-        chunk = max(512, -(-(-(-bound // want)) // 64) * 64)
-    # an eager step launches the splits its longest sequence needs; a captured one, whose grid cannot
-    # change, launches what the context limit needs (the extra CTAs leave at once)
-    cover = bound if options.get("fixed_splits") else lay.max_kv_len
-    return chunk, max(1, -(-cover // chunk))
+        cover = int(options.get("max_context", 0)) if options.get("fixed_splits") else 0
+        return chunk, max(1, -(-(cover or lay.max_kv_len) // chunk))
+    places = 2 * int(options.get("sm_count", 148))
+    pairs = lay.B * kv_heads
+    fill = float(options.get("attn_fill", 0.6))
+    splits = min(16, max(1, int(fill * places + pairs // 2) // pairs))
+    return int(options.get("attn_min_chunk", 128)), splits
 
 
 class AttentionMixer(Mixer):
@@ -80,25 +83,40 @@ class AttentionMixer(Mixer):
             return None
         return CacheNeed("kv", self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
 
+    def _names(self):
+        """Tensor names (relative to the prefix) by role; "qkv" only if the spec names a fused tensor."""
+        s = self.spec
+        names = {role: s.name(role, role + "_proj.weight") for role in ("q", "k", "v", "o")}
+        names["qkv"] = s.name("qkv")
+        if names["qkv"] is not None and self.shared:
+            raise ValueError("a mixer that reads another layer's cache has queries only: it cannot name a fused q|k|v tensor")
+        return names
+
     def weight_specs(self, prefix: str) -> List[WeightSpec]:
-        s, p = self.spec, prefix + self.spec.prefix
-        specs = [WeightSpec(p + "q_proj.weight", (self.Q, s.hidden_size)),
-                 WeightSpec(p + "o_proj.weight", (s.hidden_size, self.Q))]
-        if not self.shared:
-            specs += [WeightSpec(p + "k_proj.weight", (self.KV, s.hidden_size)),
-                      WeightSpec(p + "v_proj.weight", (self.KV, s.hidden_size))]
+        s, p, n = self.spec, prefix + self.spec.prefix, self._names()
+        specs = [WeightSpec(p + n["o"], (s.hidden_size, self.Q))]
+        if n["qkv"] is not None:
+            specs.append(WeightSpec(p + n["qkv"], (self.Q + 2 * self.KV, s.hidden_size)))
+        else:
+            specs.append(WeightSpec(p + n["q"], (self.Q, s.hidden_size)))
+            if not self.shared:
+                specs += [WeightSpec(p + n["k"], (self.KV, s.hidden_size)),
+                          WeightSpec(p + n["v"], (self.KV, s.hidden_size))]
         if s.qk_norm is not None:
             for which in ("q",) if self.shared else ("q", "k"):
                 specs.append(WeightSpec(p + s.qk_norm.weight.format(which), (s.head_dim,), "vector", ("one_plus_normal", 0.1)))
         return specs
 
     def bind(self, get) -> None:
-        s, p = self.spec, self.spec.prefix
-        parts = [get(p + "q_proj.weight")]
-        if not self.shared:
-            parts += [get(p + "k_proj.weight"), get(p + "v_proj.weight")]
-        self.w_qkv = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0]
-        self.w_o = get(p + "o_proj.weight")
+        s, p, n = self.spec, self.spec.prefix, self._names()
+        if n["qkv"] is not None:
+            self.w_qkv = get(p + n["qkv"])
+        else:
+            parts = [get(p + n["q"])]
+            if not self.shared:
+                parts += [get(p + n["k"]), get(p + n["v"])]
+            self.w_qkv = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else parts[0]
+        self.w_o = get(p + n["o"])
         if s.qk_norm is not None:
             self.q_norm = get(p + s.qk_norm.weight.format("q"))
             self.k_norm = None if self.shared else get(p + s.qk_norm.weight.format("k"))
@@ -108,13 +126,14 @@ class AttentionMixer(Mixer):
         group, index = cache
         key = (id(group), index)
         if key not in self._views:
-            assert isinstance(group, KVGroup)
+            if not isinstance(group, KVGroup):
+                raise TypeError(f"attention reads keys and values from a 'kv' cache group, not from {type(group).__name__}")
             self._views[key] = K.KvView(group.layer_storage(index).data_ptr(), group.table.data_ptr(), group.table_width,
                                         group.ring_rows, group.page_size, group.num_pages, group.need.num_kv_heads,
                                         group.need.head_dim)
         return self._views[key]
 
-    def _qk_args(self, qkv, width, q_buf, q_stride, view, lay, inv_freq, T, hd, append: bool, zero_in: bool) -> K.QkArgs:
+    def _qk_args(self, qkv, width, q_buf, q_stride, view, lay, rope, T, hd, append: bool, zero_in: bool) -> K.QkArgs:
         s = self.spec
         qa = K.QkArgs()
         qa.inp, qa.in_stride = (None if qkv is None else qkv.data_ptr()), width
@@ -122,9 +141,9 @@ class AttentionMixer(Mixer):
         qa.k_out, qa.k_stride = None, 0
         qa.q_w = None if self.q_norm is None else self.q_norm.data_ptr()
         qa.k_w = None if self.k_norm is None else self.k_norm.data_ptr()
-        qa.inv_freq = None if inv_freq is None else inv_freq.data_ptr()
+        qa.rope = rope                              # the position encoding's block, passed on as it is
         qa.eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
-        qa.rot, qa.nh, qa.nkv, qa.hd = self.position.rotary_dim, s.num_heads, (0 if self.shared else s.num_kv_heads), hd
+        qa.nh, qa.nkv, qa.hd = s.num_heads, (0 if self.shared else s.num_kv_heads), hd
         qa.pos_of, qa.seq_of, qa.slot_of_seq = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr()
         qa.cache, qa.append, qa.T = view, int(append), T
         qa.zero_in = int(zero_in)
@@ -137,25 +156,12 @@ class AttentionMixer(Mixer):
         width = Q if self.shared else Q + 2 * KV
         view = self._view(cache)
         decode = lay.all_single
-        tables = self.position.tables(ctx.device)
-        inv_freq = tables.get("inv_freq")
+        rope = self.position.kernel_args(ctx.device)
         # A decode step in bfloat16 sums Q | K | V in float32 (K slices of the product add into a zeroed
         # buffer), and the norm/rotary kernel rounds once, into the query buffer and the cache.
         wide_sum = decode and not self.shared and h.dtype == torch.bfloat16 and ctx.options.get("gemm", "fast") != "plain"
-        # ... or, on request (option qkv="fused") and where the kernel takes the shapes (heads of 128, at most
-        # 16 tokens), the projection itself sums its K slices inside a thread-block cluster and does norm,
-        # rotation and append.
-        fused = None
-        if wide_sum and ctx.options.get("qkv", "split") == "fused":
-            q_buf = ctx.empty((T, Q))
-            fused = self._qk_args(None, 0, q_buf, Q, view, lay, inv_freq, T, hd, append=True, zero_in=False)
-            if not K.gemm_qkv_accepts(h, self.w_qkv, fused, q_buf.dtype):
-                fused = None
-        if fused is not None:
-            K.gemm_qkv(h, self.w_qkv, fused, ctx.stream)
-            q_stride = Q
-        elif wide_sum:
-            key = f"qkv_sum_{T}x{width}"            # zeroed once; the norm/rotary kernel leaves it zeroed again
+        if wide_sum:
+            key = f"acc_qkv_{T}x{width}"            # zeroed once; the norm/rotary kernel leaves it zeroed again (Engine.reset_accumulators after a failed step)
             qkv = ctx.scratch.get(key)
             if qkv is None:
                 qkv = ctx.scratch[key] = torch.zeros((T, width), dtype=torch.float32, device=ctx.device)
@@ -165,17 +171,14 @@ class AttentionMixer(Mixer):
             qkv = ctx.empty((T, width))
             linear.matmul(h, self.w_qkv, qkv, linear.EPI_STORE, ctx)
             q_buf, q_stride = qkv, width
-        if fused is None:
-            # K and V go into the cache in this kernel when nothing of this step still has to read the rows
-            # they replace: always for single tokens and for caches that keep everything; in a ring only if
-            # every sequence starts at position 0 (attention then reads the step's own rows alone).
-            append_now = not self.shared and (decode or view.ring_rows == 0 or lay.all_fresh)
-            qa = self._qk_args(qkv, width, q_buf, q_stride, view, lay, inv_freq, T, hd, append=append_now, zero_in=wide_sum)
-            if not (self.shared or wide_sum):
-                qa.k_out, qa.k_stride = qkv.data_ptr() + Q * qkv.element_size(), width
-            K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
-        else:
-            append_now = True
+        # K and V go into the cache in this kernel when nothing of this step still has to read the rows
+        # they replace: always for single tokens and for caches that keep everything; in a ring only if
+        # every sequence starts at position 0 (attention then reads the step's own rows alone).
+        append_now = not self.shared and (decode or view.ring_rows == 0 or lay.all_fresh)
+        qa = self._qk_args(qkv, width, q_buf, q_stride, view, lay, rope, T, hd, append=append_now, zero_in=wide_sum)
+        if not (self.shared or wide_sum):
+            qa.k_out, qa.k_stride = qkv.data_ptr() + Q * qkv.element_size(), width
+        K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
 
         attn = ctx.empty((T, Q))
         aa = K.AttnArgs()

@@ -13,7 +13,10 @@ Mixer           ``cache_need() -> CacheNeed | None`` what it asks of the cache;
                 ``out`` (the float32 residual stream).  ``cache`` is ``(group, index)``
                 from ``SequenceCache.view_for_layer`` or None.
 FeedForward     ``forward(h[T,H], ctx, out_f32[T,H])`` adds its result into ``out``.
-PositionEncoding  owned by a mixer; ``tables(device)`` returns what the mixer's kernels need.
+PositionEncoding  owned by a mixer; ``kernel_args(device)`` returns the argument block that the
+                mixer hands to its kernels without looking inside (``kernels.RotaryArgs``: table of
+                inverse frequencies, rotated dims, an offset on positions, a factor on cosines and
+                sines).  The default builds it from ``rotary_dim`` and ``tables(device)["inv_freq"]``.
 Block           ``forward(x_f32, ctx, cache)`` runs norms, mixer and feed-forward in its arrangement.
 
 All of them: ``weight_specs(prefix) -> [WeightSpec]`` and ``bind(get)``, where
@@ -59,6 +62,11 @@ BLOCKS = Registry("block arrangement")
 
 
 class Part:
+    # Whether a decode step with this part may be captured as a CUDA graph: its forward launches kernels on the
+    # step's stream and reads nothing of the device on the host.  A part that cannot promise this says False,
+    # and the engine runs every step of a model that holds it eagerly.
+    capturable = True
+
     def weight_specs(self, prefix: str) -> List[WeightSpec]:
         return []
 
@@ -72,8 +80,17 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
+    rotary_dim = 0
+
     def tables(self, device) -> Dict[str, torch.Tensor]:
         return {}
+
+    def kernel_args(self, device):
+        """The block a mixer passes to its kernels.  Plain rotary: the table alone; an encoding with an
+        offset on positions or a factor on the rotation overrides this (or sets the two fields)."""
+        from .. import kernels as K
+        inv = self.tables(device).get("inv_freq")
+        return K.RotaryArgs(None if inv is None else inv.data_ptr(), int(self.rotary_dim) if inv is not None else 0, 0.0, 1.0)
 
 
 class Mixer(Part):

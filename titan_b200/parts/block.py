@@ -17,6 +17,8 @@ from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Part
 
 class PreNormBlock(Part):
     def __init__(self, spec):
+        if spec.feed_forward is None or spec.mixer_norm is None or spec.feed_forward_norm is None or spec.norms:
+            raise ValueError("the pre_norm arrangement takes a mixer, a feed-forward and exactly the two norms before them")
         self.spec = spec
         self.mixer_norm = NORMS.build(spec.mixer_norm)
         self.mixer = MIXERS.build(spec.mixer)

@@ -5,7 +5,10 @@ silu(g) = g / (1 + exp(-g)) (:210-219); its kernels fuse gate, up and SwiGLU in
 one launch (engine/engine-cuda/kernels/gemm_quant.cu:2589).  Here the gate and
 up matrices are interleaved row by row at bind time ([2F, H]: gate_0, up_0,
 gate_1, ...), so that one matrix product has both halves of every pair in the
-same tile and applies the activation in its epilogue.
+same tile and applies the activation in its epilogue.  The tensors' names come
+from the spec (``FeedForwardSpec.names``): gate_proj / up_proj / down_proj
+``.weight`` by default, or one stored [2F, H] tensor (gate rows, then up rows)
+under the role "gate_up".
 """
 from __future__ import annotations
 
@@ -27,18 +30,31 @@ class GatedMLP(FeedForward):
         self.spec = spec
         self.w_gate_up = self.w_down = None
 
+    def _names(self):
+        s = self.spec
+        names = {role: s.name(role, role + "_proj.weight") for role in ("gate", "up", "down")}
+        names["gate_up"] = s.name("gate_up")
+        return names
+
     def weight_specs(self, prefix: str) -> List[WeightSpec]:
-        s, p = self.spec, prefix + self.spec.prefix
-        return [WeightSpec(p + "gate_proj.weight", (s.intermediate_size, s.hidden_size)),
-                WeightSpec(p + "up_proj.weight", (s.intermediate_size, s.hidden_size)),
-                WeightSpec(p + "down_proj.weight", (s.hidden_size, s.intermediate_size))]
+        s, p, n = self.spec, prefix + self.spec.prefix, self._names()
+        if n["gate_up"] is not None:
+            first = [WeightSpec(p + n["gate_up"], (2 * s.intermediate_size, s.hidden_size))]
+        else:
+            first = [WeightSpec(p + n["gate"], (s.intermediate_size, s.hidden_size)),
+                     WeightSpec(p + n["up"], (s.intermediate_size, s.hidden_size))]
+        return first + [WeightSpec(p + n["down"], (s.hidden_size, s.intermediate_size))]
 
     def bind(self, get) -> None:
-        p = self.spec.prefix
-        gate, up = get(p + "gate_proj.weight"), get(p + "up_proj.weight")
-        self.w_gate_up = torch.stack([gate, up], dim=1).reshape(2 * self.spec.intermediate_size, self.spec.hidden_size).contiguous()
+        p, n, F = self.spec.prefix, self._names(), self.spec.intermediate_size
+        if n["gate_up"] is not None:
+            both = get(p + n["gate_up"])
+            gate, up = both[:F], both[F:]
+        else:
+            gate, up = get(p + n["gate"]), get(p + n["up"])
+        self.w_gate_up = torch.stack([gate, up], dim=1).reshape(2 * F, self.spec.hidden_size).contiguous()
         del gate, up
-        self.w_down = get(p + "down_proj.weight")
+        self.w_down = get(p + n["down"])
 
     def forward(self, h: torch.Tensor, ctx, out: torch.Tensor) -> None:
         act = ctx.empty((h.shape[0], self.spec.intermediate_size))

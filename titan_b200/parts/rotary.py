@@ -45,8 +45,6 @@ class NoPosition(PositionEncoding):
     def __init__(self, spec):
         self.spec = spec
 
-    rotary_dim = 0
-
 
 POSITIONS.register("rope", Rotary)
 POSITIONS.register("none", NoPosition)
