@@ -89,7 +89,10 @@ class PositionEncoding(Part):
         """The block a mixer passes to its kernels.  Plain rotary: the table alone; an encoding with an
         offset on positions or a factor on the rotation overrides this (or sets the two fields)."""
         from .. import kernels as K
-        inv = self.tables(device).get("inv_freq")
+        held = getattr(self, "_held_tables", None)
+        if held is None:
+            held = self._held_tables = self.tables(device)      # kept: the block holds an address into them
+        inv = held.get("inv_freq")
         return K.RotaryArgs(None if inv is None else inv.data_ptr(), int(self.rotary_dim) if inv is not None else 0, 0.0, 1.0)
 
 
