@@ -290,6 +290,61 @@ def test_attention_prefill_over_cache_and_new_keys(K, dtype, nh, nkv, hd, window
         assert rel_l2(o1.float().cpu(), want1.reshape(3, Q)) < KTOL[dtype], splits
 
 
+@pytest.mark.parametrize("nh,nkv,hd,window", [(8, 2, 128, 0), (4, 4, 64, 0), (6, 1, 128, 100), (16, 8, 64, 300)])
+def test_attention_of_continuation_chunks_on_tensor_cores(K, nh, nkv, hd, window):
+    """The tensor-core prompt kernels with keys and values taken from the cache's pages: one step holds a fresh
+    prompt, a chunk of 200 tokens onto 450 cached ones (query blocks and key tiles that straddle the border), a
+    chunk that starts inside a page, and a single token on a long sequence.  A far key of every sequence
+    stands out.  Against float64, and the two kernels against each other."""
+    g = torch.Generator().manual_seed(nh + hd + window)
+    slots, starts, news = [2, 0, 5, 3], [0, 450, 37, 700], [130, 200, 64, 1]
+    lay = layout_for(slots, starts, news)
+    T, Q, KV = sum(news), nh * hd, nkv * hd
+    scale = 1 / math.sqrt(hd)
+    full_k = [torch.randn(s + n, nkv, hd, generator=g) for s, n in zip(starts, news)]
+    full_v = [torch.randn(s + n, nkv, hd, generator=g) for s, n in zip(starts, news)]
+    q = torch.randn(T, nh, hd, generator=g).to(torch.bfloat16)
+    for i in range(4):
+        far = 3 if not window else max(0, starts[i] + news[i] - window)
+        full_k[i][far] *= 5.0
+    full_k, full_v = [k.to(torch.bfloat16) for k in full_k], [v.to(torch.bfloat16) for v in full_v]
+    cache = Paged(K, slots, [s + n for s, n in zip(starts, news)], nkv, hd, torch.bfloat16)
+    for i, s in enumerate(slots):
+        for p in range(starts[i] + news[i]):                       # the step's own keys are in the cache already
+            cache.put(s, p, full_k[i][p], full_v[i][p])
+    qb = q.reshape(T, Q).cuda()
+    want = torch.zeros(T, nh, hd)
+    at = 0
+    for i in range(4):
+        for j in range(news[i]):
+            want[at + j] = reference_attention(q[at + j].float(), full_k[i].float(), full_v[i].float(), starts[i] + j, window, scale)
+        at += news[i]
+    outs = {}
+    for name in ("tc", "mma"):
+        if name == "tc" and hd != 128:
+            continue
+        out = torch.full((T, Q), float("nan"), dtype=torch.bfloat16, device="cuda")
+        a = K.AttnArgs()
+        a.q, a.q_stride, a.out, a.out_stride = qb.data_ptr(), Q, out.data_ptr(), Q
+        a.kv_new, a.kv_stride = None, 0
+        a.cache, a.batch = cache.view, lay.c_struct()
+        a.nh, a.nkv, a.hd, a.window, a.scale = nh, nkv, hd, window, scale
+        accepts, run = (K.attn_prefill_tc_accepts, K.attn_prefill_tc) if name == "tc" else (K.attn_prefill_mma_accepts, K.attn_prefill_mma)
+        assert accepts(a, torch.bfloat16, K.KV_FROM_CACHE)
+        assert not accepts(a, torch.bfloat16, K.KV_FROM_STEP) and not accepts(a, torch.bfloat16, K.KV_NOWHERE)
+        run(a, K.KV_FROM_CACHE, stream())
+        assert K.wait_errors() == {}
+        outs[name] = out.float().cpu()
+        assert rel_l2(outs[name], want.reshape(T, Q)) < 8e-3, name
+        rows = ((outs[name] - want.reshape(T, Q)).norm(dim=1) / want.reshape(T, Q).norm(dim=1))
+        assert float(rows.max()) < 3e-2, (name, int(rows.argmax()))
+    if len(outs) == 2:
+        assert rel_l2(outs["tc"], outs["mma"]) < 8e-3
+    ring = Paged(K, slots, [s + n for s, n in zip(starts, news)], nkv, hd, torch.bfloat16, ring_rows=128)
+    a.cache = ring.view
+    assert not K.attn_prefill_mma_accepts(a, torch.bfloat16, K.KV_FROM_CACHE)       # a ring has lost the early keys
+
+
 def test_attention_refuses_bad_heads(K):
     a = K.AttnArgs()
     a.nh, a.nkv, a.hd = 5, 2, 32

@@ -240,3 +240,29 @@ def test_the_models_position_limit_bounds_the_context():
     with pytest.raises(StepError, match="beyond the model"):
         Engine.from_tensors(config_from_dict(cfg), w, dtype="float32", max_tokens=1024, max_context=200)
     assert Engine.from_tensors(config_from_dict(cfg), w, dtype="float32", max_tokens=1024, max_context=64).max_context == 64
+
+
+def test_a_prompt_in_chunks_takes_the_tensor_core_kernels(monkeypatch):
+    """A prompt fed as four chunks of 512 runs its continuation chunks on the tensor-core prompt attention (keys from
+    the cache's pages), not on the any-size kernel, and gives the logits of the prompt fed whole."""
+    from titan_b200 import Engine, StepEntry, kernels as K
+    from titan_b200.config import config_from_dict
+    w = random_weights(MID, 35, torch.bfloat16, std=0.03)
+    e = Engine.from_tensors(config_from_dict(MID), w, dtype="bfloat16", max_tokens=4096, max_context=2048)
+    toks = random_tokens(2048, MID["vocab_size"], 4)
+    used = {"tc": 0, "plain": 0}
+    tc, plain = K.attn_prefill_tc, K.attn_prefill
+    monkeypatch.setattr(K, "attn_prefill_tc", lambda *a, **k: (used.__setitem__("tc", used["tc"] + 1), tc(*a, **k))[1])
+    monkeypatch.setattr(K, "attn_prefill", lambda *a, **k: (used.__setitem__("plain", used["plain"] + 1), plain(*a, **k))[1])
+    want_rows = sorted(set(range(0, 2048, 61)) | {511, 512, 1535, 2047})
+    s = e.alloc_slot()
+    whole = e.step([StepEntry(s, toks, want_rows)])
+    e.free_slot(s)
+    s = e.alloc_slot()
+    parts = []
+    for at in range(0, 2048, 512):
+        parts.append(e.step([StepEntry(s, toks[at:at + 512], [r - at for r in want_rows if at <= r < at + 512])]))
+    e.free_slot(s)
+    e.check_kernels()
+    assert used["plain"] == 0 and used["tc"] == 2 * 5                   # two layers: one whole prompt and four chunks
+    rows_close(torch.cat(parts), whole.float().cpu(), "bfloat16", "chunks against the whole prompt")

@@ -3,6 +3,10 @@
 #pragma once
 #include "common.cuh"
 
+// Where the tensor-core prompt kernels take keys and values from.
+#define TB_KV_FROM_STEP 1      // the step's own rows: every sequence of the step starts at position 0
+#define TB_KV_FROM_CACHE 2     // the cache's pages, where the step's own keys have been appended already
+
 struct AttnArgs {
     const void* q; int q_stride;            // [T][q_stride], head h at h*hd
     const void* kv_new; int kv_stride;      // [T][kv_stride]: K heads then V heads of this step (may be null)

@@ -290,22 +290,25 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
 }
 
 
-// ------------------------------------------------------------------ prompts that start at position 0
+// ------------------------------------------------------------------ prompts and continuation chunks
 // One CTA per (sequence, query head, block of 64 queries), four compute warps of 16 query rows each
-// and a producer warp.  Queries, keys and values are read by TMA straight from the step's own
-// [T][Q | K | V] rows (64 x 64 boxes, 128-byte swizzle); the cache is not touched.  Key tiles of 64
-// run from the window's first key to the diagonal; S and P.V are mma.sync.m16n8k16 as above.
-// Heavy (late) query blocks are scheduled first.
+// and a producer warp.  Queries are read by TMA from the step's own [T][Q | K | V] rows (64 x 64 boxes,
+// 128-byte swizzle); keys and values from the same rows when every sequence starts at position 0 (the
+// cache is not touched), else from the cache's pages through the block table (a key tile is one page;
+// the step's own keys were appended before).  Key tiles of 64 run from the window's first key to the
+// diagonal; S and P.V are mma.sync.m16n8k16 as above.  Heavy (late) query blocks are scheduled first.
 struct PreArgs {
     __nv_bfloat16* out; int out_stride;
     const int* q_start; int B;
     int nh; int nkv; int window; float scale_log2;
     int k_col0; int v_col0;                  // first column of the K heads and of the V heads
+    // keys and values from the cache: first position of each sequence's rows, slots, block table, first V row of the map
+    int paged; const int* start_pos; const int* slot_of_seq; const int* table; int table_width; int v_row0;
 };
 
 template <int HD>
 __global__ void __launch_bounds__(DEC_THREADS, 2)
-attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, PreArgs a) {
+attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, const __grid_constant__ CUtensorMap kv_map, PreArgs a) {
     constexpr int STAGES = 2;
     constexpr int BOXES = HD / 64;
     constexpr uint32_t TILE_BYTES = 64 * HD * 2;
@@ -329,9 +332,10 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, PreArgs a) 
     if (seq < 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, kh = h / (a.nh / a.nkv);
-    const int r0 = blk * 64;                                         // first query position of the block
-    const int last_key = min(n - 1, r0 + 63);
-    const int first_key = a.window > 0 ? max(0, r0 - a.window + 1) : 0;
+    const int r0 = blk * 64;                                         // first row of the block among the sequence's rows
+    const int p0 = a.paged ? a.start_pos[seq] : 0;                   // position of the sequence's first row
+    const int last_key = p0 + min(n - 1, r0 + 63);
+    const int first_key = a.window > 0 ? max(0, p0 + r0 - a.window + 1) : 0;
     const int kt0 = first_key >> 6, n_tiles = (last_key >> 6) - kt0 + 1;
 
     if (threadIdx.x == 0) {
@@ -346,16 +350,19 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, PreArgs a) 
             mbar_expect_tx(qbar, TILE_BYTES);
 #pragma unroll
             for (int x = 0; x < BOXES; ++x) tma_load_2d(q_smem + x * 8192, &qkv_map, qbar, h * HD + x * 64, tok0 + r0);
+            const int* tab = a.paged ? a.table + (size_t)a.slot_of_seq[seq] * a.table_width : nullptr;
+            const int kx = a.paged ? 0 : a.k_col0 + kh * HD, vx = a.paged ? 0 : a.v_col0 + kh * HD;
             for (int i = 0; i < n_tiles; ++i) {
                 const int s = i % STAGES, round = i / STAGES;
                 if (round > 0) mbar_wait(empty + s, (round - 1) & 1, &g_attn_error, 3);
                 uint8_t* kd = base + s * 2 * TILE_BYTES;
-                const int row = tok0 + (kt0 + i) * 64;
+                const int krow = a.paged ? (tab[kt0 + i] * a.nkv + kh) * 64 : tok0 + (kt0 + i) * 64;
+                const int vrow = a.paged ? a.v_row0 + krow : krow;
                 mbar_expect_tx(full + s, 2 * TILE_BYTES);
 #pragma unroll
                 for (int x = 0; x < BOXES; ++x) {
-                    tma_load_2d(kd + x * 8192, &qkv_map, full + s, a.k_col0 + kh * HD + x * 64, row);
-                    tma_load_2d(kd + TILE_BYTES + x * 8192, &qkv_map, full + s, a.v_col0 + kh * HD + x * 64, row);
+                    tma_load_2d(kd + x * 8192, a.paged ? &kv_map : &qkv_map, full + s, kx + x * 64, krow);
+                    tma_load_2d(kd + TILE_BYTES + x * 8192, a.paged ? &kv_map : &qkv_map, full + s, vx + x * 64, vrow);
                 }
             }
         }
@@ -378,7 +385,8 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, PreArgs a) 
 #pragma unroll
     for (int i = 0; i < NT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
-    const int qp0 = r0 + warp * 16 + g, qp1 = qp0 + 8;              // positions of this thread's two rows
+    const int qr0 = r0 + warp * 16 + g, qr1 = qr0 + 8;              // this thread's two rows among the sequence's rows ...
+    const int qp0 = p0 + qr0, qp1 = p0 + qr1;                       // ... and their positions
     const int lo0 = a.window > 0 ? qp0 - a.window + 1 : 0, lo1 = a.window > 0 ? qp1 - a.window + 1 : 0;
 
     for (int i = 0; i < n_tiles; ++i) {
@@ -448,12 +456,12 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, PreArgs a) 
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const float i0 = 1.0f / l0, i1 = 1.0f / l1;
-    __nv_bfloat16* out0 = a.out + (size_t)(tok0 + qp0) * a.out_stride + h * HD + 2 * t;
-    __nv_bfloat16* out1 = a.out + (size_t)(tok0 + qp1) * a.out_stride + h * HD + 2 * t;
+    __nv_bfloat16* out0 = a.out + (size_t)(tok0 + qr0) * a.out_stride + h * HD + 2 * t;
+    __nv_bfloat16* out1 = a.out + (size_t)(tok0 + qr1) * a.out_stride + h * HD + 2 * t;
 #pragma unroll
     for (int nn = 0; nn < NT; ++nn) {
-        if (qp0 < n) *reinterpret_cast<uint32_t*>(out0 + nn * 8) = pack2(o[nn][0] * i0, o[nn][1] * i0);
-        if (qp1 < n) *reinterpret_cast<uint32_t*>(out1 + nn * 8) = pack2(o[nn][2] * i1, o[nn][3] * i1);
+        if (qr0 < n) *reinterpret_cast<uint32_t*>(out0 + nn * 8) = pack2(o[nn][0] * i0, o[nn][1] * i0);
+        if (qr1 < n) *reinterpret_cast<uint32_t*>(out1 + nn * 8) = pack2(o[nn][2] * i1, o[nn][3] * i1);
     }
 }
 
@@ -571,7 +579,7 @@ extern "C" int tb_attn_mma_error() {
 }
 
 template <int HD>
-static int launch_prefill(const CUtensorMap& map, const PreArgs& p, dim3 grid, cudaStream_t stream) {
+static int launch_prefill(const CUtensorMap& map, const CUtensorMap& kv_map, const PreArgs& p, dim3 grid, cudaStream_t stream) {
     constexpr size_t smem = 1024 + (size_t)(2 * 2 + 1) * 64 * HD * 2 + 8 * sizeof(uint64_t);
     static bool configured = false;
     if (!configured) {
@@ -580,39 +588,50 @@ static int launch_prefill(const CUtensorMap& map, const PreArgs& p, dim3 grid, c
         TB_REQUIRE(e == cudaSuccess, "attn_prefill_mma: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    tb_launch(attn_prefill_mma_kernel<HD>, grid, DEC_THREADS, smem, stream, map, p);
+    tb_launch(attn_prefill_mma_kernel<HD>, grid, DEC_THREADS, smem, stream, map, kv_map, p);
     return 0;
 }
 
-// 0 if the tensor-core prompt kernel takes this problem (every sequence of the step starts at
-// position 0, so all keys are among the step's own rows), else 1 with the reason.
-extern "C" int tb_attn_prefill_mma_check(const AttnArgs* a, int dtype, int all_fresh) {
+// 0 if the tensor-core prompt kernel takes this problem, else 1 with the reason.  source: TB_KV_FROM_STEP (every
+// sequence of the step starts at position 0, so all keys are among the step's own rows) or TB_KV_FROM_CACHE (keys
+// and values from the pages of a cache that keeps every key, the step's own appended already).
+extern "C" int tb_attn_prefill_mma_check(const AttnArgs* a, int dtype, int source) {
     TB_REQUIRE(dtype == TB_BF16, "attn_prefill_mma: bfloat16 only");
-    TB_REQUIRE(all_fresh, "attn_prefill_mma: a sequence continues from the cache");
+    TB_REQUIRE(source == TB_KV_FROM_STEP || source == TB_KV_FROM_CACHE, "attn_prefill_mma: a sequence continues from the cache and its keys are not all there");
     TB_REQUIRE(a->hd == 64 || a->hd == 128, "attn_prefill_mma: head_dim %d is not 64 or 128", a->hd);
     TB_REQUIRE(a->nkv > 0 && a->nh % a->nkv == 0, "attn_prefill_mma: heads");
-    TB_REQUIRE(a->kv_new && a->q_stride == a->kv_stride && a->q_stride % 8 == 0, "attn_prefill_mma: Q, K and V must be columns of one row-major buffer");
-    TB_REQUIRE(((uintptr_t)a->q & 15) == 0, "attn_prefill_mma: the buffer must be 16-byte aligned");
-    const long long off = ((const char*)a->kv_new - (const char*)a->q) / 2;
-    TB_REQUIRE(off == (long long)a->nh * a->hd, "attn_prefill_mma: K must follow Q in the buffer");
+    TB_REQUIRE(a->q_stride % 8 == 0 && ((uintptr_t)a->q & 15) == 0, "attn_prefill_mma: the queries must be 16-byte aligned rows");
+    if (source == TB_KV_FROM_STEP) {
+        TB_REQUIRE(a->kv_new && a->q_stride == a->kv_stride, "attn_prefill_mma: Q, K and V must be columns of one row-major buffer");
+        const long long off = ((const char*)a->kv_new - (const char*)a->q) / 2;
+        TB_REQUIRE(off == (long long)a->nh * a->hd, "attn_prefill_mma: K must follow Q in the buffer");
+    } else {
+        TB_REQUIRE(a->cache.storage && a->cache.page_size == PAGE && a->cache.ring_rows == 0, "attn_prefill_mma: needs a cache of %d-row pages that keeps every key", PAGE);
+        TB_REQUIRE(a->cache.head_dim == a->hd && a->cache.kv_heads == a->nkv, "attn_prefill_mma: the cache view does not match the heads");
+    }
     TB_REQUIRE(a->out_stride % 2 == 0 && ((uintptr_t)a->out & 3) == 0, "attn_prefill_mma: the output must be 4-byte aligned");
     return 0;
 }
 
-extern "C" int tb_attn_prefill_mma(const AttnArgs* args, int all_fresh, cudaStream_t stream) {
+extern "C" int tb_attn_prefill_mma(const AttnArgs* args, int source, cudaStream_t stream) {
     const AttnArgs& a = *args;
-    if (tb_attn_prefill_mma_check(args, TB_BF16, all_fresh)) return 1;
+    if (tb_attn_prefill_mma_check(args, TB_BF16, source)) return 1;
     TB_REQUIRE(a.batch.T > 0 && a.batch.B > 0, "attn_prefill_mma: no tokens");
-    CUtensorMap map;
+    CUtensorMap map, kv_map;
     if (tb_make_map_bf16(&map, a.q, a.batch.T, a.q_stride, a.q_stride, 64)) return 1;
+    kv_map = map;
     PreArgs p;
+    p.paged = source == TB_KV_FROM_CACHE;
+    if (p.paged && tb_make_map_bf16(&kv_map, a.cache.storage, 2LL * a.cache.num_pages * a.nkv * PAGE, a.hd, a.hd, PAGE)) return 1;
+    p.start_pos = a.batch.start_pos; p.slot_of_seq = a.batch.slot_of_seq; p.table = a.cache.table; p.table_width = a.cache.table_width;
+    p.v_row0 = a.cache.num_pages * a.nkv * PAGE;
     p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
     p.nh = a.nh; p.nkv = a.nkv; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
     p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd;
     const int blocks = (a.batch.T + 63) / 64 + a.batch.B;          // upper bound on sum over sequences of ceil(n / 64)
     TB_REQUIRE(blocks <= 65535, "attn_prefill_mma: too many query blocks (%d)", blocks);
     dim3 grid(a.nh, blocks);
-    const int rc = a.hd == 128 ? launch_prefill<128>(map, p, grid, stream) : launch_prefill<64>(map, p, grid, stream);
+    const int rc = a.hd == 128 ? launch_prefill<128>(map, kv_map, p, grid, stream) : launch_prefill<64>(map, kv_map, p, grid, stream);
     if (rc) return rc;
     TB_CHECK_LAUNCH("attn_prefill_mma");
     return 0;

@@ -1,4 +1,4 @@
-// Causal attention of prompts that start at position 0 on the tcgen05 tensor cores (head size 128).
+// Causal attention of prompts and of continuation chunks on the tcgen05 tensor cores (head size 128).
 //
 // One CTA per (sequence, query head, block of 128 queries).  Per tile of 64 keys:
 //     S = Q . K^T        tcgen05.mma, A = Q and B = K both K-major in shared memory, S in tensor memory
@@ -58,6 +58,9 @@ struct TcAttnArgs {
     const int* q_start; int B;
     int nh; int nkv; int window; float scale_log2;
     int k_col0; int v_col0;
+    // keys and values from the cache (continuation steps): the first position of each sequence's rows, its slot,
+    // the block table, and the row of the first V page in the cache's tensor map; paged = 0: from the step's rows
+    int paged; const int* start_pos; const int* slot_of_seq; const int* table; int table_width; int v_row0;
 };
 
 __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity, unsigned code) {
@@ -143,9 +146,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     if (seq < 0) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, kh = h / (a.nh / a.nkv);
-    const int r0 = blk * BQ;
-    const int last_key = min(n - 1, r0 + BQ - 1);
-    const int first_key = a.window > 0 ? max(0, r0 - a.window + 1) : 0;
+    const int r0 = blk * BQ;                                      // first row of the block among the sequence's rows of this step
+    const int p0 = a.paged ? a.start_pos[seq] : 0;                // position of the sequence's first row
+    const int last_key = p0 + min(n - 1, r0 + BQ - 1);
+    const int first_key = a.window > 0 ? max(0, p0 + r0 - a.window + 1) : 0;
     const int kt0 = first_key / BKEY, n_tiles = last_key / BKEY - kt0 + 1;
 
     if (threadIdx.x == 0) {
@@ -170,22 +174,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             tma_load_2d(q_smem, &q_map, q_full, h * HD, tok0 + r0);
             tma_load_2d(q_smem + Q_BOX, &q_map, q_full, h * HD + 64, tok0 + r0);
             // K and V tiles as their rings allow, whichever is free first (bounded polling)
+            const int* tab = a.paged ? a.table + (size_t)a.slot_of_seq[seq] * a.table_width : nullptr;
+            const int kx = a.paged ? 0 : a.k_col0 + kh * HD, vx = a.paged ? 0 : a.v_col0 + kh * HD;
             int ki = 0, vi = 0;
             for (uint32_t spin = 0; (ki < n_tiles || vi < n_tiles) && spin < (tbtma::WAIT_LIMIT << 4); ++spin) {
                 if (ki < n_tiles && (ki < KV_STAGES || tbtma::mbar_test(s_done + ki % KV_STAGES, (ki / KV_STAGES - 1) & 1))) {
-                    const int s = ki % KV_STAGES, row = tok0 + (kt0 + ki) * BKEY;
+                    const int s = ki % KV_STAGES;
+                    const int row = a.paged ? (tab[kt0 + ki] * a.nkv + kh) * BKEY : tok0 + (kt0 + ki) * BKEY;
                     uint8_t* kd = kv_smem + s * 2 * KV_TILE;
                     mbar_expect_tx(k_full + s, KV_TILE);
-                    tma_load_2d(kd, &kv_map, k_full + s, a.k_col0 + kh * HD, row);
-                    tma_load_2d(kd + KV_BOX, &kv_map, k_full + s, a.k_col0 + kh * HD + 64, row);
+                    tma_load_2d(kd, &kv_map, k_full + s, kx, row);
+                    tma_load_2d(kd + KV_BOX, &kv_map, k_full + s, kx + 64, row);
                     ++ki; spin = 0;
                 }
                 if (vi < n_tiles && (vi < KV_STAGES || tbtma::mbar_test(pv_done + vi % KV_STAGES, (vi / KV_STAGES - 1) & 1))) {
-                    const int s = vi % KV_STAGES, row = tok0 + (kt0 + vi) * BKEY;
+                    const int s = vi % KV_STAGES;
+                    const int row = a.paged ? a.v_row0 + (tab[kt0 + vi] * a.nkv + kh) * BKEY : tok0 + (kt0 + vi) * BKEY;
                     uint8_t* vd = kv_smem + s * 2 * KV_TILE + KV_TILE;
                     mbar_expect_tx(v_full + s, KV_TILE);
-                    tma_load_2d(vd, &kv_map, v_full + s, a.v_col0 + kh * HD, row);
-                    tma_load_2d(vd + KV_BOX, &kv_map, v_full + s, a.v_col0 + kh * HD + 64, row);
+                    tma_load_2d(vd, &kv_map, v_full + s, vx, row);
+                    tma_load_2d(vd + KV_BOX, &kv_map, v_full + s, vx + 64, row);
                     ++vi; spin = 0;
                 }
             }
@@ -232,7 +240,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         const int g = (warp - 2) >> 2, quarter = warp & 3;       // a warp may touch the tensor-memory lanes 32 * (warp % 4) ..
         const int row = quarter * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const int qpos = r0 + row;
+        const int qpos = p0 + r0 + row;                          // the row's position in its sequence
         const int lo = a.window > 0 ? qpos - a.window + 1 : 0;
         float m_run = -1e30f, l_run = 0.f;                       // the maximum P is taken against (may lag), the sum
         int mine = 0;                                            // tiles of this group so far
@@ -325,9 +333,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         }
         tmem_wait_ld<64>(o0);
         if (n_tiles > 1) tmem_wait_ld<64>(o1);
-        if (qpos < n) {
+        if (r0 + row < n) {
             const float c0 = w0 * inv, c1 = w1 * inv;
-            __nv_bfloat16* dst = a.out + (size_t)(tok0 + qpos) * a.out_stride + h * HD + g * 64;
+            __nv_bfloat16* dst = a.out + (size_t)(tok0 + r0 + row) * a.out_stride + h * HD + g * 64;
 #pragma unroll
             for (int i = 0; i < 64; i += 8) {
                 float r[8];
@@ -351,27 +359,41 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 }  // namespace
 
 // 0 if the tcgen05 prompt kernel takes this problem, else 1 with the reason in tb_last_error().
-extern "C" int tb_attn_prefill_tc_check(const AttnArgs* a, int dtype, int all_fresh) {
+// source: TB_KV_FROM_STEP (1): keys and values are the step's own rows, so every sequence must start at position 0;
+// TB_KV_FROM_CACHE (2): they are read from the cache's pages, where the step's own keys already lie (a cache
+// that keeps every key: no ring).
+extern "C" int tb_attn_prefill_tc_check(const AttnArgs* a, int dtype, int source) {
     TB_REQUIRE(dtype == TB_BF16, "attn_prefill_tc: bfloat16 only");
-    TB_REQUIRE(all_fresh, "attn_prefill_tc: a sequence continues from the cache");
+    TB_REQUIRE(source == TB_KV_FROM_STEP || source == TB_KV_FROM_CACHE, "attn_prefill_tc: a sequence continues from the cache and its keys are not all there");
     TB_REQUIRE(a->hd == HD, "attn_prefill_tc: head_dim %d is not %d", a->hd, HD);
     TB_REQUIRE(a->nkv > 0 && a->nh % a->nkv == 0, "attn_prefill_tc: heads");
-    TB_REQUIRE(a->kv_new && a->q_stride == a->kv_stride && a->q_stride % 8 == 0, "attn_prefill_tc: Q, K and V must be columns of one row-major buffer");
-    TB_REQUIRE(((uintptr_t)a->q & 15) == 0, "attn_prefill_tc: the buffer must be 16-byte aligned");
-    const long long off = ((const char*)a->kv_new - (const char*)a->q) / 2;
-    TB_REQUIRE(off == (long long)a->nh * a->hd, "attn_prefill_tc: K must follow Q in the buffer");
+    TB_REQUIRE(a->q_stride % 8 == 0 && ((uintptr_t)a->q & 15) == 0, "attn_prefill_tc: the queries must be 16-byte aligned rows");
+    if (source == TB_KV_FROM_STEP) {
+        TB_REQUIRE(a->kv_new && a->q_stride == a->kv_stride, "attn_prefill_tc: Q, K and V must be columns of one row-major buffer");
+        const long long off = ((const char*)a->kv_new - (const char*)a->q) / 2;
+        TB_REQUIRE(off == (long long)a->nh * a->hd, "attn_prefill_tc: K must follow Q in the buffer");
+    } else {
+        TB_REQUIRE(a->cache.storage && a->cache.page_size == BKEY && a->cache.ring_rows == 0, "attn_prefill_tc: needs a cache of %d-row pages that keeps every key", BKEY);
+        TB_REQUIRE(a->cache.head_dim == a->hd && a->cache.kv_heads == a->nkv, "attn_prefill_tc: the cache view does not match the heads");
+    }
     TB_REQUIRE(a->out_stride % 8 == 0 && ((uintptr_t)a->out & 15) == 0, "attn_prefill_tc: the output must be 16-byte aligned");
     return 0;
 }
 
-extern "C" int tb_attn_prefill_tc(const AttnArgs* args, int all_fresh, cudaStream_t stream) {
+extern "C" int tb_attn_prefill_tc(const AttnArgs* args, int source, cudaStream_t stream) {
     const AttnArgs& a = *args;
-    if (tb_attn_prefill_tc_check(args, TB_BF16, all_fresh)) return 1;
+    if (tb_attn_prefill_tc_check(args, TB_BF16, source)) return 1;
     TB_REQUIRE(a.batch.T > 0 && a.batch.B > 0, "attn_prefill_tc: no tokens");
-    CUtensorMap q_map, kv_map;       // the same rows, cut into boxes of 128 rows (Q) and of 64 rows (K, V)
+    CUtensorMap q_map, kv_map;       // the step's rows cut into boxes of 128 rows (Q), and of 64 rows (K, V) or the cache's pages
     if (tb_make_map_bf16(&q_map, a.q, a.batch.T, a.q_stride, a.q_stride, BQ)) return 1;
-    if (tb_make_map_bf16(&kv_map, a.q, a.batch.T, a.q_stride, a.q_stride, BKEY)) return 1;
     TcAttnArgs p;
+    p.paged = source == TB_KV_FROM_CACHE;
+    if (p.paged) {
+        const long long rows = 2LL * a.cache.num_pages * a.nkv * BKEY;
+        if (tb_make_map_bf16(&kv_map, a.cache.storage, rows, a.hd, a.hd, BKEY)) return 1;
+    } else if (tb_make_map_bf16(&kv_map, a.q, a.batch.T, a.q_stride, a.q_stride, BKEY)) return 1;
+    p.start_pos = a.batch.start_pos; p.slot_of_seq = a.batch.slot_of_seq; p.table = a.cache.table; p.table_width = a.cache.table_width;
+    p.v_row0 = a.cache.num_pages * a.nkv * BKEY;
     p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
     p.nh = a.nh; p.nkv = a.nkv; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
     p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd;

@@ -48,6 +48,9 @@ constexpr int BM = 128;          // rows of A per tile = M of the instruction
 constexpr int BK = 64;           // bf16 elements per stage row = 128 bytes = one swizzle span
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
+#ifndef TB_SWAP16_STAGES
+#define TB_SWAP16_STAGES 6
+#endif
 
 __device__ unsigned int g_tc_error = 0;
 
@@ -98,7 +101,7 @@ struct TcArgs {
 
 // TMA ring depth.  Decode tiles (BN <= 64) take as many stages as still let two CTAs share an SM: the
 // ring is filled before the wait on the previous kernel, so its depth is what bridges kernel boundaries.
-template <int BN> constexpr int stages_for() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 4 : (BN >= 32 ? 5 : 6))); }
+template <int BN> constexpr int stages_for() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 4 : (BN >= 32 ? 5 : TB_SWAP16_STAGES))); }
 // Swap mode with 65..128 rows of activations: three stages, so that two CTAs share an SM here too and the
 // 192 tiles of the gate-and-up product are resident at once (measured at 96 rows: 59.8 -> 44.0 us).  The
 // bfloat16 store (a short prompt's Q|K|V: 48 tiles, no K slices) keeps the deeper ring of one CTA per SM.

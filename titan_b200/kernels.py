@@ -250,22 +250,27 @@ def set_attn_decode_cluster(on: bool) -> None:
     tlib().tb_attn_decode_set_cluster(int(bool(on)))
 
 
-def attn_prefill_mma_accepts(args: AttnArgs, dtype: torch.dtype, all_fresh: bool) -> bool:
-    return dtype == torch.bfloat16 and tlib().tb_attn_prefill_mma_check(byref(args), BF16, int(all_fresh)) == 0
+# Where the tensor-core prompt kernels take keys and values from: nowhere they can (0), the step's own rows (every
+# sequence starts at position 0), or the cache's pages (the step's keys are appended already; no ring).
+KV_NOWHERE, KV_FROM_STEP, KV_FROM_CACHE = 0, 1, 2
 
 
-def attn_prefill_mma(args: AttnArgs, all_fresh: bool, stream: int) -> None:
-    """Causal attention of prompts that start at position 0, on tensor cores (bfloat16, head_dim 64 or 128)."""
-    _check(tlib().tb_attn_prefill_mma(byref(args), int(all_fresh), stream))
+def attn_prefill_mma_accepts(args: AttnArgs, dtype: torch.dtype, source: int) -> bool:
+    return dtype == torch.bfloat16 and tlib().tb_attn_prefill_mma_check(byref(args), BF16, int(source)) == 0
 
 
-def attn_prefill_tc_accepts(args: AttnArgs, dtype: torch.dtype, all_fresh: bool) -> bool:
-    return dtype == torch.bfloat16 and tlib().tb_attn_prefill_tc_check(byref(args), BF16, int(all_fresh)) == 0
+def attn_prefill_mma(args: AttnArgs, source: int, stream: int) -> None:
+    """Causal attention of prompts and continuation chunks on tensor cores (bfloat16, head_dim 64 or 128)."""
+    _check(tlib().tb_attn_prefill_mma(byref(args), int(source), stream))
 
 
-def attn_prefill_tc(args: AttnArgs, all_fresh: bool, stream: int) -> None:
-    """Causal attention of prompts that start at position 0 on the tcgen05 tensor cores (bfloat16, head_dim 128)."""
-    _check(tlib().tb_attn_prefill_tc(byref(args), int(all_fresh), stream))
+def attn_prefill_tc_accepts(args: AttnArgs, dtype: torch.dtype, source: int) -> bool:
+    return dtype == torch.bfloat16 and tlib().tb_attn_prefill_tc_check(byref(args), BF16, int(source)) == 0
+
+
+def attn_prefill_tc(args: AttnArgs, source: int, stream: int) -> None:
+    """Causal attention of prompts and continuation chunks on the tcgen05 tensor cores (bfloat16, head_dim 128)."""
+    _check(tlib().tb_attn_prefill_tc(byref(args), int(source), stream))
 
 
 def attn_tc_error() -> int:

@@ -210,11 +210,20 @@ class AttentionMixer(Mixer):
                 aa.kv_new, aa.kv_stride = None, 0
             else:
                 aa.kv_new, aa.kv_stride = qkv.data_ptr() + Q * qkv.element_size(), width
-            mode = "plain" if self.shared else ctx.options.get("attention", "fast")   # "fast" | "mma" | "plain"
-            if mode == "fast" and K.attn_prefill_tc_accepts(aa, q_buf.dtype, lay.all_fresh):
-                K.attn_prefill_tc(aa, lay.all_fresh, ctx.stream)
-            elif mode in ("fast", "mma") and K.attn_prefill_mma_accepts(aa, q_buf.dtype, lay.all_fresh):
-                K.attn_prefill_mma(aa, lay.all_fresh, ctx.stream)
+            mode = ctx.options.get("attention", "fast")   # "fast" | "mma" | "plain"
+            # The tensor-core kernels read keys and values from the step's own rows when every sequence starts at
+            # position 0, and else from the cache's pages, if the step's keys lie there already (a cache that keeps
+            # everything; a reader of another layer's cache finds them there in any case).
+            if lay.all_fresh and not self.shared:
+                source = K.KV_FROM_STEP
+            elif view.ring_rows == 0 and (self.shared or append_now):
+                source = K.KV_FROM_CACHE
+            else:
+                source = K.KV_NOWHERE
+            if mode == "fast" and source and K.attn_prefill_tc_accepts(aa, q_buf.dtype, source):
+                K.attn_prefill_tc(aa, source, ctx.stream)
+            elif mode in ("fast", "mma") and source and K.attn_prefill_mma_accepts(aa, q_buf.dtype, source):
+                K.attn_prefill_mma(aa, source, ctx.stream)
             else:
                 K.attn_prefill(aa, q_buf.dtype, ctx.stream)
             if not self.shared and not append_now:
