@@ -155,16 +155,20 @@ def time_decode(engine, torch, K, batch, kv_timed, steps, warmup):
             engine.free_slot(s)
 
 
-def time_prefill(engine, torch, T, warmup, reps):
+def time_prefill(engine, torch, T, warmup, reps, chunk=None):
+    """One prompt of T tokens in one step, or (chunk) in steps of ``chunk`` tokens; (median, best) ms."""
     from titan_b200 import StepEntry
     prompt = [(13 * i + 5) % engine.vocab_size for i in range(T)]
+    chunk = chunk or T
     times = []
     for r in range(warmup + reps):
         s = engine.alloc_slot()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         start.record()
-        engine.step([StepEntry(s, prompt, [T - 1])])
+        for at in range(0, T, chunk):
+            part = prompt[at:at + chunk]
+            engine.step([StepEntry(s, part, [len(part) - 1] if at + chunk >= T else [])])
         stop.record()
         torch.cuda.synchronize()
         engine.free_slot(s)
@@ -219,6 +223,7 @@ def run_ours(args):
     pre_clocks.start()
     pre_ms, pre_best = time_prefill(engine, torch, T, 3, 12)       # ~0.4 s back to back: the power cap is reached
     pre_rec = pre_clocks.stop()
+    chunked_ms = time_prefill(engine, torch, T, 2, 6, chunk=512)[0]    # the same prompt in chunks of 512 (continuation steps)
     flops = prefill_flops(cfg, args.layers, T)
     engine.check_kernels()                                        # raises if a bounded wait gave up anywhere
     line = {
@@ -236,10 +241,109 @@ def run_ours(args):
         "prefill": {"value": round(T * 1e3 / pre_ms, 1), "tokens": T, "ms": round(pre_ms, 3),
                     "frac": round(flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
                     "frac_of_sustained_peak": round(flops / (pre_ms * 1e-3) / (pk.get("bf16_tflops_sustained", pk["bf16_tflops"]) * 1e12), 4),
-                    "best_ms": round(pre_best, 3), "sm_mhz": pre_rec.get("sm_mhz"), "reasons": pre_rec.get("reasons")},
+                    "best_ms": round(pre_best, 3), "in_chunks_of_512_ms": round(chunked_ms, 3), "sm_mhz": pre_rec.get("sm_mhz"), "reasons": pre_rec.get("reasons")},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm, "unit": "GB/s",
                      "frac": round(achieved / hbm, 4)},
         "points": points, "clocks": clock_rec, "kernel_error": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# The further configurations of the benchmark set: other layer sizes, ragged prompts, longer contexts, sampling.
+QWEN3_4B = dict(QWEN3_8B, hidden_size=2560, intermediate_size=9728, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)
+OTHER_CONFIGS = {
+    4: dict(name="Qwen3-4B shape", cfg=QWEN3_4B, seed=3, batch=8, prompt_range=(512, 16384), context=32768, steps=256,
+            temperature=0.0, end_of_context=True),
+    5: dict(name="Qwen3-32B shape", cfg=QWEN3_32B, seed=4, batch=16, prompt_range=(256, 4096), context=8192, steps=512,
+            temperature=0.7, end_of_context=False),
+}
+
+
+def run_other(args, which):
+    """Configurations 4 and 5: unequal prompts of seeded lengths in one step (prefill tokens per second over all of
+    them), then the stated number of decode steps through the Python entry point (tokens per second, bytes a step
+    must read over its time), and for configuration 4 the same at the end of its 32,768-token context."""
+    import random
+
+    import torch
+
+    from titan_b200 import Engine, SamplerParams, StepEntry, kernels as K
+    from titan_b200.config import config_from_dict
+    c = OTHER_CONFIGS[which]
+    pk = peaks()
+    cfg = dict(c["cfg"])
+    layers_of_model = cfg["num_hidden_layers"]
+    if args.layers != 36:
+        cfg["num_hidden_layers"] = args.layers
+    B, context, steps = c["batch"], c["context"], c["steps"]
+    rng = random.Random(c["seed"])
+    lengths = [rng.randint(*c["prompt_range"]) for _ in range(B)]
+    engine = Engine.from_random(config_from_dict(cfg), seed=c["seed"], dtype="bfloat16", max_tokens=B * context,
+                                max_context=context, max_slots=B, max_batch=B)
+    V = engine.vocab_size
+    params = SamplerParams.greedy() if c["temperature"] <= 0 else SamplerParams(c["temperature"], 1.0, 0, 1.0, c["seed"])
+
+    def run(lengths, steps):
+        slots = [engine.alloc_slot() for _ in lengths]
+        try:
+            engine.sampler.configure(slots, [params] * len(slots), list(range(len(slots))))
+            prompts = [[(13 * i + 977 * j + 5) % V for i in range(n)] for j, n in enumerate(lengths)]
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            torch.cuda.synchronize()
+            ev[0].record()
+            at = 0
+            while at < len(slots):                               # prompts of up to 65,536 tokens to a step
+                take, total = [], 0
+                while at + len(take) < len(slots) and (not take or total + lengths[at + len(take)] <= 65536):
+                    total += lengths[at + len(take)]
+                    take.append(at + len(take))
+                engine.step([StepEntry(slots[j], prompts[j], []) for j in take])
+                at += len(take)
+            ev[1].record()
+            tokens = [(7 * i + 1) % V for i in range(len(slots))]
+            for _ in range(max(3, args.warmup)):
+                tokens = engine.advance(slots, tokens)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            ev[2].record()
+            for _ in range(steps):
+                tokens = engine.advance(slots, tokens)
+            ev[3].record()
+            torch.cuda.synchronize()
+            wall = (time.perf_counter() - t0) * 1e3 / steps
+            engine.check_kernels()
+            held = sum(lengths) + len(lengths) * (max(3, args.warmup) + steps // 2)
+            step_bytes = decode_flops_and_bytes(engine, 1, held)
+            ms = ev[2].elapsed_time(ev[3]) / steps
+            return dict(prefill_ms=ev[0].elapsed_time(ev[1]), ms=ms, wall_ms=wall, gbs=step_bytes / ms / 1e6, bytes=step_bytes)
+        finally:
+            for s in slots:
+                engine.free_slot(s)
+    first = run(lengths, steps)
+    points = {}
+    if c["end_of_context"]:
+        tail_steps = 128
+        tail = run([context - tail_steps - max(3, args.warmup) - 1] * B, tail_steps)
+        points = {"decode_at_context_end": round(B * 1e3 / tail["ms"], 1), "decode_at_context_end_ms": round(tail["ms"], 4),
+                  "decode_at_context_end_frac": round(tail["gbs"] / pk["hbm_gbs"], 4), "kv_len_at_context_end": context - tail_steps - 1,
+                  "prefill_of_long_prompts_tok_s": round(B * (context - tail_steps - max(3, args.warmup) - 1) * 1e3 / tail["prefill_ms"], 1)}
+    line = {
+        "metric": f"decode tok/s ({c['name']}, bf16, batch {B}, unequal prompts)", "value": round(B * 1e3 / first["ms"], 1), "unit": "tok/s",
+        "n_gpus": 1, "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": round(first["ms"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": f"synthetic: random weights (seed {c['seed']}), prompts of seeded lengths and patterned ids, run through the engine",
+        "config": {"model": c["name"], "layers": cfg["num_hidden_layers"], "layers_of_model": layers_of_model, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": B, "seq_len": context,
+                   "prompt_tokens_min": min(lengths), "prompt_tokens_max": max(lengths), "prompt_tokens_total": sum(lengths),
+                   "temperature": c["temperature"], "parallelism": "single_gpu", "l2": "inputs_larger_than_l2", "peaks": pk["source"]},
+        "e2e": {"value": round(B * 1e3 / first["wall_ms"], 1), "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B},
+        "prefill": {"value": round(sum(lengths) * 1e3 / first["prefill_ms"], 1), "tokens": sum(lengths), "ms": round(first["prefill_ms"], 3)},
+        "roofline": {"bound": "hbm", "achieved": round(first["gbs"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(first["gbs"] / pk["hbm_gbs"], 4), "bytes_per_step": first["bytes"]},
+        "points": points, "device_memory_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1),
     }
     print(json.dumps(line))
     return 0
@@ -379,6 +483,7 @@ def main():
     ap.add_argument("--point-steps", type=int, default=256, help="decode steps of each entry of 'points'")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--config", type=int, default=3, choices=[3, 4, 5], help="3: the benchmark configuration (default); 4, 5: the Qwen3-4B and Qwen3-32B shaped ones")
     ap.add_argument("--profile-case", action="store_true", help="run the small one-layer case used for ncu captures and exit")
     ap.add_argument("--micro", action="store_true", help="time the layer's kernels alone (CUDA events) and exit; text lines, not the JSON line")
     args = ap.parse_args()
@@ -395,6 +500,8 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.config != 3:
+        return run_other(args, args.config)
     return run_ours(args)
 
 
