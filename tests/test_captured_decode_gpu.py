@@ -112,3 +112,24 @@ def test_decoding_on_the_device_against_the_plain_implementation(models, model):
         e.finish(s)
     agree = sum(int(a == m[-1]) for a, m in zip(last, made))
     assert agree >= 2, (last, [m[-1] for m in made])      # float32 sums of K slices add in any order: a near-tie may fall the other way once
+
+
+@pytest.mark.parametrize("B", [1, 8, 20])
+def test_folded_norms_change_results_by_rounding_only(models, B):
+    """Decode steps with the norms folded into the products that consume them (the default) and with the norms as
+    kernels of their own: both against the plain implementation, and the option really switches (launch counts)."""
+    from titan_b200 import Engine, kernels as K
+    from titan_b200.config import config_from_dict
+    cfg, w, w32 = models["hd128"]
+    lens = [40 + 13 * i for i in range(B)]
+    reqs = [random_tokens(n + 12, cfg["vocab_size"], 500 + n) for n in lens]
+    want = [P.forward_logits(cfg, w32, r)[n - 1:] for r, n in zip(reqs, lens)]
+    launches = {}
+    for fold in (True, False):
+        e = Engine.from_tensors(config_from_dict(cfg), w, dtype="bfloat16", max_tokens=B * 384, max_context=384, max_batch=B, fold_norms=fold)
+        before = K.launch_count
+        got = teacher_forced(e, reqs, lens, 12)
+        launches[fold] = K.launch_count - before + e.graph_launches
+        for i in range(B):
+            rows_close(got[i], want[i], "bfloat16", f"batch {B}, fold_norms={fold}, request {i}")
+    assert launches[True] < launches[False]

@@ -118,3 +118,48 @@ def test_refuses_misaligned(K):
         K.gemm_tc(x, w, out, K.EPI_F32, stream())
     with pytest.raises(K.KernelError, match="bfloat16"):
         K.gemm_tc(x.float(), w.float(), out, K.EPI_F32, stream())
+
+
+@pytest.mark.parametrize("M,N,Kd", [(1, 256, 64), (1, 6144, 4096), (3, 200, 72), (8, 1000, 520), (13, 4096, 1024), (16, 24576, 4096),
+                                    (17, 384, 256), (32, 2600, 1096)])
+def test_the_norm_before_a_decode_product_folded_into_it(K, M, N, Kd):
+    """tb_gemm_tc_normed: rmsnorm(x) . W^T with the norm inside the product, against the plain functions.  With
+    the SwiGLU epilogue the result is complete; with float32 sums (K cut into slices) the product of the unscaled
+    rows comes out beside the rows' sums of squares, and the head norm / rotary kernel applies the scale.  The
+    rows' sizes differ by orders of magnitude, so a scale that is lost or taken from another row shows."""
+    g = torch.Generator().manual_seed(M * 31 + N + Kd)
+    x = torch.randn(M, Kd, generator=g) * (10.0 ** torch.linspace(-1, 2, M))[:, None]
+    nw = 1 + 0.2 * torch.randn(Kd, generator=g)
+    w = (torch.randn(N - N % 2, Kd, generator=g) * 0.1).to(torch.bfloat16)
+    N = w.shape[0]
+    eps = 1e-5
+    h = P.rms_norm(x, nw, eps)
+    want = P.linear(h, w.float())
+    xd, nd, wd = x.cuda(), nw.cuda(), w.cuda()
+    # SwiGLU: gate and up rows interleaved, as the feed-forward part binds them
+    act = torch.full((M, -(-(N // 2) // 8) * 8), float("nan"), dtype=torch.bfloat16, device="cuda")[:, :N // 2]
+    assert K.gemm_tc_normed_accepts(xd, nd, wd, act, K.EPI_SWIGLU, None)
+    K.gemm_tc_normed(xd, nd, eps, wd, act, K.EPI_SWIGLU, stream())
+    assert K.gemm_tc_error() == 0
+    assert rel_l2(act.float().cpu(), P.swiglu(want[:, 0::2], want[:, 1::2])) < 6e-3
+    per_row = (act.float().cpu() - P.swiglu(want[:, 0::2], want[:, 1::2])).norm(dim=1) / P.swiglu(want[:, 0::2], want[:, 1::2]).norm(dim=1)
+    assert float(per_row.max()) < 1.2e-2, per_row
+    # float32 sums + sums of squares, twice in a row into the same buffers (cleared by the caller in between)
+    n4 = -(-N // 4) * 4
+    for _ in range(2):
+        acc = torch.zeros(M, n4, device="cuda")[:, :N]
+        sums = torch.zeros(M, device="cuda")
+        assert K.gemm_tc_normed_accepts(xd, nd, wd, acc, K.EPI_ADD, sums)
+        K.gemm_tc_normed(xd, nd, eps, wd, acc, K.EPI_ADD, stream(), sumsq=sums)
+        assert K.gemm_tc_error() == 0
+        assert rel_l2(sums.cpu(), (x.double() ** 2).sum(1).float()) < 1e-5
+        scale = 1.0 / torch.sqrt(sums.cpu() / Kd + eps)
+        got = acc.cpu() * scale[:, None]
+        assert rel_l2(got, want) < 6e-3
+        rows = (got - want).norm(dim=1) / want.norm(dim=1)
+        assert float(rows.max()) < 1.2e-2, rows
+    # what it refuses
+    assert not K.gemm_tc_normed_accepts(xd, nd, wd, acc, K.EPI_ADD, None)                   # sums need their place
+    assert not K.gemm_tc_normed_accepts(xd, nd, wd, act, K.EPI_SWIGLU, sums)
+    big = torch.zeros(33, Kd, device="cuda")
+    assert not K.gemm_tc_normed_accepts(big, nd, wd, torch.zeros(33, N // 2, dtype=torch.bfloat16, device="cuda"), K.EPI_SWIGLU, None)

@@ -202,6 +202,43 @@ def test_attention_prefill_tensor_cores_long_prompt_many_times(K):
     assert not torch.isnan(outs["mma"]).any()
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 128), (3, 1, 48)])
+def test_qk_norm_rope_scales_rows_whose_norm_was_folded_into_the_projection(K, nh, nkv, hd):
+    """Float32 sums of unscaled rows in, with the rows' sums of squares: the kernel scales every row (Q, K and V
+    heads) by 1/sqrt(sum / width + eps) first, and the result equals that of scaled rows."""
+    g = torch.Generator().manual_seed(nh + hd)
+    T, Q, KV, width, eps = 5, nh * hd, nkv * hd, 777, 1e-6
+    slots, lens = [1, 3, 0, 2, 4], [9, 70, 1, 64, 200]
+    lay = layout_for(slots, [n - 1 for n in lens], [1] * T)
+    rows = torch.randn(T, Q + 2 * KV, generator=g)
+    sums = torch.rand(T, generator=g) * 5000 + 10
+    scale = 1.0 / torch.sqrt(sums / width + eps)
+    qw, kw = 1 + 0.1 * torch.randn(hd, generator=g), 1 + 0.1 * torch.randn(hd, generator=g)
+    k_ = torch.arange(hd // 2, dtype=torch.float64)
+    inv = (torch.tensor(1e4, dtype=torch.float64) ** (-2 * k_ / hd)).float().cuda()
+    keep = (qw.cuda(), kw.cuda(), sums.cuda())
+    outs = []
+    for folded in (True, False):
+        cache = Paged(K, slots, lens, nkv, hd, torch.bfloat16)
+        buf = (rows if folded else rows * scale[:, None]).cuda()
+        q_out = torch.empty(T, Q, dtype=torch.bfloat16, device="cuda")
+        a = K.QkArgs()
+        a.inp, a.in_stride, a.q_out, a.q_stride, a.k_out, a.k_stride = buf.data_ptr(), Q + 2 * KV, q_out.data_ptr(), Q, None, 0
+        a.q_w, a.k_w, a.rope = keep[0].data_ptr(), keep[1].data_ptr(), K.RotaryArgs(inv.data_ptr(), hd, 0.0, 1.0)
+        a.eps, a.nh, a.nkv, a.hd = 1e-5, nh, nkv, hd
+        a.pos_of, a.seq_of, a.slot_of_seq, a.kv_len = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr(), lay.kv_len.data_ptr()
+        a.cache, a.append, a.T, a.zero_in = cache.view, 1, T, 1
+        if folded:
+            a.row_sumsq, a.row_width, a.row_eps = keep[2].data_ptr(), width, eps
+        K.qk_norm_rope(a, torch.float32, torch.bfloat16, stream())
+        assert float(buf.abs().sum()) == 0                                          # the sums are left cleared
+        kv = [torch.cat(cache.get(s, n - 1)) for s, n in zip(slots, lens)]
+        outs.append((q_out.float().cpu(), torch.stack(kv)))
+    assert rel_l2(outs[0][0], outs[1][0]) < 4e-3 and rel_l2(outs[0][1], outs[1][1]) < 4e-3
+    v_want = (rows[:, Q + KV:] * scale[:, None]).view(T, nkv, hd)
+    assert rel_l2(outs[0][1][:, nkv:], v_want) < 4e-3                               # V rows: scaled, else untouched
+
+
 def reference_attention(q, keys, vals, qpos, window, scale):
     """q [nh, hd] at position qpos; keys/vals [len, nkv, hd]; float64."""
     nh, nkv = q.shape[0], keys.shape[1]

@@ -44,6 +44,21 @@ __global__ void scale_f32_kernel(float* __restrict__ x, long long n, float facto
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] *= factor;
 }
 
+__global__ void fill_f32_kernel(float* __restrict__ x, long long n, float value) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] = value;
+}
+
+// x[i] = value: small float32 buffers that a step wants cleared at its start (sums that its kernels add into).
+extern "C" int tb_fill_f32(float* x, long long n, float value, cudaStream_t stream) {
+    TB_REQUIRE(x && n > 0, "fill_f32: nothing to fill");
+    const long long blocks = (n + 255) / 256;
+    tb_launch(fill_f32_kernel, (int)(blocks < 1024 ? blocks : 1024), 256, 0, stream, x, n, value);
+    TB_CHECK_LAUNCH("fill_f32");
+    return 0;
+}
+
 extern "C" int tb_scale_f32(float* x, long long n, float factor, cudaStream_t stream) {
     TB_REQUIRE(x && n > 0, "scale_f32: nothing to scale");
     const int threads = 256;
@@ -165,12 +180,13 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
     const int col = is_q ? head * hd : (is_k ? a.nh * hd + (head - a.nh) * hd
                                              : (a.nh + a.nkv) * hd + (head - a.nh - a.nkv) * hd);
     const TIn* x = (const TIn*)a.in + (size_t)t * a.in_stride + col;
+    const float row_scale = a.row_sumsq ? 1.0f / sqrtf(a.row_sumsq[t] / (float)a.row_width + a.row_eps) : 1.f;
     float v[QK_MAXE];
     float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < QK_MAXE; ++j) {
         const int e = lane + 32 * j;
-        v[j] = e < hd ? ldf(x + e) : 0.f;
+        v[j] = e < hd ? ldf(x + e) * row_scale : 0.f;
         ss += v[j] * v[j];
         if (a.zero_in && e < hd) const_cast<TIn*>(x)[e] = TIn(0.f);
     }
@@ -284,6 +300,7 @@ __global__ void qk_norm_rope_vec_kernel(QkArgs a) {
     extern __shared__ __align__(16) float head_smem[];
     constexpr int HALF = HD / 2;
     __shared__ long long row_off[TOK];              // element offset of the token's cache row for kv head 0; < 0: not written
+    __shared__ float row_scale[TOK];                // what the token's input row is multiplied by first (a folded norm's scale)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int t0 = blockIdx.x * TOK;
     const int n_tok = a.T - t0 < TOK ? a.T - t0 : TOK;
@@ -295,6 +312,7 @@ __global__ void qk_norm_rope_vec_kernel(QkArgs a) {
         const int pos = a.pos_of[t], seq = a.seq_of[t];
         const bool to_cache = a.append && !(a.cache.ring_rows && a.kv_len && pos < a.kv_len[seq] - a.cache.ring_rows);
         row_off[threadIdx.x] = to_cache ? (long long)kv_row_offset(a.cache, a.slot_of_seq[seq], pos, 0) : -1;
+        row_scale[threadIdx.x] = a.row_sumsq ? 1.0f / sqrtf(a.row_sumsq[t] / (float)a.row_width + a.row_eps) : 1.f;
     }
     if (a.rope.inv_freq) {
         for (int i = threadIdx.x; i < n_tok * HALF; i += blockDim.x) {
@@ -352,9 +370,13 @@ __global__ void qk_norm_rope_vec_kernel(QkArgs a) {
                 store_vec<TIn, HV>(src, z);
                 store_vec<TIn, HV>(src + HALF, z);
             }
+            const float rs = row_scale[j < n_tok ? j : 0];
             float ss = 0.f;
 #pragma unroll
-            for (int i = 0; i < HV; ++i) ss += lo[j][i] * lo[j][i] + hi[j][i] * hi[j][i];
+            for (int i = 0; i < HV; ++i) {
+                lo[j][i] *= rs; hi[j][i] *= rs;
+                ss += lo[j][i] * lo[j][i] + hi[j][i] * hi[j][i];
+            }
 #pragma unroll
             for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             const float scale = w ? 1.0f / sqrtf(ss / (float)HD + a.eps) : 1.f;
@@ -411,6 +433,7 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     TB_REQUIRE(a.rope.rot >= 0 && a.rope.rot <= a.hd && a.rope.rot % 2 == 0, "qk_norm_rope: rotary_dim %d must be even and <= head_dim %d", a.rope.rot, a.hd);
     TB_REQUIRE(!a.zero_in || (a.append && a.in != a.q_out && a.k_out == nullptr),
                "qk_norm_rope: zeroing the input needs every head to be read (append) and outputs elsewhere");
+    TB_REQUIRE(!a.row_sumsq || a.row_width > 0, "qk_norm_rope: row sums of squares need the rows' width");
     TB_REQUIRE(!a.append || (a.cache.storage && a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv),
                "qk_norm_rope: the cache view does not match the heads");
     const int warps = 4;

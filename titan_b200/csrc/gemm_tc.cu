@@ -48,9 +48,6 @@ constexpr int BM = 128;          // rows of A per tile = M of the instruction
 constexpr int BK = 64;           // bf16 elements per stage row = 128 bytes = one swizzle span
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-#ifndef TB_SWAP16_STAGES
-#define TB_SWAP16_STAGES 6
-#endif
 
 __device__ unsigned int g_tc_error = 0;
 
@@ -97,11 +94,16 @@ struct TcArgs {
     int tiles_m;     // persistent kernel: tiles along A's rows and along B's rows
     int tiles_n;
     int tail_split;  // persistent kernel, ADD epilogue: K parts of the tiles of the last, partly filled round (1: whole)
+    // swap mode with the RMS norm of the input folded in (NORMED): the activations are float32 rows xf [rows_b][ldxf]
+    // and the norm's weight norm_w [K]; the kernel multiplies by the weight on the way into shared memory and by
+    // 1/sqrt(mean(x^2) + eps) in its epilogue, or (K cut into slices: no CTA sees a whole row) adds its rows'
+    // partial sums of squares into sumsq_out [rows_b] for the consumer of the sums to apply
+    const float* xf; int ldxf; const float* norm_w; float* sumsq_out; float norm_eps;
 };
 
 // TMA ring depth.  Decode tiles (BN <= 64) take as many stages as still let two CTAs share an SM: the
 // ring is filled before the wait on the previous kernel, so its depth is what bridges kernel boundaries.
-template <int BN> constexpr int stages_for() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 4 : (BN >= 32 ? 5 : TB_SWAP16_STAGES))); }
+template <int BN> constexpr int stages_for() { return BN >= 256 ? 4 : (BN >= 128 ? 5 : (BN >= 64 ? 4 : (BN >= 32 ? 5 : 6))); }
 // Swap mode with 65..128 rows of activations: three stages, so that two CTAs share an SM here too and the
 // 192 tiles of the gate-and-up product are resident at once (measured at 96 rows: 59.8 -> 44.0 us).  The
 // bfloat16 store (a short prompt's Q|K|V: 48 tiles, no K slices) keeps the deeper ring of one CTA per SM.
@@ -111,7 +113,7 @@ template <int BN, int EPI, bool SWAP> constexpr int stages_of() {
 template <int BN> constexpr int tmem_cols_for() { return BN < 32 ? 32 : BN; }
 constexpr int EPI_TILE_FLOATS = 32 * 33;      // one warp's 32 x 32 transposition tile, padded against bank conflicts
 template <int BN, bool SWAP, int STAGES = stages_for<BN>()> constexpr size_t smem_for() {
-    return 1024 /*alignment slack*/ + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + 256 +
+    return 1024 /*alignment slack*/ + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (SWAP ? 1024 : 256) /*barriers; sums of the folded norm*/ +
            (SWAP ? 0 : 4 * EPI_TILE_FLOATS * sizeof(float));
 }
 
@@ -249,9 +251,10 @@ __device__ __forceinline__ void epilogue_rows(const float* val, float* tile, con
     }
 }
 
-template <int BN, int EPI, bool SWAP>
+template <int BN, int EPI, bool SWAP, bool NORMED = false>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs a) {
+    static_assert(!NORMED || (SWAP && BN <= 32), "the folded norm is for decode tiles (swap mode, at most 32 rows of activations)");
     constexpr int STAGES = stages_of<BN, EPI, SWAP>();
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     constexpr uint32_t TMEM_COLS = tmem_cols_for<BN>();
@@ -263,6 +266,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* empty = full + STAGES;
     uint64_t* accum = empty + STAGES;
     uint32_t* tmem_slot = (uint32_t*)(accum + 1);
+    float* norm_sh = (float*)(tmem_slot + 2);               // NORMED: [4 warps][BN] sums of squares, then [BN] scales
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile_a = blockIdx.y;                          // tile index along A's rows
@@ -274,15 +278,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+        // NORMED: a stage is full when the weights have landed (TMA) and a warp has written the activations
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, NORMED ? 2 : 1); mbar_init(empty + s, 1); }
         mbar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (NORMED) {       // rows of the activation tiles that no token fills stay zero (TMA would have filled them so)
+        for (int i = threadIdx.x; i < (int)(STAGES * B_BYTES / 16); i += THREADS) reinterpret_cast<uint4*>(smem_b)[i] = make_uint4(0, 0, 0, 0);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    constexpr uint32_t TX_BYTES = NORMED ? A_BYTES : A_BYTES + B_BYTES;
 
     if (n_kb > 0) {
         if (warp == 0) {
@@ -292,22 +302,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int pre = n_kb < STAGES ? n_kb : STAGES;
                 const uint64_t once = tbtma::l2_evict_first_policy();     // swap mode: every weight is read once
                 for (int i = 0; i < pre; ++i) {
-                    mbar_expect_tx(full + i, A_BYTES + B_BYTES);
+                    mbar_expect_tx(full + i, TX_BYTES);
                     if (SWAP) tma_load_2d_hint(smem_a + i * A_BYTES, &map_a, full + i, (kb0 + i) * BK, tile_a * BM, once);
                     else tma_load_2d(smem_b + i * B_BYTES, &map_b, full + i, (kb0 + i) * BK, tile_b * BN);
                 }
                 pdl_wait();
                 for (int i = 0; i < pre; ++i) {
+                    if (NORMED) continue;
                     if (SWAP) tma_load_2d(smem_b + i * B_BYTES, &map_b, full + i, (kb0 + i) * BK, tile_b * BN);
                     else tma_load_2d(smem_a + i * A_BYTES, &map_a, full + i, (kb0 + i) * BK, tile_a * BM);
                 }
                 for (int i = pre; i < n_kb; ++i) {
                     const int s = i % STAGES, round = i / STAGES;
                     mbar_wait(empty + s, (round - 1) & 1, 1);
-                    mbar_expect_tx(full + s, A_BYTES + B_BYTES);
+                    mbar_expect_tx(full + s, TX_BYTES);
                     if (SWAP) tma_load_2d_hint(smem_a + s * A_BYTES, &map_a, full + s, (kb0 + i) * BK, tile_a * BM, once);
                     else tma_load_2d(smem_a + s * A_BYTES, &map_a, full + s, (kb0 + i) * BK, tile_a * BM);
-                    tma_load_2d(smem_b + s * B_BYTES, &map_b, full + s, (kb0 + i) * BK, tile_b * BN);
+                    if (!NORMED) tma_load_2d(smem_b + s * B_BYTES, &map_b, full + s, (kb0 + i) * BK, tile_b * BN);
                 }
             }
         } else if (warp == 1) {
@@ -329,6 +340,70 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         } else {
             pdl_wait();
+            if (NORMED) {
+                // The four epilogue warps make the activation tiles meanwhile, a stage each in turn (four stages in
+                // flight): float32 rows of the residual stream times the norm's weight, rounded to bfloat16, into the
+                // K-major 128-byte-swizzled layout that TMA would have written; and the rows' sums of squares.
+                const int w4 = warp - 2;
+                constexpr int UNITS = BN * 8 / 32;            // (row, 16-byte chunk) units per lane
+                float ss[UNITS];
+#pragma unroll
+                for (int u = 0; u < UNITS; ++u) ss[u] = 0.f;
+                for (int i = w4; i < n_kb; i += 4) {
+                    const int s = i % STAGES, round = i / STAGES;
+                    float xv[UNITS][8], wv[8];
+                    const int chunk = lane & 7, k0 = (kb0 + i) * BK + chunk * 8;
+                    const bool k_ok = k0 < a.K;               // K is a multiple of 8: a chunk is inside or outside
+                    if (k_ok) {
+                        const float4 w0 = *reinterpret_cast<const float4*>(a.norm_w + k0), w1 = *reinterpret_cast<const float4*>(a.norm_w + k0 + 4);
+                        wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+                    }
+#pragma unroll
+                    for (int u = 0; u < UNITS; ++u) {         // all loads first
+                        const int row = (lane >> 3) + 4 * u;
+                        if (k_ok && row < a.rows_b) {
+                            const float* xp = a.xf + (size_t)row * a.ldxf + k0;
+                            const float4 x0 = *reinterpret_cast<const float4*>(xp), x1 = *reinterpret_cast<const float4*>(xp + 4);
+                            xv[u][0] = x0.x; xv[u][1] = x0.y; xv[u][2] = x0.z; xv[u][3] = x0.w; xv[u][4] = x1.x; xv[u][5] = x1.y; xv[u][6] = x1.z; xv[u][7] = x1.w;
+                        }
+                    }
+                    if (round > 0) mbar_wait(empty + s, (round - 1) & 1, 5);
+#pragma unroll
+                    for (int u = 0; u < UNITS; ++u) {
+                        const int row = (lane >> 3) + 4 * u;
+                        if (row >= a.rows_b) continue;
+                        uint4 pk = make_uint4(0, 0, 0, 0);
+                        if (k_ok) {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) ss[u] = fmaf(xv[u][e], xv[u][e], ss[u]);
+                            pk.x = pack_bf16(xv[u][0] * wv[0], xv[u][1] * wv[1]); pk.y = pack_bf16(xv[u][2] * wv[2], xv[u][3] * wv[3]);
+                            pk.z = pack_bf16(xv[u][4] * wv[4], xv[u][5] * wv[5]); pk.w = pack_bf16(xv[u][6] * wv[6], xv[u][7] * wv[7]);
+                        }
+                        *reinterpret_cast<uint4*>(smem_b + s * B_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4)) = pk;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the tensor core reads these writes
+                    __syncwarp();
+                    if (lane == 0) tbtma::mbar_arrive(full + s);
+                }
+                // a row's sum: over the eight lanes that share it, then over the four warps
+#pragma unroll
+                for (int u = 0; u < UNITS; ++u) {
+                    float v = ss[u];
+                    v += __shfl_xor_sync(0xffffffffu, v, 1); v += __shfl_xor_sync(0xffffffffu, v, 2); v += __shfl_xor_sync(0xffffffffu, v, 4);
+                    if ((lane & 7) == 0) norm_sh[w4 * BN + (lane >> 3) + 4 * u] = v;
+                }
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (warp == 2 && lane < BN) {
+                    const float total = norm_sh[lane] + norm_sh[BN + lane] + norm_sh[2 * BN + lane] + norm_sh[3 * BN + lane];
+                    if (a.sumsq_out) {                        // K slices: the consumer of the sums scales
+                        if (tile_a == 0 && lane < a.rows_b) atomicAdd(a.sumsq_out + lane, total);
+                        norm_sh[4 * BN + lane] = 1.f;
+                    } else {
+                        norm_sh[4 * BN + lane] = 1.0f / sqrtf(total / (float)a.K + a.norm_eps);
+                    }
+                }
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+            }
             mbar_wait(accum, 0, 3);
             tc_fence_after();
             const int quarter = warp & 3;                     // a warp reads TMEM lanes 32 * (warp % 4) ..
@@ -339,11 +414,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int c = 0; c < BN; c += 32) {
                     float v[32];
                     tmem_ld32(taddr + c, v);
+                    if (NORMED) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] *= norm_sh[4 * BN + c + j];
+                    }
                     epilogue_chunk<EPI, SWAP, 32>(v, a, row, tile_b * BN + c, lane);
                 }
             } else {
                 float v[16];
                 tmem_ld16(taddr, v);
+                if (NORMED) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] *= norm_sh[4 * BN + j];
+                }
                 epilogue_chunk<EPI, SWAP, 16>(v, a, row, tile_b * BN, lane);
             }
         }
@@ -686,6 +769,20 @@ int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim
 }
 
 template <int BN, int EPI>
+int launch_tc_normed(const CUtensorMap& ma, const TcArgs& a, dim3 grid, cudaStream_t stream) {
+    static bool configured = false;
+    constexpr size_t smem = smem_for<BN, true, stages_of<BN, EPI, true>()>();
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI, true, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        TB_REQUIRE(e == cudaSuccess, "gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    tb_launch(gemm_tc_kernel<BN, EPI, true, true>, grid, THREADS, smem, stream, ma, ma, a);
+    return 0;
+}
+
+template <int BN, int EPI>
 int launch_persistent_epi(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t stream) {
     static bool configured = false;
     constexpr size_t smem = smem_for<BN, false>();
@@ -807,6 +904,59 @@ extern "C" int tb_gemm_tc_check(int M, int N, int K, int ldx, int ldo, int epi, 
     return 0;
 }
 
+// 0 if tb_gemm_tc_normed takes this product: a decode step's rows (at most 32), the SwiGLU epilogue or float32 sums.
+extern "C" int tb_gemm_tc_normed_check(int M, int N, int K, int ldxf, int ldo, int epi, const void* xf, const void* norm_w,
+                                       const void* W, const void* out, const void* sumsq_out) {
+    TB_REQUIRE(M > 0 && M <= 32 && M < g_swap_below, "gemm_tc_normed: %d rows (a decode step's: at most 32)", M);
+    TB_REQUIRE(epi == TB_EPI_ADD || epi == TB_EPI_SWIGLU, "gemm_tc_normed: the epilogue must be ADD (sums for a consumer that scales) or SWIGLU");
+    TB_REQUIRE((epi == TB_EPI_ADD) == (sumsq_out != nullptr), "gemm_tc_normed: sums of squares go out with the ADD epilogue and only with it");
+    TB_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && ldxf % 4 == 0, "gemm_tc_normed: K=%d must be a multiple of 8 and the row stride %d of x a multiple of 4", K, ldxf);
+    TB_REQUIRE(((uintptr_t)xf & 15) == 0 && ((uintptr_t)norm_w & 15) == 0 && ((uintptr_t)W & 15) == 0 && ((uintptr_t)out & 15) == 0,
+               "gemm_tc_normed: operands must be 16-byte aligned");
+    TB_REQUIRE(epi != TB_EPI_SWIGLU || N % 2 == 0, "gemm_tc_normed: the SwiGLU epilogue needs an even N");
+    TB_REQUIRE(ldo % (epi == TB_EPI_SWIGLU ? 8 : 4) == 0, "gemm_tc_normed: the row stride %d of the output", ldo);
+    return 0;
+}
+
+// out (epilogue) = rmsnorm(xf; norm_w, eps)[M,K] . W[N,K]^T for a decode step's rows, the norm folded into the product:
+// the kernel reads the float32 rows, multiplies by the norm's weight on the way into shared memory and by
+// 1/sqrt(mean(x^2) + eps) in its epilogue (SWIGLU), or (ADD: K is cut into slices) adds the products of the
+// unscaled rows into ``out`` and the rows' sums of squares into ``sumsq_out`` [M], for the consumer to scale.
+extern "C" int tb_gemm_tc_normed(const float* xf, int ldxf, const float* norm_w, float eps, const void* W, void* out,
+                                 int M, int N, int K, int ldo, int epi, float* sumsq_out, cudaStream_t stream) {
+    if (tb_gemm_tc_normed_check(M, N, K, ldxf, ldo, epi, xf, norm_w, W, out, sumsq_out)) return 1;
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
+    }
+    const int kb = (K + BK - 1) / BK;
+    const int tiles = (N + BM - 1) / BM;
+    TB_REQUIRE(tiles <= 65535, "gemm_tc_normed: N=%d is too large for one launch", N);
+    int s = 1;
+    if (epi == TB_EPI_ADD) {                                  // as many K slices as fill the machine once, four blocks each at least
+        s = 2 * sm_count / tiles;
+        const int max_s = kb / 4 > 0 ? kb / 4 : 1;
+        s = s < 1 ? 1 : (s > max_s ? max_s : s);
+    }
+    TcArgs a;
+    a.out = out; a.rows_a = N; a.rows_b = M; a.K = K; a.ldo = ldo; a.tiles_m = a.tiles_n = 0; a.tail_split = 1;
+    a.k_blocks_per_split = (kb + s - 1) / s;
+    s = (kb + a.k_blocks_per_split - 1) / a.k_blocks_per_split;
+    a.atomic = s > 1;
+    a.xf = xf; a.ldxf = ldxf; a.norm_w = norm_w; a.sumsq_out = sumsq_out; a.norm_eps = eps;
+    CUtensorMap ma;
+    if (tb_make_map_bf16(&ma, W, N, K, K, BM)) return 1;
+    dim3 grid(1, tiles, s);
+    int rc;
+    if (M <= 16) rc = epi == TB_EPI_ADD ? launch_tc_normed<16, TB_EPI_ADD>(ma, a, grid, stream) : launch_tc_normed<16, TB_EPI_SWIGLU>(ma, a, grid, stream);
+    else rc = epi == TB_EPI_ADD ? launch_tc_normed<32, TB_EPI_ADD>(ma, a, grid, stream) : launch_tc_normed<32, TB_EPI_SWIGLU>(ma, a, grid, stream);
+    if (rc) return rc;
+    TB_CHECK_LAUNCH("gemm_tc_normed");
+    return 0;
+}
+
 // splits: K slices (swap mode, ADD epilogue only); 0 = choose.
 extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N, int K, int ldx, int ldo, int epi,
                           int splits, cudaStream_t stream) {
@@ -816,6 +966,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
     CUtensorMap ma, mb;
     TcArgs a;
     a.out = out; a.K = K; a.ldo = ldo; a.k_blocks_per_split = kb; a.atomic = 0; a.tiles_m = a.tiles_n = 0; a.tail_split = 1;
+    a.xf = nullptr; a.ldxf = 0; a.norm_w = nullptr; a.sumsq_out = nullptr; a.norm_eps = 0.f;
     int rc = 0;
     static int sm_count = 0;
     if (!sm_count) {

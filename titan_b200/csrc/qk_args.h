@@ -24,4 +24,7 @@ struct QkArgs {
     TbKvView cache; int append; int T;
     int zero_in;                            // after reading a head, write zeros over it (an accumulation buffer is left clean)
     const int* kv_len;                      // [B] lengths after the step: in a ring, a row that a later token of the step reuses is not written
+    // The input rows are products of UNSCALED activations (the RMS norm before the projection was folded into the
+    // product): row t is first multiplied by 1/sqrt(row_sumsq[t] / row_width + row_eps).  Null: the rows are as they should be.
+    const float* row_sumsq; int row_width; float row_eps;
 };

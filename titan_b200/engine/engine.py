@@ -49,6 +49,7 @@ class EngineOptions:
     attention: str = "fast"           # "plain": the any-size attention kernels even where a tensor-core one fits
     attn_chunk: int = 256             # keys per split of decode attention
     mark_freed_pages: bool = False    # debugging: pages of a freed slot are overwritten with a large finite value, so a stale read shows
+    fold_norms: bool = True           # decode steps: a norm goes into the product that consumes it where the kernels can take it
     early_pages: bool = True          # decode attention requests pages of older positions before it waits for the kernels before it
     decode_graphs: bool = True        # replay single-token steps as CUDA graphs once a batch size has run eagerly
     device: str = "cuda:0"
@@ -78,7 +79,7 @@ class Engine:
         self.sampler = DeviceSampler(self.cache.state, max_slots, self.spec.vocab_size, self.device)
         self.scratch: Dict[str, torch.Tensor] = {}
         self.step_options = {"gemm": options.gemm, "attention": options.attention, "attn_chunk": options.attn_chunk,
-                             "early_pages": options.early_pages,
+                             "early_pages": options.early_pages, "fold_norms": options.fold_norms,
                              "max_context": self.cache.max_context,
                              "sm_count": torch.cuda.get_device_properties(self.device).multi_processor_count}
         self.h2d_bytes = 0

@@ -33,6 +33,7 @@ from ..cache.groups import CacheNeed, KVGroup
 from ..weights.loader import WeightSpec
 from . import linear
 from .base import MIXERS, POSITIONS, Mixer
+from .norm import DeferredNorm, rows_of
 
 
 def decode_split(lay, kv_heads: int, options, fast: bool):
@@ -59,6 +60,8 @@ def decode_split(lay, kv_heads: int, options, fast: bool):
 
 
 class AttentionMixer(Mixer):
+    folds_norm = True           # a decode step's Q|K|V product takes the norm before it in
+
     def __init__(self, spec):
         s = spec
         if s.num_heads <= 0 or s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
@@ -150,7 +153,7 @@ class AttentionMixer(Mixer):
         qa.kv_len = lay.kv_len.data_ptr()
         return qa
 
-    def forward(self, h: torch.Tensor, ctx, cache, out: torch.Tensor) -> None:
+    def forward(self, h, ctx, cache, out: torch.Tensor) -> None:
         s, lay = self.spec, ctx.layout
         T, Q, KV, hd = lay.T, self.Q, self.KV, s.head_dim
         width = Q if self.shared else Q + 2 * KV
@@ -160,16 +163,27 @@ class AttentionMixer(Mixer):
         # A decode step in bfloat16 sums Q | K | V in float32 (K slices of the product add into a zeroed
         # buffer), and the norm/rotary kernel rounds once, into the query buffer and the cache.
         wide_sum = decode and not self.shared and h.dtype == torch.bfloat16 and ctx.options.get("gemm", "fast") != "plain"
+        row_sums = None
         if wide_sum:
             key = f"acc_qkv_{T}x{width}"            # zeroed once; the norm/rotary kernel leaves it zeroed again (Engine.reset_accumulators after a failed step)
             qkv = ctx.scratch.get(key)
             if qkv is None:
                 qkv = ctx.scratch[key] = torch.zeros((T, width), dtype=torch.float32, device=ctx.device)
-            linear.matmul(h, self.w_qkv, qkv, linear.EPI_ADD, ctx)
+            # The norm before the projection, if it was handed over unevaluated, goes into the product: the kernel
+            # adds the products of the unscaled rows into the sums and the rows' sums of squares into a place of
+            # this step's own, and the head norm/rotary kernel scales the rows first.
+            if isinstance(h, DeferredNorm):
+                row_sums = ctx.row_sums(T)
+                if row_sums is not None and K.gemm_tc_normed_accepts(h.x, h.weight, self.w_qkv, qkv, linear.EPI_ADD, row_sums):
+                    K.gemm_tc_normed(h.x, h.weight, h.eps, self.w_qkv, qkv, linear.EPI_ADD, ctx.stream, sumsq=row_sums)
+                else:
+                    row_sums = None
+            if row_sums is None:
+                linear.matmul(rows_of(h), self.w_qkv, qkv, linear.EPI_ADD, ctx)
             q_buf, q_stride = ctx.empty((T, Q)), Q
         else:
             qkv = ctx.empty((T, width))
-            linear.matmul(h, self.w_qkv, qkv, linear.EPI_STORE, ctx)
+            linear.matmul(rows_of(h), self.w_qkv, qkv, linear.EPI_STORE, ctx)
             q_buf, q_stride = qkv, width
         # K and V go into the cache in this kernel when nothing of this step still has to read the rows
         # they replace: always for single tokens and for caches that keep everything; in a ring only if
@@ -178,6 +192,8 @@ class AttentionMixer(Mixer):
         qa = self._qk_args(qkv, width, q_buf, q_stride, view, lay, rope, T, hd, append=append_now, zero_in=wide_sum)
         if not (self.shared or wide_sum):
             qa.k_out, qa.k_stride = qkv.data_ptr() + Q * qkv.element_size(), width
+        if row_sums is not None:
+            qa.row_sumsq, qa.row_width, qa.row_eps = row_sums.data_ptr(), s.hidden_size, h.eps
         K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
 
         attn = ctx.empty((T, Q))

@@ -1,6 +1,7 @@
 """Arrangements of a block's parts around the residual stream.
 
-``pre_norm``:  x += mixer(norm1(x));  x += feed_forward(norm2(x))
+``pre_norm``:  x += mixer(norm1(x));  x += feed_forward(norm2(x)); a norm whose consumer can fold it into
+its first matrix product is handed over unevaluated (``norm.DeferredNorm``)
 (berniehans/titan: engine/engine-core/src/forward_cpu.rs:281-386).  The
 residual stream ``x`` is float32 and is updated in place: mixer and
 feed-forward add into it in the epilogue of their last matrix product.
@@ -38,9 +39,17 @@ class PreNormBlock(Part):
         for part in self.parts():
             part.bind(lambda name: get(self.spec.prefix + name))
 
+    @staticmethod
+    def _normed(norm, consumer, x, ctx):
+        """The norm's rows for the part that consumes them; not yet computed (a DeferredNorm) if the norm can be
+        deferred and the part can fold it into its first product."""
+        if getattr(consumer, "folds_norm", False) and hasattr(norm, "deferred") and ctx.options.get("fold_norms", True):
+            return norm.deferred(x, ctx)
+        return norm.forward(x, ctx)
+
     def forward(self, x: torch.Tensor, ctx, cache) -> None:
-        self.mixer.forward(self.mixer_norm.forward(x, ctx), ctx, cache, x)
-        self.feed_forward.forward(self.feed_forward_norm.forward(x, ctx), ctx, x)
+        self.mixer.forward(self._normed(self.mixer_norm, self.mixer, x, ctx), ctx, cache, x)
+        self.feed_forward.forward(self._normed(self.feed_forward_norm, self.feed_forward, x, ctx), ctx, x)
 
 
 BLOCKS.register("pre_norm", PreNormBlock)

@@ -17,11 +17,15 @@ from typing import List
 import torch
 
 from ..weights.loader import WeightSpec
+from .. import kernels as K
 from . import linear
 from .base import FEED_FORWARDS, FeedForward
+from .norm import DeferredNorm, rows_of
 
 
 class GatedMLP(FeedForward):
+    folds_norm = True           # a decode step's gate-and-up product takes the norm before it in
+
     def __init__(self, spec):
         if spec.activation != "silu":
             raise ValueError(f"activation '{spec.activation}' is not supported (only 'silu')")
@@ -56,9 +60,13 @@ class GatedMLP(FeedForward):
         del gate, up
         self.w_down = get(p + n["down"])
 
-    def forward(self, h: torch.Tensor, ctx, out: torch.Tensor) -> None:
+    def forward(self, h, ctx, out: torch.Tensor) -> None:
         act = ctx.empty((h.shape[0], self.spec.intermediate_size))
-        linear.matmul(h, self.w_gate_up, act, linear.EPI_SWIGLU, ctx)
+        if (isinstance(h, DeferredNorm) and ctx.options.get("gemm", "fast") != "plain" and self.w_gate_up.dtype == torch.bfloat16
+                and K.gemm_tc_normed_accepts(h.x, h.weight, self.w_gate_up, act, linear.EPI_SWIGLU, None)):
+            K.gemm_tc_normed(h.x, h.weight, h.eps, self.w_gate_up, act, linear.EPI_SWIGLU, ctx.stream)
+        else:
+            linear.matmul(rows_of(h), self.w_gate_up, act, linear.EPI_SWIGLU, ctx)
         linear.matmul(act, self.w_down, out, linear.EPI_ADD, ctx)
 
 
