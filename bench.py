@@ -349,10 +349,11 @@ def run_other(args, which):
     return 0
 
 
-def profile_case():
-    """The small case that the ncu summaries under profiles/ were captured on: ONE layer of the
-    benchmark's sizes; two 2,048-token prompts, then decode steps at batch 8 with 8,100 cached tokens
-    per sequence, CUDA graphs off so that every kernel is a launch of its own.  About 4 GB on the device."""
+def profile_case(kv=2048):
+    """The small case that the ncu summaries under profiles/ are captured on: ONE layer of the benchmark's sizes;
+    two 2,048-token prompts in one step each, one in four chunks of 512 (continuation steps), then two decode
+    steps at batch 8 and two at batch 1 after prompts of ``kv`` tokens, CUDA graphs off so that every kernel is
+    a launch of its own.  A few GB on the device."""
     import torch
 
     from titan_b200 import Engine, SamplerParams, StepEntry
@@ -360,19 +361,28 @@ def profile_case():
     cfg = dict(QWEN3_8B)
     cfg["num_hidden_layers"] = 1
     batch = 8
-    engine = Engine.from_random(config_from_dict(cfg), 2, "bfloat16", max_tokens=batch * 8192 + 4096, max_context=8192,
-                                max_slots=batch + 1, decode_graphs=False)
+    engine = Engine.from_random(config_from_dict(cfg), 2, "bfloat16", max_tokens=(batch + 1) * (kv + 128) + 4096, max_context=8192,
+                                max_slots=batch + 2, decode_graphs=False)
+    prompt = [(13 * i + 5) % 151936 for i in range(2048)]
     for _ in range(2):
         s = engine.alloc_slot()
-        engine.step([StepEntry(s, [(13 * i + 5) % 151936 for i in range(2048)], [2047])])
+        engine.step([StepEntry(s, prompt, [2047])])
         engine.free_slot(s)
-    slots = [engine.alloc_slot() for _ in range(batch)]
-    fill_cache_random(engine, slots, 8100)
-    engine.sampler.configure(slots, [SamplerParams.greedy()] * batch, list(range(batch)))
-    tokens = [1] * batch
-    for _ in range(2):
-        tokens = engine.advance(slots, tokens)
+    s = engine.alloc_slot()
+    for at in range(0, 2048, 512):
+        engine.step([StepEntry(s, prompt[at:at + 512], [])])
+    engine.free_slot(s)
+    for b in (batch, 1):
+        slots = [engine.alloc_slot() for _ in range(b)]
+        engine.sampler.configure(slots, [SamplerParams.greedy()] * b, list(range(b)))
+        run_prompts(engine, slots, kv)
+        tokens = [1] * b
+        for _ in range(2):
+            tokens = engine.advance(slots, tokens)
+        for s in slots:
+            engine.free_slot(s)
     torch.cuda.synchronize()
+    engine.check_kernels()
     print("profile case done", tokens)
     return 0
 
@@ -488,7 +498,7 @@ def main():
     ap.add_argument("--micro", action="store_true", help="time the layer's kernels alone (CUDA events) and exit; text lines, not the JSON line")
     args = ap.parse_args()
     if args.profile_case:
-        return profile_case()
+        return profile_case(args.prompt_tokens)
     if args.micro:
         return micro()
     if args.impl == "reference":

@@ -133,3 +133,14 @@ def test_folded_norms_change_results_by_rounding_only(models, B):
         for i in range(B):
             rows_close(got[i], want[i], "bfloat16", f"batch {B}, fold_norms={fold}, request {i}")
     assert launches[True] < launches[False]
+    # what one eager decode step of this model launches, by launcher
+    from titan_b200 import SamplerParams
+    slots, first = e.start([r[:5] for r in reqs[:2]], [SamplerParams.greedy()] * 2, [0, 1])
+    K.launch_log_start()
+    e.advance(slots, first)                    # batch size 2 has not run before: an eager step
+    log = K.launch_log_stop()
+    for s_ in slots:
+        e.finish(s_)
+    layers = cfg["num_hidden_layers"]
+    assert log["rmsnorm"] == 2 * layers + 1 and log["qk_norm_rope"] == layers and log["attn_decode_mma"] == layers
+    assert log["gemm_tc"] == 4 * layers + 1 and log["embed"] == 1 and "gemm_tc_normed" not in log       # this engine does not fold

@@ -422,8 +422,8 @@ static void launch_qk_vec_tok(const QkArgs& a, int warps, int head_groups, cudaS
 template <typename TIn, typename TOut>
 static void launch_qk_vec(const QkArgs& a, dim3 grid, int threads, cudaStream_t stream) {
     (void)threads;
-    if (a.T >= 64) launch_qk_vec_tok<TIn, TOut, 4>(a, 4, 2, stream);          // prompts: half of the heads of four tokens per block
-    else launch_qk_vec_tok<TIn, TOut, 1>(a, 4, (grid.y + 1) / 2, stream);    // decode steps: eight heads of one token per block
+    if (a.T >= 512) launch_qk_vec_tok<TIn, TOut, 4>(a, 4, 2, stream);         // prompts: half of the heads of four tokens per block
+    else launch_qk_vec_tok<TIn, TOut, 1>(a, 4, (grid.y + 1) / 2, stream);    // decode steps and short prompts: eight heads of one token per block (T x heads / 8 blocks)
 }
 
 extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, cudaStream_t stream) {

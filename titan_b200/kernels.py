@@ -8,6 +8,7 @@ library: if the extension cannot be built or loaded, the first call raises.
 from __future__ import annotations
 
 import ctypes
+import sys
 from ctypes import POINTER, Structure, byref, c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -19,6 +20,20 @@ EPI_STORE, EPI_F32, EPI_ADD, EPI_SWIGLU = 0, 1, 2, 3
 F32, BF16 = 0, 1
 
 launch_count = 0          # launcher calls since import (a launcher starts one or two kernels)
+_launch_log = None        # while a log is open: launcher name -> calls (berniehans/titan keeps such a record per launch, engine-cuda/src/dispatch_telemetry.rs:13-143)
+
+
+def launch_log_start() -> None:
+    """Begin counting launcher calls by name (what a step launched, and how often)."""
+    global _launch_log
+    _launch_log = {}
+
+
+def launch_log_stop() -> dict:
+    """End the count; {launcher name: calls}, in the order of first use."""
+    global _launch_log
+    log, _launch_log = _launch_log or {}, None
+    return log
 
 
 class KernelError(RuntimeError):
@@ -122,6 +137,9 @@ def tlib():
 def _check(rc: int) -> None:
     global launch_count
     launch_count += 1
+    if _launch_log is not None:
+        name = sys._getframe(1).f_code.co_name
+        _launch_log[name] = _launch_log.get(name, 0) + 1
     if rc:
         raise KernelError(lib().tb_last_error().decode())
 

@@ -44,19 +44,22 @@ def decode_split(lay, kv_heads: int, options, fast: bool):
 
     The any-size kernel takes splits of ``attn_chunk`` keys, as many as the longest sequence needs (an eager
     step) or as the context limit needs (a captured one, whose grid is fixed; the spare ones leave at once):
-    the borders are multiples of ``attn_chunk`` either way.  The tensor-core kernel takes a number of splits
-    that fills the machine at this batch size: two of its CTAs fit an SM, one round of CTAs on about 0.6 of
-    those places was fastest over batch sizes 1 to 8, and at most 16 splits merge inside a thread-block
-    cluster (no scratch, no merge kernel)."""
+    the borders are multiples of ``attn_chunk`` either way.  The tensor-core kernel takes the number of splits
+    that fills the machine once at this batch size: two of its CTAs fit an SM, so (sequences x kv heads x
+    splits) stays within 2 x SMs; at most 16 splits merge inside a thread-block cluster (no scratch, no merge
+    kernel), and clusters of more than 8 CTAs only while they fill half of the machine (measured at 2,048 and
+    8,192 keys: 16 / 9 / 8 / 4 / 2 / 1 splits at batch 1 / 2 / 4 / 8 / 16 / 32 with 8 kv heads)."""
     if not fast:
         chunk = int(options.get("attn_chunk", 256))
         cover = int(options.get("max_context", 0)) if options.get("fixed_splits") else 0
         return chunk, max(1, -(-(cover or lay.max_kv_len) // chunk))
-    places = 2 * int(options.get("sm_count", 148))
+    sms = int(options.get("sm_count", 148))
     pairs = lay.B * kv_heads
-    fill = float(options.get("attn_fill", 0.6))
-    splits = min(16, max(1, int(fill * places + pairs // 2) // pairs))
-    return int(options.get("attn_min_chunk", 128)), splits
+    splits = max(1, min(16, 2 * sms // pairs))
+    if splits > 8:
+        splits = max(8, min(splits, sms // pairs))
+    forced = int(options.get("attn_splits", 0))
+    return int(options.get("attn_min_chunk", 128)), forced or splits
 
 
 class AttentionMixer(Mixer):
