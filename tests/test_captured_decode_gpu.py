@@ -104,14 +104,22 @@ def test_decoding_on_the_device_against_the_plain_implementation(models, model):
             best = int(torch.argmax(row))
             if tok != best:
                 assert float(row[best] - row[tok]) < 0.05 * float(row.abs().max()), (model, j, tok, best)
-    # and many steps in one call end where one step at a time ends
+    # and 64 steps in one call, nothing read in between: every token again the plain choice for its own sequence so far
+    # (the two runs may part at a near-tie: the float32 sums of K slices add in any order)
     slots, first = e.start(prompts, [SamplerParams.greedy()] * 3, [0, 1, 2])
-    e.advance(slots, first)
-    last = e.decode_on_device(slots, 64).cpu().tolist()
+    second = e.advance(slots, first)
+    rest = e.decode_on_device(slots, 64, keep_all=True).cpu().tolist()
     for s in slots:
         e.finish(s)
-    agree = sum(int(a == m[-1]) for a, m in zip(last, made))
-    assert agree >= 2, (last, [m[-1] for m in made])      # float32 sums of K slices add in any order: a near-tie may fall the other way once
+    e.check_kernels()
+    for i, p in enumerate(prompts):
+        toks = [first[i], second[i]] + [row[i] for row in rest]
+        logits = P.forward_logits(cfg, w32, list(p) + toks)
+        for j, tok in enumerate(toks):
+            row = logits[len(p) - 1 + j]
+            best = int(torch.argmax(row))
+            if tok != best:
+                assert float(row[best] - row[tok]) < 0.05 * float(row.abs().max()), (model, j, tok, best)
 
 
 @pytest.mark.parametrize("B", [1, 8, 20])
@@ -133,14 +141,14 @@ def test_folded_norms_change_results_by_rounding_only(models, B):
         for i in range(B):
             rows_close(got[i], want[i], "bfloat16", f"batch {B}, fold_norms={fold}, request {i}")
     assert launches[True] < launches[False]
-    # what one eager decode step of this model launches, by launcher
+    # what one eager decode step of this model launches, by launcher (norms as kernels of their own here)
     from titan_b200 import SamplerParams
-    slots, first = e.start([r[:5] for r in reqs[:2]], [SamplerParams.greedy()] * 2, [0, 1])
+    e = Engine.from_tensors(config_from_dict(cfg), w, dtype="bfloat16", max_tokens=512, fold_norms=False, decode_graphs=False)
+    slots, first = e.start([r[:5] for r in reqs[:1]], [SamplerParams.greedy()], [0])
     K.launch_log_start()
-    e.advance(slots, first)                    # batch size 2 has not run before: an eager step
+    e.advance(slots, first)
     log = K.launch_log_stop()
-    for s_ in slots:
-        e.finish(s_)
+    e.finish(slots[0])
     layers = cfg["num_hidden_layers"]
     assert log["rmsnorm"] == 2 * layers + 1 and log["qk_norm_rope"] == layers and log["attn_decode_mma"] == layers
-    assert log["gemm_tc"] == 4 * layers + 1 and log["embed"] == 1 and "gemm_tc_normed" not in log       # this engine does not fold
+    assert log["gemm_tc"] == 4 * layers + 1 and log["embed"] == 1 and "gemm_tc_normed" not in log

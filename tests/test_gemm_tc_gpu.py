@@ -148,10 +148,13 @@ def test_the_norm_before_a_decode_product_folded_into_it(K, M, N, Kd):
     n4 = -(-N // 4) * 4
     for _ in range(2):
         acc = torch.zeros(M, n4, device="cuda")[:, :N]
-        sums = torch.zeros(M, device="cuda")
-        assert K.gemm_tc_normed_accepts(xd, nd, wd, acc, K.EPI_ADD, sums)
-        K.gemm_tc_normed(xd, nd, eps, wd, acc, K.EPI_ADD, stream(), sumsq=sums)
+        parts = torch.full((16, 32), float("nan"), device="cuda")      # one row per K slice is written, nothing is added to
+        assert K.gemm_tc_normed_accepts(xd, nd, wd, acc, K.EPI_ADD, parts)
+        K.gemm_tc_normed(xd, nd, eps, wd, acc, K.EPI_ADD, stream(), sumsq=parts)
         assert K.gemm_tc_error() == 0
+        n_parts = K.gemm_tc_normed_slices(wd, K.EPI_ADD)
+        assert 1 <= n_parts <= 16 and not torch.isnan(parts[:n_parts, :M]).any() and torch.isnan(parts[n_parts:]).all()
+        sums = parts[:n_parts, :M].sum(0)
         assert rel_l2(sums.cpu(), (x.double() ** 2).sum(1).float()) < 1e-5
         scale = 1.0 / torch.sqrt(sums.cpu() / Kd + eps)
         got = acc.cpu() * scale[:, None]
@@ -160,6 +163,6 @@ def test_the_norm_before_a_decode_product_folded_into_it(K, M, N, Kd):
         assert float(rows.max()) < 1.2e-2, rows
     # what it refuses
     assert not K.gemm_tc_normed_accepts(xd, nd, wd, acc, K.EPI_ADD, None)                   # sums need their place
-    assert not K.gemm_tc_normed_accepts(xd, nd, wd, act, K.EPI_SWIGLU, sums)
+    assert not K.gemm_tc_normed_accepts(xd, nd, wd, act, K.EPI_SWIGLU, parts)
     big = torch.zeros(33, Kd, device="cuda")
     assert not K.gemm_tc_normed_accepts(big, nd, wd, torch.zeros(33, N // 2, dtype=torch.bfloat16, device="cuda"), K.EPI_SWIGLU, None)

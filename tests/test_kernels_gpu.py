@@ -211,12 +211,15 @@ def test_qk_norm_rope_scales_rows_whose_norm_was_folded_into_the_projection(K, n
     slots, lens = [1, 3, 0, 2, 4], [9, 70, 1, 64, 200]
     lay = layout_for(slots, [n - 1 for n in lens], [1] * T)
     rows = torch.randn(T, Q + 2 * KV, generator=g)
-    sums = torch.rand(T, generator=g) * 5000 + 10
+    parts = torch.zeros(16, 32)
+    parts[:3, :T] = torch.rand(3, T, generator=g) * 2000 + 10            # three K slices' partial sums
+    parts[3:] = float("nan")                                              # parts beyond the count are not read
+    sums = parts[:3, :T].sum(0)
     scale = 1.0 / torch.sqrt(sums / width + eps)
     qw, kw = 1 + 0.1 * torch.randn(hd, generator=g), 1 + 0.1 * torch.randn(hd, generator=g)
     k_ = torch.arange(hd // 2, dtype=torch.float64)
     inv = (torch.tensor(1e4, dtype=torch.float64) ** (-2 * k_ / hd)).float().cuda()
-    keep = (qw.cuda(), kw.cuda(), sums.cuda())
+    keep = (qw.cuda(), kw.cuda(), parts.cuda())
     outs = []
     for folded in (True, False):
         cache = Paged(K, slots, lens, nkv, hd, torch.bfloat16)
@@ -229,7 +232,7 @@ def test_qk_norm_rope_scales_rows_whose_norm_was_folded_into_the_projection(K, n
         a.pos_of, a.seq_of, a.slot_of_seq, a.kv_len = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr(), lay.kv_len.data_ptr()
         a.cache, a.append, a.T, a.zero_in = cache.view, 1, T, 1
         if folded:
-            a.row_sumsq, a.row_width, a.row_eps = keep[2].data_ptr(), width, eps
+            a.row_sumsq, a.row_parts, a.row_width, a.row_eps = keep[2].data_ptr(), 3, width, eps
         K.qk_norm_rope(a, torch.float32, torch.bfloat16, stream())
         assert float(buf.abs().sum()) == 0                                          # the sums are left cleared
         kv = [torch.cat(cache.get(s, n - 1)) for s, n in zip(slots, lens)]

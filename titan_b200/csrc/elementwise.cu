@@ -44,21 +44,6 @@ __global__ void scale_f32_kernel(float* __restrict__ x, long long n, float facto
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] *= factor;
 }
 
-__global__ void fill_f32_kernel(float* __restrict__ x, long long n, float value) {
-    pdl_launch_dependents();
-    pdl_wait();
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] = value;
-}
-
-// x[i] = value: small float32 buffers that a step wants cleared at its start (sums that its kernels add into).
-extern "C" int tb_fill_f32(float* x, long long n, float value, cudaStream_t stream) {
-    TB_REQUIRE(x && n > 0, "fill_f32: nothing to fill");
-    const long long blocks = (n + 255) / 256;
-    tb_launch(fill_f32_kernel, (int)(blocks < 1024 ? blocks : 1024), 256, 0, stream, x, n, value);
-    TB_CHECK_LAUNCH("fill_f32");
-    return 0;
-}
-
 extern "C" int tb_scale_f32(float* x, long long n, float factor, cudaStream_t stream) {
     TB_REQUIRE(x && n > 0, "scale_f32: nothing to scale");
     const int threads = 256;
@@ -143,6 +128,15 @@ extern "C" int tb_rmsnorm(const float* x, const float* w, void* y, int dtype, co
     return 0;
 }
 
+// The scale of a row whose norm was folded into the projection: its partial sums of squares, one per K slice of
+// that product, added in slice order (read through L2: they were written by the kernel just before).
+__device__ __forceinline__ float folded_row_scale(const QkArgs& a, int t) {
+    if (!a.row_sumsq) return 1.f;
+    float total = 0.f;
+    for (int z = 0; z < a.row_parts; ++z) total += __ldcg(a.row_sumsq + z * 32 + t);
+    return 1.0f / sqrtf(total / (float)a.row_width + a.row_eps);
+}
+
 // ------------------------------------------------------------------ Q/K head norm + rotary (+ append)
 // One warp per (token, head).  Heads 0..nh-1 are Q, nh..nh+nkv-1 are K, and, when the cache is
 // written here, nh+nkv.. are V (copied unchanged).  Per head: RMSNorm over head_dim with a shared
@@ -180,7 +174,7 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
     const int col = is_q ? head * hd : (is_k ? a.nh * hd + (head - a.nh) * hd
                                              : (a.nh + a.nkv) * hd + (head - a.nh - a.nkv) * hd);
     const TIn* x = (const TIn*)a.in + (size_t)t * a.in_stride + col;
-    const float row_scale = a.row_sumsq ? 1.0f / sqrtf(a.row_sumsq[t] / (float)a.row_width + a.row_eps) : 1.f;
+    const float row_scale = folded_row_scale(a, t);
     float v[QK_MAXE];
     float ss = 0.f;
 #pragma unroll
@@ -312,7 +306,7 @@ __global__ void qk_norm_rope_vec_kernel(QkArgs a) {
         const int pos = a.pos_of[t], seq = a.seq_of[t];
         const bool to_cache = a.append && !(a.cache.ring_rows && a.kv_len && pos < a.kv_len[seq] - a.cache.ring_rows);
         row_off[threadIdx.x] = to_cache ? (long long)kv_row_offset(a.cache, a.slot_of_seq[seq], pos, 0) : -1;
-        row_scale[threadIdx.x] = a.row_sumsq ? 1.0f / sqrtf(a.row_sumsq[t] / (float)a.row_width + a.row_eps) : 1.f;
+        row_scale[threadIdx.x] = folded_row_scale(a, t);
     }
     if (a.rope.inv_freq) {
         for (int i = threadIdx.x; i < n_tok * HALF; i += blockDim.x) {
@@ -433,7 +427,7 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     TB_REQUIRE(a.rope.rot >= 0 && a.rope.rot <= a.hd && a.rope.rot % 2 == 0, "qk_norm_rope: rotary_dim %d must be even and <= head_dim %d", a.rope.rot, a.hd);
     TB_REQUIRE(!a.zero_in || (a.append && a.in != a.q_out && a.k_out == nullptr),
                "qk_norm_rope: zeroing the input needs every head to be read (append) and outputs elsewhere");
-    TB_REQUIRE(!a.row_sumsq || a.row_width > 0, "qk_norm_rope: row sums of squares need the rows' width");
+    TB_REQUIRE(!a.row_sumsq || (a.row_width > 0 && a.row_parts > 0 && a.T <= 32), "qk_norm_rope: row sums of squares need the rows' width, their number of parts and at most 32 rows");
     TB_REQUIRE(!a.append || (a.cache.storage && a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv),
                "qk_norm_rope: the cache view does not match the heads");
     const int warps = 4;

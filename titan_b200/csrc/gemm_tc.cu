@@ -96,8 +96,8 @@ struct TcArgs {
     int tail_split;  // persistent kernel, ADD epilogue: K parts of the tiles of the last, partly filled round (1: whole)
     // swap mode with the RMS norm of the input folded in (NORMED): the activations are float32 rows xf [rows_b][ldxf]
     // and the norm's weight norm_w [K]; the kernel multiplies by the weight on the way into shared memory and by
-    // 1/sqrt(mean(x^2) + eps) in its epilogue, or (K cut into slices: no CTA sees a whole row) adds its rows'
-    // partial sums of squares into sumsq_out [rows_b] for the consumer of the sums to apply
+    // 1/sqrt(mean(x^2) + eps) in its epilogue, or (K cut into slices: no CTA sees a whole row) leaves its rows'
+    // partial sums of squares at sumsq_out [slice][32] for the consumer of the sums to add up, in slice order, and apply
     const float* xf; int ldxf; const float* norm_w; float* sumsq_out; float norm_eps;
 };
 
@@ -362,8 +362,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (int u = 0; u < UNITS; ++u) {         // all loads first
                         const int row = (lane >> 3) + 4 * u;
                         if (k_ok && row < a.rows_b) {
+                            // Through L2 only: the rows were changed (float32 reductions at L2) by the product before, and
+                            // this SM's L1 may still hold them as an earlier product's CTAs read them while this grid was
+                            // already launched and waiting (programmatic dependent launch keeps three grids in flight).
                             const float* xp = a.xf + (size_t)row * a.ldxf + k0;
-                            const float4 x0 = *reinterpret_cast<const float4*>(xp), x1 = *reinterpret_cast<const float4*>(xp + 4);
+                            const float4 x0 = __ldcg(reinterpret_cast<const float4*>(xp)), x1 = __ldcg(reinterpret_cast<const float4*>(xp + 4));
                             xv[u][0] = x0.x; xv[u][1] = x0.y; xv[u][2] = x0.z; xv[u][3] = x0.w; xv[u][4] = x1.x; xv[u][5] = x1.y; xv[u][6] = x1.z; xv[u][7] = x1.w;
                         }
                     }
@@ -395,8 +398,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 asm volatile("bar.sync 2, 128;" ::: "memory");
                 if (warp == 2 && lane < BN) {
                     const float total = norm_sh[lane] + norm_sh[BN + lane] + norm_sh[2 * BN + lane] + norm_sh[3 * BN + lane];
-                    if (a.sumsq_out) {                        // K slices: the consumer of the sums scales
-                        if (tile_a == 0 && lane < a.rows_b) atomicAdd(a.sumsq_out + lane, total);
+                    if (a.sumsq_out) {                        // K slices: the consumer of the sums scales (a store, not an atomic: a fixed order of addition)
+                        if (tile_a == 0 && lane < a.rows_b) a.sumsq_out[blockIdx.z * 32 + lane] = total;
                         norm_sh[4 * BN + lane] = 1.f;
                     } else {
                         norm_sh[4 * BN + lane] = 1.0f / sqrtf(total / (float)a.K + a.norm_eps);
@@ -918,32 +921,42 @@ extern "C" int tb_gemm_tc_normed_check(int M, int N, int K, int ldxf, int ldo, i
     return 0;
 }
 
-// out (epilogue) = rmsnorm(xf; norm_w, eps)[M,K] . W[N,K]^T for a decode step's rows, the norm folded into the product:
-// the kernel reads the float32 rows, multiplies by the norm's weight on the way into shared memory and by
-// 1/sqrt(mean(x^2) + eps) in its epilogue (SWIGLU), or (ADD: K is cut into slices) adds the products of the
-// unscaled rows into ``out`` and the rows' sums of squares into ``sumsq_out`` [M], for the consumer to scale.
-extern "C" int tb_gemm_tc_normed(const float* xf, int ldxf, const float* norm_w, float eps, const void* W, void* out,
-                                 int M, int N, int K, int ldo, int epi, float* sumsq_out, cudaStream_t stream) {
-    if (tb_gemm_tc_normed_check(M, N, K, ldxf, ldo, epi, xf, norm_w, W, out, sumsq_out)) return 1;
+// K slices of tb_gemm_tc_normed with the ADD epilogue for these sizes: as many as fill the machine once, four blocks each at least.
+static int normed_slices(int N, int K, int epi) {
     static int sm_count = 0;
     if (!sm_count) {
         int dev = 0;
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) sm_count = 148;
     }
-    const int kb = (K + BK - 1) / BK;
-    const int tiles = (N + BM - 1) / BM;
-    TB_REQUIRE(tiles <= 65535, "gemm_tc_normed: N=%d is too large for one launch", N);
+    const int kb = (K + BK - 1) / BK, tiles = (N + BM - 1) / BM;
     int s = 1;
-    if (epi == TB_EPI_ADD) {                                  // as many K slices as fill the machine once, four blocks each at least
+    if (epi == TB_EPI_ADD) {
         s = 2 * sm_count / tiles;
         const int max_s = kb / 4 > 0 ? kb / 4 : 1;
         s = s < 1 ? 1 : (s > max_s ? max_s : s);
+        s = s > 16 ? 16 : s;
     }
+    const int per = (kb + s - 1) / s;
+    return (kb + per - 1) / per;
+}
+extern "C" int tb_gemm_tc_normed_slices(int N, int K, int epi) { return normed_slices(N, K, epi); }
+
+// out (epilogue) = rmsnorm(xf; norm_w, eps)[M,K] . W[N,K]^T for a decode step's rows, the norm folded into the product:
+// the kernel reads the float32 rows, multiplies by the norm's weight on the way into shared memory and by
+// 1/sqrt(mean(x^2) + eps) in its epilogue (SWIGLU), or (ADD: K is cut into slices) adds the products of the
+// unscaled rows into ``out`` and leaves the rows' sums of squares, one row of 32 per K slice
+// (tb_gemm_tc_normed_slices of them), at ``sumsq_out`` [slices][32], for the consumer to add up and scale.
+extern "C" int tb_gemm_tc_normed(const float* xf, int ldxf, const float* norm_w, float eps, const void* W, void* out,
+                                 int M, int N, int K, int ldo, int epi, float* sumsq_out, cudaStream_t stream) {
+    if (tb_gemm_tc_normed_check(M, N, K, ldxf, ldo, epi, xf, norm_w, W, out, sumsq_out)) return 1;
+    const int kb = (K + BK - 1) / BK;
+    const int tiles = (N + BM - 1) / BM;
+    TB_REQUIRE(tiles <= 65535, "gemm_tc_normed: N=%d is too large for one launch", N);
+    const int s = normed_slices(N, K, epi);
     TcArgs a;
     a.out = out; a.rows_a = N; a.rows_b = M; a.K = K; a.ldo = ldo; a.tiles_m = a.tiles_n = 0; a.tail_split = 1;
     a.k_blocks_per_split = (kb + s - 1) / s;
-    s = (kb + a.k_blocks_per_split - 1) / a.k_blocks_per_split;
     a.atomic = s > 1;
     a.xf = xf; a.ldxf = ldxf; a.norm_w = norm_w; a.sumsq_out = sumsq_out; a.norm_eps = eps;
     CUtensorMap ma;

@@ -25,6 +25,7 @@ struct QkArgs {
     int zero_in;                            // after reading a head, write zeros over it (an accumulation buffer is left clean)
     const int* kv_len;                      // [B] lengths after the step: in a ring, a row that a later token of the step reuses is not written
     // The input rows are products of UNSCALED activations (the RMS norm before the projection was folded into the
-    // product): row t is first multiplied by 1/sqrt(row_sumsq[t] / row_width + row_eps).  Null: the rows are as they should be.
-    const float* row_sumsq; int row_width; float row_eps;
+    // product): row t is first multiplied by 1/sqrt(sum_z row_sumsq[z][t] / row_width + row_eps), the row_parts partial
+    // sums [part][32] added in the order of the parts.  Null: the rows are as they should be.
+    const float* row_sumsq; int row_parts; int row_width; float row_eps;
 };

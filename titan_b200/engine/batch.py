@@ -113,16 +113,17 @@ class StepContext:
     options: Dict[str, object] = field(default_factory=dict)
     scratch: Dict[str, torch.Tensor] = field(default_factory=dict)   # long-lived buffers by name
 
-    sites_taken: int = 0               # places of "acc_row_sums" handed out in this step
+    sites_taken: int = 0               # places of "row_sums" handed out in this step
 
-    def row_sums(self, rows: int) -> Optional[torch.Tensor]:
-        """A float32 vector of ``rows`` zeros of this step's own, for a product that leaves its rows' sums of squares
-        to its consumer; None if the step has no such places (left).  The model clears them all when a step begins."""
-        places = self.scratch.get("acc_row_sums")
-        if places is None or self.sites_taken >= places.shape[0] or rows > places.shape[1]:
+    def row_sums(self) -> Optional[torch.Tensor]:
+        """A float32 [16, 32] place of this step's own, for a product that leaves its rows' partial sums of squares
+        (one row per K slice) to its consumer; None when the step has none left (the model provides one per run of
+        a layer).  Nothing has to be cleared: every part a consumer reads was stored by the producer in the same step."""
+        places = self.scratch.get("row_sums")
+        if places is None or self.sites_taken >= places.shape[0]:
             return None
         self.sites_taken += 1
-        return places[self.sites_taken - 1, :rows]
+        return places[self.sites_taken - 1]
 
     def empty(self, shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

@@ -228,19 +228,23 @@ class Engine:
         self.d2h_bytes += 4 * B
         return host.tolist()
 
-    def decode_on_device(self, slots, steps: int) -> torch.Tensor:
+    def decode_on_device(self, slots, steps: int, keep_all: bool = False) -> torch.Tensor:
         """``steps`` decode steps without the host in the loop: every step feeds each sequence the
         token it sampled in the step before (``last_token`` of its slot).  Returns the last step's
-        tokens as a device tensor; nothing is copied back."""
+        tokens as a device tensor [B], or with ``keep_all`` every step's [steps, B] (a device-to-device
+        copy of B numbers per step); nothing is copied back to the host."""
         if not self._capturable:
             raise StepError("a part of this model cannot run in a captured step; decode with advance()")
         g = self._prepare_graph_step(slots, steps)
-        for _ in range(steps):
+        history = torch.empty((steps, len(slots)), dtype=torch.int32, device=self.device) if keep_all else None
+        for i in range(steps):
             self._replay(g, True)
+            if keep_all:
+                history[i].copy_(g.out_tokens, non_blocking=True)
         for s in slots:
             self.cache.commit(s, self.cache.length[s] + steps)
         self.steps_run += steps
-        return g.out_tokens
+        return history if keep_all else g.out_tokens
 
     def _prepare_graph_step(self, slots, steps: int) -> "DecodeGraph":
         seen = set()

@@ -63,7 +63,7 @@ class QkArgs(Structure):
                 ("rope", RotaryArgs), ("eps", c_float), ("nh", c_int), ("nkv", c_int),
                 ("hd", c_int), ("pos_of", c_void_p), ("seq_of", c_void_p), ("slot_of_seq", c_void_p),
                 ("cache", KvView), ("append", c_int), ("T", c_int), ("zero_in", c_int), ("kv_len", c_void_p),
-                ("row_sumsq", c_void_p), ("row_width", c_int), ("row_eps", c_float)]
+                ("row_sumsq", c_void_p), ("row_parts", c_int), ("row_width", c_int), ("row_eps", c_float)]
 
 
 class AttnArgs(Structure):
@@ -95,7 +95,6 @@ def lib():
         l.tb_uniform24.argtypes = [c_longlong, c_longlong, c_longlong]
         l.tb_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         l.tb_fill_random.argtypes = [c_void_p, c_int, c_longlong, ctypes.c_ulonglong, c_float, c_float, c_void_p]
-        l.tb_fill_f32.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
         l.tb_scale_f32.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
         l.tb_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
         l.tb_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
@@ -183,14 +182,6 @@ def fill_random(out: torch.Tensor, key: int, std: float, mean: float) -> None:
     _check(lib().tb_fill_random(out.data_ptr(), code, out.numel(), key & ((1 << 64) - 1), std, mean, current_stream()))
 
 
-def fill_f32(x: torch.Tensor, value: float, stream: int) -> None:
-    """x[...] = value (float32, contiguous)."""
-    _need_cuda(x)
-    if x.dtype != torch.float32 or not x.is_contiguous():
-        raise KernelError("fill_f32: a contiguous float32 tensor is wanted")
-    _check(lib().tb_fill_f32(x.data_ptr(), x.numel(), value, stream))
-
-
 def scale_f32(x: torch.Tensor, factor: float, stream: int) -> None:
     """x *= factor in place (float32, contiguous)."""
     _need_cuda(x)
@@ -259,14 +250,20 @@ def gemm_tc_normed(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w: torch.T
                    sumsq: Optional[torch.Tensor] = None) -> None:
     """out (epilogue ``epi``) = rmsnorm(x; norm_w, eps) . w^T for the rows of a decode step, the norm folded into the
     product: x is the float32 residual stream.  EPI_SWIGLU: complete.  EPI_ADD: ``out`` (float32) receives the products
-    of the rows times the norm's weight WITHOUT the rows' scales, and ``sumsq`` [M] (float32, zeroed by the caller) the
-    rows' sums of squares; the consumer multiplies row m by 1/sqrt(sumsq[m] / K + eps)."""
+    of the rows times the norm's weight WITHOUT the rows' scales, and ``sumsq`` [slices, 32] (float32; ``gemm_tc_normed_slices``
+    rows of it are written) the rows' sums of squares per K slice; the consumer multiplies row m by
+    1/sqrt(sum_z sumsq[z, m] / K + eps)."""
     _need_cuda(x, norm_w, w, out, sumsq)
     want = torch.bfloat16 if epi == EPI_SWIGLU else torch.float32
     if out.dtype != want:
         raise KernelError(f"gemm_tc_normed: this epilogue writes {want}, the output is {out.dtype}")
     _check(tlib().tb_gemm_tc_normed(x.data_ptr(), x.stride(0), norm_w.data_ptr(), eps, w.data_ptr(), out.data_ptr(), x.shape[0],
                                    w.shape[0], x.shape[1], out.stride(0), epi, _ptr(sumsq), stream))
+
+
+def gemm_tc_normed_slices(w: torch.Tensor, epi: int) -> int:
+    """K slices that gemm_tc_normed cuts this product into (one row of partial sums of squares each)."""
+    return int(tlib().tb_gemm_tc_normed_slices(w.shape[0], w.shape[1], epi))
 
 
 def gemm_tc_error() -> int:

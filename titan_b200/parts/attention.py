@@ -173,10 +173,10 @@ class AttentionMixer(Mixer):
             if qkv is None:
                 qkv = ctx.scratch[key] = torch.zeros((T, width), dtype=torch.float32, device=ctx.device)
             # The norm before the projection, if it was handed over unevaluated, goes into the product: the kernel
-            # adds the products of the unscaled rows into the sums and the rows' sums of squares into a place of
-            # this step's own, and the head norm/rotary kernel scales the rows first.
-            if isinstance(h, DeferredNorm):
-                row_sums = ctx.row_sums(T)
+            # adds the products of the unscaled rows into the sums and leaves the rows' sums of squares, one part per
+            # K slice, at a place of this step's own; the head norm/rotary kernel adds the parts and scales the rows first.
+            if isinstance(h, DeferredNorm) and T <= 32:
+                row_sums = ctx.row_sums()
                 if row_sums is not None and K.gemm_tc_normed_accepts(h.x, h.weight, self.w_qkv, qkv, linear.EPI_ADD, row_sums):
                     K.gemm_tc_normed(h.x, h.weight, h.eps, self.w_qkv, qkv, linear.EPI_ADD, ctx.stream, sumsq=row_sums)
                 else:
@@ -196,7 +196,8 @@ class AttentionMixer(Mixer):
         if not (self.shared or wide_sum):
             qa.k_out, qa.k_stride = qkv.data_ptr() + Q * qkv.element_size(), width
         if row_sums is not None:
-            qa.row_sumsq, qa.row_width, qa.row_eps = row_sums.data_ptr(), s.hidden_size, h.eps
+            qa.row_sumsq, qa.row_parts = row_sums.data_ptr(), K.gemm_tc_normed_slices(self.w_qkv, linear.EPI_ADD)
+            qa.row_width, qa.row_eps = s.hidden_size, h.eps
         K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
 
         attn = ctx.empty((T, Q))
