@@ -73,6 +73,8 @@ class DecoderModel:
         lay = ctx.layout
         x = torch.empty((lay.T, self.spec.hidden_size), dtype=torch.float32, device=ctx.device)
         K.embed(self.embedding, lay.tokens, x, ctx.stream)
+        if self.spec.embedding_scale is not None:
+            K.scale_f32(x, float(self.spec.embedding_scale), ctx.stream)
         if "row_sums" not in ctx.scratch:      # places where folded norms leave sums of squares: one per run of a layer
             ctx.scratch["row_sums"] = torch.zeros((len(self.spec.order), 16, 32), dtype=torch.float32, device=ctx.device)
         for run, i in enumerate(self.spec.order):
