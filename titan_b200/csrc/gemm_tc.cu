@@ -211,7 +211,10 @@ __device__ __forceinline__ void epilogue_rows(const float* val, float* tile, con
     for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = val[j];
     __syncwarp();
     if (EPI == TB_EPI_ADD && atomic) {
-        // four rows per instruction, a lane adds four neighbouring columns with one vector reduction
+        // The residual sum as reductions at L2 (red.global.add.v4.f32), for whole tiles as for the K parts of a tail
+        // tile: nothing is read back, so the epilogue does not wait for a round trip per 32 rows (the o-projection of
+        // a 2,048-token prompt: 69 -> 58 us); an element that one CTA alone adds to gets the same sum as by load and store.
+        // Four rows per instruction, a lane adds four neighbouring columns with one vector reduction.
         const int sub = lane >> 3, c = (lane & 7) * 4;
         float* base = (float*)a.out + (size_t)row0 * a.ldo + col0 + c;
 #pragma unroll
@@ -590,7 +593,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         int t, kb0, count;
         for (int j = 0; segs.next(t, kb0, count); ++j) {
             const int tile_a = t % a.tiles_m, tile_b = t / a.tiles_m;
-            const bool partial = count < n_kb;           // another CTA adds the rest of this tile
+            (void)count;
             const int buf = j & 1;
             mbar_wait(acc_full + buf, (j >> 1) & 1, 3);
             tc_fence_after();
@@ -602,7 +605,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 for (int c = 0; c < BN; c += 32) {
                     float v[32];
                     tmem_ld32(taddr + c, v);
-                    epilogue_rows<EPI>(v, tile, a, row0, tile_b * BN + c, a.rows_b, lane, partial);
+                    epilogue_rows<EPI>(v, tile, a, row0, tile_b * BN + c, a.rows_b, lane, true);
                 }
             } else {
 #pragma unroll 1
@@ -729,7 +732,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int t, kb0, count;
         for (int j = 0; segs.next(t, kb0, count); ++j) {
             const int tile_a = t % a.tiles_m, tile_b = t / a.tiles_m;
-            const bool partial = count < n_kb;
+            (void)count;
             const int buf = j & 1;
             mbar_wait(acc_full + buf, (j >> 1) & 1, 3);
             tc_fence_after();
@@ -739,7 +742,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int c = 0; c < PAIR_N; c += 32) {
                 float v[32];
                 tmem_ld32(taddr + c, v);
-                if (EPI == TB_EPI_ADD) epilogue_rows<EPI>(v, tile, a, row0, tile_b * PAIR_N + c, a.rows_b, lane, partial);
+                if (EPI == TB_EPI_ADD) epilogue_rows<EPI>(v, tile, a, row0, tile_b * PAIR_N + c, a.rows_b, lane, true);
                 else epilogue_chunk<EPI, false, 32>(v, a, row0 + lane, tile_b * PAIR_N + c, lane);
             }
             tc_fence_before();
