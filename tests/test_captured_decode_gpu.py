@@ -141,14 +141,53 @@ def test_folded_norms_change_results_by_rounding_only(models, B):
         for i in range(B):
             rows_close(got[i], want[i], "bfloat16", f"batch {B}, fold_norms={fold}, request {i}")
     assert launches[True] < launches[False]
-    # what one eager decode step of this model launches, by launcher (norms as kernels of their own here)
+    # what one eager decode step of this model launches, by launcher: with every kernel on its own, and by default
     from titan_b200 import SamplerParams
-    e = Engine.from_tensors(config_from_dict(cfg), w, dtype="bfloat16", max_tokens=512, fold_norms=False, decode_graphs=False)
-    slots, first = e.start([r[:5] for r in reqs[:1]], [SamplerParams.greedy()], [0])
-    K.launch_log_start()
-    e.advance(slots, first)
-    log = K.launch_log_stop()
-    e.finish(slots[0])
     layers = cfg["num_hidden_layers"]
+    logs = {}
+    for name, kw in (("apart", dict(fold_norms=False, fold_head_norm=False)), ("default", {})):
+        e = Engine.from_tensors(config_from_dict(cfg), w, dtype="bfloat16", max_tokens=512, decode_graphs=False, **kw)
+        slots, first = e.start([r[:5] for r in reqs[:1]], [SamplerParams.greedy()], [0])
+        K.launch_log_start()
+        e.advance(slots, first)
+        logs[name] = K.launch_log_stop()
+        e.finish(slots[0])
+    log = logs["apart"]
     assert log["rmsnorm"] == 2 * layers + 1 and log["qk_norm_rope"] == layers and log["attn_decode_mma"] == layers
     assert log["gemm_tc"] == 4 * layers + 1 and log["embed"] == 1 and "gemm_tc_normed" not in log
+    log = logs["default"]
+    assert log["rmsnorm"] == 1 and "qk_norm_rope" not in log and log["attn_decode_mma"] == layers
+    assert log["gemm_tc_normed"] == 2 * layers and log["gemm_tc"] == 2 * layers + 1
+
+
+@pytest.mark.parametrize("model", ["hd128", "hd64"])
+def test_head_norm_inside_the_attention_kernel_changes_results_by_rounding_only(models, model):
+    """Decode steps with head norm, rotation and cache append inside the attention kernel (the default) and as a
+    kernel of their own, on sequences that cross pages while they grow (the new key's row moves through a page and
+    into the next; the split that holds it changes): both against the plain implementation, and the caches they
+    leave are the same to rounding (a later prompt step reads them)."""
+    from titan_b200 import Engine, StepEntry
+    from titan_b200.config import config_from_dict
+    cfg, w, w32 = models[model]
+    lens = [62, 1, 127, 190]
+    reqs = [random_tokens(n + 70, cfg["vocab_size"], 700 + n) for n in lens]
+    want = [P.forward_logits(cfg, w32, r) for r in reqs]
+    for fold in (True, False):
+        e = Engine.from_tensors(config_from_dict(cfg), w, dtype="bfloat16", max_tokens=4 * 320, max_context=320, fold_head_norm=fold,
+                                decode_graphs=False, mark_freed_pages=True)
+        for round_ in range(2):
+            got = teacher_forced(e, reqs, lens, 66) if round_ == 0 else None
+            if got is not None:
+                for i in range(4):
+                    rows_close(got[i], want[i][lens[i] - 1:lens[i] + 66], "bfloat16", f"{model}, fold_head_norm={fold}, request {i}")
+        # the cache that decoding left: decode 66 tokens, then read all of it with a chunk of 4 more tokens
+        slots = [e.alloc_slot() for _ in reqs]
+        e.step([StepEntry(s, r[:n], []) for s, r, n in zip(slots, reqs, lens)])
+        for d in range(66):
+            e.step([StepEntry(s, [r[n + d]], []) for s, r, n in zip(slots, reqs, lens)])
+        out = e.step([StepEntry(s, r[n + 66:n + 70], [0, 1, 2, 3]) for s, r, n in zip(slots, reqs, lens)])
+        for i in range(4):
+            rows_close(out[4 * i:4 * i + 4], want[i][lens[i] + 66:lens[i] + 70], "bfloat16", f"{model}, fold_head_norm={fold}, cache of request {i}")
+        for s in slots:
+            e.free_slot(s)
+        e.check_kernels()

@@ -196,7 +196,7 @@ def test_decoding_at_the_end_of_a_32768_token_context(dtype):
 def test_a_step_that_fails_between_a_product_and_its_consumer_spoils_no_later_step(monkeypatch):
     """Decode products add their K slices into a float32 buffer that the next kernel consumes and leaves zeroed.
     A step that ends between the two (here: the consumer's launcher refuses once) must not leave its sums
-    there for the next step of the same shape, eager or captured."""
+    there for the next step of the same shape, eager or captured; with the consumer as a kernel of its own too."""
     from titan_b200 import Engine, StepEntry, kernels as K
     from titan_b200.config import config_from_dict
     w = random_weights(MID, 33, torch.bfloat16, std=0.03)
@@ -208,17 +208,17 @@ def test_a_step_that_fails_between_a_product_and_its_consumer_spoils_no_later_st
     e.step([StepEntry(s, toks[:30], [])])
     rows_close(e.step([StepEntry(s, [toks[30]], [0])]), want[30:31], "bfloat16", "before the failure")
     assert any(k.startswith("acc_") for k in e.scratch)
-    real, calls = K.qk_norm_rope, {"n": 0}
+    real, calls = K.attn_decode_mma, {"n": 0}       # the consumer of the sums: the attention kernel (head norm inside it)
 
     def refuse_once(*a, **k):
         calls["n"] += 1
         if calls["n"] == 2:                                             # the second layer's: the first layer's sums were consumed, these are not
             raise K.KernelError("refused for the test")
         return real(*a, **k)
-    monkeypatch.setattr(K, "qk_norm_rope", refuse_once)
+    monkeypatch.setattr(K, "attn_decode_mma", refuse_once)
     with pytest.raises(K.KernelError):
         e.step([StepEntry(s, [toks[31]], [0])])
-    monkeypatch.setattr(K, "qk_norm_rope", real)
+    monkeypatch.setattr(K, "attn_decode_mma", real)
     assert e.cache.length[s] == 31                                      # nothing was committed
     # the failed step wrote the first layer's key and value of position 31, which the same token now writes again
     rows_close(e.step([StepEntry(s, [toks[31]], [0])]), want[31:32], "bfloat16", "the step after the failure")

@@ -2,6 +2,7 @@
 // titan_b200.kernels.AttnArgs.
 #pragma once
 #include "common.cuh"
+#include "qk_args.h"
 
 // Where the tensor-core prompt kernels take keys and values from.
 #define TB_KV_FROM_STEP 1      // the step's own rows: every sequence of the step starts at position 0
@@ -24,6 +25,11 @@ struct AttnArgs {
     // put there by a copy, not by a kernel); 2: early_len[slot] + 1 = batch.kv_len[b] (the cache's committed
     // length of the slot, for steps whose kv_len a kernel of the step computes); 0 or a null pointer: none.
     const int* early_len; int early_mode;
+    // decode on tensor cores, optional: the head norm / rotary / append step folded into the attention kernel.  The
+    // queries and the new token's key and value then come as the projection's float32 sums (fused_qk->in, rows of
+    // fused_qk->in_stride: Q heads, K heads, V heads), with the norm weights, the rotary block, the row scales and the
+    // cache of *fused_qk; ``q`` is not read.  Null: queries are bfloat16 rows at ``q`` and the cache holds every key.
+    const QkArgs* fused_qk;
 };
 
 // How decode attention cuts the keys of ONE sequence into splits: ``chunk`` keys each while ``n_splits`` of

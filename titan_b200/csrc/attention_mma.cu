@@ -41,6 +41,11 @@ struct DecArgs {
     int nh; int nkv; int window; float scale_log2;   // scale * log2(e)
     int chunk; int n_splits;
     __nv_bfloat16* out; int out_stride;      // [B][out_stride]: written by the kernel itself when its splits form a cluster
+    // FUSED: the projection's float32 sums [B][acc_stride] (Q heads, K heads, V heads; rows not yet scaled if row_sumsq is
+    // given), which this kernel scales, norms, rotates and, for the new key and value, appends to the cache itself
+    float* acc; int acc_stride; const float* q_w; const float* k_w; float qk_eps; TbRotary rope;
+    const float* row_sumsq; int row_parts; int row_width; float row_eps;
+    __nv_bfloat16* storage; long long v_half;      // the cache's K half and the distance to its V half, in elements
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -67,9 +72,44 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk16) { return (uint32_t
 // its part (m, l, O) in its own shared memory, and after a cluster barrier every CTA merges a slice of the
 // output rows from all of them through distributed shared memory and writes the result; no scratch
 // memory, no merge kernel.
-template <int HD, bool WIDE, bool CL>
+// One head of the projection's sums through row scale, head norm and rotation: a lane holds elements lane + 32 i, so an
+// element and its rotation partner (HD / 2 further on) sit in the same lane.  The formulas of qk_norm_rope_vec_kernel.
+template <int HD>
+__device__ __forceinline__ void load_head(const float* src, int lane, float* v) {      // through L2: reductions at L2 made these sums
+#pragma unroll
+    for (int i = 0; i < HD / 32; ++i) v[i] = __ldcg(src + lane + 32 * i);
+}
+template <int HD>
+__device__ __forceinline__ void fused_head(float row_scale, const float* w, float eps, const TbRotary& rope,
+                                           int pos, int lane, float* v) {
+    constexpr int N = HD / 32;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) { v[i] *= row_scale; ss += v[i] * v[i]; }
+    if (w) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float scale = 1.0f / sqrtf(ss / (float)HD + eps);
+#pragma unroll
+        for (int i = 0; i < N; ++i) v[i] = v[i] * scale * w[lane + 32 * i];
+    }
+    if (rope.inv_freq) {
+#pragma unroll
+        for (int i = 0; i < N / 2; ++i) {
+            float sv, cv;
+            sincosf(((float)pos + rope.offset) * rope.inv_freq[lane + 32 * i], &sv, &cv);
+            sv *= rope.magnitude; cv *= rope.magnitude;
+            const float x = v[i], y = v[i + N / 2];
+            v[i] = x * cv - y * sv;
+            v[i + N / 2] = y * cv + x * sv;
+        }
+    }
+}
+
+template <int HD, bool WIDE, bool CL, bool FUSED = false>
 __global__ void __launch_bounds__(DEC_THREADS)
 attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
+    static_assert(!FUSED || CL, "the folded head norm needs the cluster's barrier to know when the sums may be cleared");
     constexpr int STAGES = HD == 128 ? 3 : 4;
     constexpr int BOXES = HD / 64;                      // 64-column boxes per tile
     constexpr uint32_t TILE_BYTES = PAGE * HD * 2;      // one K or V page of one head
@@ -78,6 +118,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(base + STAGES * 2 * TILE_BYTES);
     uint64_t* empty = full + STAGES;
+    __nv_bfloat16* q_sh = (__nv_bfloat16*)(empty + STAGES + 2);      // FUSED: the group's queries [16][HD], made here
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
@@ -109,7 +150,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
             const uint64_t once = l2_evict_first_policy();          // a step reads every page once
             // before the wait: the first pages of the ring, but never the page that holds position len - 1
             // (the last page of the split that ends at len), whose newest row is still being written
-            const int old_pages = n_pages - (hi == len && n_pages > 0 ? 1 : 0);
+            // (FUSED: no kernel before writes the cache; the newest row is this kernel's own and is patched in shared memory)
+            const int old_pages = FUSED ? n_pages : n_pages - (hi == len && n_pages > 0 ? 1 : 0);
             const int ahead = early ? (old_pages < STAGES ? old_pages : STAGES) : 0;
             for (int i = 0; i < n_pages; ++i) {
                 if (early && i == ahead) {
@@ -144,8 +186,57 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     const int g = lane >> 2, t = lane & 3;
     uint32_t qf[KS][4];
     if (early) pdl_wait();
+    // FUSED: the warp that owns the newest key's row of the last page keeps the new key and value, to put them there
+    const int new_row = (len - 1) % PAGE;
+    const bool appends = FUSED && hi == len && n_pages > 0 && warp == (new_row >> 4);
+    float kn[HD / 32], vn[HD / 32];
+    if (FUSED) {
+        // every load first (the sums of this warp's first query head, of the new key and value, the row's parts):
+        // they do not depend on one another, and at small batches this kernel is all latency
+        float* arow = a.acc + (size_t)b * a.acc_stride;
+        float* ksrc = arow + (size_t)(a.nh + kh) * HD;
+        float* vsrc = arow + (size_t)(a.nh + a.nkv + kh) * HD;
+        float v[HD / 32];
+        if (warp < group) load_head<HD>(arow + (size_t)(kh * group + warp) * HD, lane, v);
+        if (appends) { load_head<HD>(ksrc, lane, kn); load_head<HD>(vsrc, lane, vn); }
+        float rs = 1.f;
+        if (a.row_sumsq) {
+            float part[16];
+#pragma unroll
+            for (int z = 0; z < 16; ++z) part[z] = z < a.row_parts ? __ldcg(a.row_sumsq + z * 32 + b) : 0.f;
+            float total = 0.f;
+#pragma unroll
+            for (int z = 0; z < 16; ++z) total += part[z];                 // in the order of the parts
+            rs = 1.0f / sqrtf(total / (float)a.row_width + a.row_eps);
+        }
+        const int pos = len - 1;
+        for (int h = warp; h < group; h += DEC_WARPS) {
+            if (h != warp) load_head<HD>(arow + (size_t)(kh * group + h) * HD, lane, v);
+            fused_head<HD>(rs, a.q_w, a.qk_eps, a.rope, pos, lane, v);
+#pragma unroll
+            for (int i = 0; i < HD / 32; ++i) q_sh[h * HD + lane + 32 * i] = __float2bfloat16_rn(v[i]);
+        }
+        if (appends) {
+            fused_head<HD>(rs, a.k_w, a.qk_eps, a.rope, pos, lane, kn);
+            const int slot = a.slot_of_seq[b];
+            const int crow = a.ring_rows ? pos % a.ring_rows : pos;
+            const int page = a.table[(size_t)slot * a.table_width + crow / PAGE];
+            __nv_bfloat16* kdst = a.storage + ((size_t)(page * a.nkv + kh) * PAGE + new_row) * HD;
+#pragma unroll
+            for (int i = 0; i < HD / 32; ++i) {
+                vn[i] *= rs;
+                kn[i] = __bfloat162float(__float2bfloat16_rn(kn[i]));          // as the cache holds them
+                vn[i] = __bfloat162float(__float2bfloat16_rn(vn[i]));
+                kdst[lane + 32 * i] = __float2bfloat16_rn(kn[i]);
+                kdst[a.v_half + lane + 32 * i] = __float2bfloat16_rn(vn[i]);
+                ksrc[lane + 32 * i] = 0.f;                                       // the sums are left cleared for the next step
+                vsrc[lane + 32 * i] = 0.f;
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32));      // the group's queries are in shared memory
+    }
     {
-        const __nv_bfloat16* q0 = a.q + (size_t)b * a.q_stride + (size_t)(kh * group) * HD;
+        const __nv_bfloat16* q0 = FUSED ? q_sh : a.q + (size_t)b * a.q_stride + (size_t)(kh * group) * HD;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             const int d = ks * 16 + 2 * t;
@@ -165,6 +256,17 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
         mbar_wait(full + s, (i / STAGES) & 1, &g_attn_error, 2);
         const uint32_t ks_base = smem_u32(base + s * 2 * TILE_BYTES);
         const uint32_t vs_base = ks_base + TILE_BYTES;
+        if (appends && i == n_pages - 1) {                  // the page as the cache held it before this step: put the new row in
+            uint8_t* kt = base + s * 2 * TILE_BYTES;
+#pragma unroll
+            for (int j = 0; j < HD / 32; ++j) {
+                const int e = lane + 32 * j;
+                const uint32_t off = (uint32_t)((e >> 6) * (PAGE * 128)) + swz(new_row, (e & 63) >> 3) + (uint32_t)((e & 7) * 2);
+                *reinterpret_cast<__nv_bfloat16*>(kt + off) = __float2bfloat16_rn(kn[j]);
+                *reinterpret_cast<__nv_bfloat16*>(kt + TILE_BYTES + off) = __float2bfloat16_rn(vn[j]);
+            }
+            __syncwarp();
+        }
         // S[16 x 16] = Q . K^T for this warp's 16 keys: two n-tiles of 8 keys
         float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         {
@@ -271,6 +373,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     if (CL) {
         // every thread of every CTA of the cluster (the producer warp too): parts written -> merged -> may leave
         tbtma::cluster_sync();
+        if (FUSED && split == 0) {      // every split has read the queries' sums long ago: clear them for the next step
+            float* qsum = a.acc + (size_t)b * a.acc_stride + (size_t)(kh * group) * HD;
+            for (int i = threadIdx.x; i < group * HD; i += DEC_THREADS) qsum[i] = 0.f;
+        }
         const int n = a.n_splits, total = group * HD;
         const int per = (total + n - 1) / n, first = (int)tbtma::cluster_rank() * per, last = min(total, first + per);
         for (int idx = first + (int)threadIdx.x; idx < last; idx += DEC_THREADS) {
@@ -470,23 +576,26 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, const __gri
 
 extern "C" int tb_attn_merge(const AttnArgs* args, int dtype, cudaStream_t stream);
 
-template <int HD, bool WIDE, bool CL>
+// Shared memory of the decode kernel: the ring, its barriers, and the group's queries (used when the head norm is folded in).
+template <int HD> constexpr size_t decode_smem() {
+    return 1024 + (size_t)(HD == 128 ? 3 : 4) * 2 * PAGE * HD * 2 + 2 * (HD == 128 ? 3 : 4) * sizeof(uint64_t) + 16 + 16 * HD * 2;
+}
+template <int HD, bool WIDE, bool CL, bool FUSED = false>
 static int launch_decode(const CUtensorMap& map, const DecArgs& d, dim3 grid, cudaStream_t stream) {
-    constexpr int STAGES = HD == 128 ? 3 : 4;
-    constexpr size_t smem = 1024 + (size_t)STAGES * 2 * PAGE * HD * 2 + 2 * STAGES * sizeof(uint64_t);
+    constexpr size_t smem = decode_smem<HD>();
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE, CL>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // room for several CTAs per SM
-        if (CL) cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE, CL>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);    // clusters of up to 16
+        const cudaError_t e = cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE, CL, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE, CL, FUSED>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);   // room for several CTAs per SM
+        if (CL) cudaFuncSetAttribute(attn_decode_mma_kernel<HD, WIDE, CL, FUSED>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);    // clusters of up to 16
         TB_REQUIRE(e == cudaSuccess, "attn_decode_mma: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
     if (CL) {
-        const cudaError_t e = tb_launch_cluster_z(attn_decode_mma_kernel<HD, WIDE, CL>, grid, DEC_THREADS, smem, stream, (int)grid.z, map, d);
+        const cudaError_t e = tb_launch_cluster_z(attn_decode_mma_kernel<HD, WIDE, CL, FUSED>, grid, DEC_THREADS, smem, stream, (int)grid.z, map, d);
         TB_REQUIRE(e == cudaSuccess, "attn_decode_mma: cluster launch failed: %s", cudaGetErrorString(e));
     } else {
-        tb_launch(attn_decode_mma_kernel<HD, WIDE, CL>, grid, DEC_THREADS, smem, stream, map, d);
+        tb_launch(attn_decode_mma_kernel<HD, WIDE, CL, FUSED>, grid, DEC_THREADS, smem, stream, map, d);
     }
     return 0;
 }
@@ -497,8 +606,7 @@ static int cluster_limit() {
     static int limit = -1;
     if (limit < 0) {
         limit = 1;
-        constexpr int STAGES = HD == 128 ? 3 : 4;
-        constexpr size_t smem = 1024 + (size_t)STAGES * 2 * PAGE * HD * 2 + 2 * STAGES * sizeof(uint64_t);
+        constexpr size_t smem = decode_smem<HD>();
         auto kernel = attn_decode_mma_kernel<HD, WIDE, true>;
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
@@ -520,6 +628,10 @@ static int cluster_limit() {
 template <int HD, bool WIDE>
 static int launch_decode_any(const CUtensorMap& map, const DecArgs& d, dim3 grid, bool may_cluster, bool* merged, cudaStream_t stream) {
     *merged = may_cluster && (int)grid.z <= cluster_limit<HD, WIDE>();
+    if (d.acc) {
+        TB_REQUIRE(*merged, "attn_decode_mma: the folded head norm needs the splits to form a cluster (%d splits)", (int)grid.z);
+        return launch_decode<HD, WIDE, true, true>(map, d, grid, stream);
+    }
     TB_REQUIRE(*merged || d.scratch, "attn_decode_mma: %d splits need scratch memory", (int)grid.z);
     return *merged ? launch_decode<HD, WIDE, true>(map, d, grid, stream) : launch_decode<HD, WIDE, false>(map, d, grid, stream);
 }
@@ -535,7 +647,20 @@ extern "C" int tb_attn_decode_mma_check(const AttnArgs* a, int dtype) {
     TB_REQUIRE(a->cache.page_size == PAGE, "attn_decode_mma: pages of %d rows, not %d", PAGE, a->cache.page_size);
     TB_REQUIRE(a->nkv > 0 && a->nh % a->nkv == 0 && a->nh / a->nkv <= 16, "attn_decode_mma: at most 16 query heads per kv head");
     TB_REQUIRE(a->chunk > 0 && a->chunk % PAGE == 0, "attn_decode_mma: the chunk %d must be a multiple of %d", a->chunk, PAGE);
-    TB_REQUIRE(a->q_stride % 2 == 0 && ((uintptr_t)a->q & 3) == 0, "attn_decode_mma: queries must be 4-byte aligned");
+    if (a->fused_qk) {
+        const QkArgs& q = *a->fused_qk;
+        TB_REQUIRE(q.in && q.in_stride % 4 == 0 && ((uintptr_t)q.in & 15) == 0, "attn_decode_mma: the projection's sums must be 16-byte aligned float32 rows");
+        TB_REQUIRE(q.nh == a->nh && q.nkv == a->nkv && q.hd == a->hd, "attn_decode_mma: the folded head norm's heads do not match");
+        TB_REQUIRE(!q.rope.inv_freq || q.rope.rot == a->hd, "attn_decode_mma: the folded rotation must span the whole head");
+        TB_REQUIRE(q.cache.storage == a->cache.storage && a->batch.B <= 32, "attn_decode_mma: the folded append writes the cache it reads, for at most 32 sequences");
+        TB_REQUIRE(!q.row_sumsq || (q.row_width > 0 && q.row_parts > 0 && q.row_parts <= 16), "attn_decode_mma: row sums of squares need their width and 1 to 16 parts");
+        const bool wide = a->nh / a->nkv > 8;
+        const int limit = a->hd == 128 ? (wide ? cluster_limit<128, true>() : cluster_limit<128, false>())
+                                       : (wide ? cluster_limit<64, true>() : cluster_limit<64, false>());
+        TB_REQUIRE(g_decode_cluster && a->out && a->n_splits <= limit, "attn_decode_mma: the folded head norm needs the splits to form a cluster");
+    } else {
+        TB_REQUIRE(a->q_stride % 2 == 0 && ((uintptr_t)a->q & 3) == 0, "attn_decode_mma: queries must be 4-byte aligned");
+    }
     return 0;
 }
 
@@ -559,6 +684,14 @@ extern "C" int tb_attn_decode_mma(const AttnArgs* args, cudaStream_t stream) {
     d.nh = a.nh; d.nkv = a.nkv; d.window = a.window; d.scale_log2 = a.scale * 1.4426950408889634f;
     d.chunk = a.chunk; d.n_splits = a.n_splits;
     d.out = (__nv_bfloat16*)a.out; d.out_stride = a.out_stride;
+    d.acc = nullptr; d.acc_stride = 0; d.q_w = d.k_w = nullptr; d.qk_eps = 0.f; d.rope = TbRotary{nullptr, 0, 0.f, 1.f};
+    d.row_sumsq = nullptr; d.row_parts = 0; d.row_width = 1; d.row_eps = 0.f; d.storage = nullptr; d.v_half = 0;
+    if (a.fused_qk) {
+        const QkArgs& q = *a.fused_qk;
+        d.acc = (float*)const_cast<void*>(q.in); d.acc_stride = q.in_stride; d.q_w = q.q_w; d.k_w = q.k_w; d.qk_eps = q.eps; d.rope = q.rope;
+        d.row_sumsq = q.row_sumsq; d.row_parts = q.row_parts; d.row_width = q.row_width; d.row_eps = q.row_eps;
+        d.storage = (__nv_bfloat16*)a.cache.storage; d.v_half = (long long)a.cache.num_pages * a.nkv * PAGE * a.hd;
+    }
     dim3 grid(a.batch.B, a.nkv, a.n_splits);
     const bool wide = a.nh / a.nkv > 8;
     int rc;

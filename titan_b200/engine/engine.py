@@ -49,6 +49,7 @@ class EngineOptions:
     attention: str = "fast"           # "plain": the any-size attention kernels even where a tensor-core one fits
     attn_chunk: int = 256             # keys per split of decode attention
     mark_freed_pages: bool = False    # debugging: pages of a freed slot are overwritten with a large finite value, so a stale read shows
+    fold_head_norm: bool = True       # decode steps: head norm, rotation and cache append inside the attention kernel where it can take them
     fold_norms: bool = True           # decode steps: a norm goes into the product that consumes it where the kernels can take it
     early_pages: bool = True          # decode attention requests pages of older positions before it waits for the kernels before it
     decode_graphs: bool = True        # replay single-token steps as CUDA graphs once a batch size has run eagerly
@@ -79,7 +80,7 @@ class Engine:
         self.sampler = DeviceSampler(self.cache.state, max_slots, self.spec.vocab_size, self.device)
         self.scratch: Dict[str, torch.Tensor] = {}
         self.step_options = {"gemm": options.gemm, "attention": options.attention, "attn_chunk": options.attn_chunk,
-                             "early_pages": options.early_pages, "fold_norms": options.fold_norms,
+                             "early_pages": options.early_pages, "fold_norms": options.fold_norms, "fold_head_norm": options.fold_head_norm,
                              "max_context": self.cache.max_context,
                              "sm_count": torch.cuda.get_device_properties(self.device).multi_processor_count}
         self.h2d_bytes = 0

@@ -71,7 +71,7 @@ class AttnArgs(Structure):
                 ("out", c_void_p), ("out_stride", c_int), ("cache", KvView), ("batch", Batch),
                 ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("window", c_int), ("scale", c_float),
                 ("chunk", c_int), ("n_splits", c_int), ("scratch", c_void_p),
-                ("early_len", c_void_p), ("early_mode", c_int)]
+                ("early_len", c_void_p), ("early_mode", c_int), ("fused_qk", POINTER(QkArgs))]
 
 
 class SampleArgs(Structure):

@@ -23,6 +23,7 @@ the named layer's cache.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 from typing import List, Optional
 
@@ -198,7 +199,12 @@ class AttentionMixer(Mixer):
         if row_sums is not None:
             qa.row_sumsq, qa.row_parts = row_sums.data_ptr(), K.gemm_tc_normed_slices(self.w_qkv, linear.EPI_ADD)
             qa.row_width, qa.row_eps = s.hidden_size, h.eps
-        K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
+        # A decode step whose Q | K | V are float32 sums may leave head norm, rotation and append to the attention
+        # kernel itself (one kernel less between the projection and the attention); decided below, where the
+        # attention's arguments are known.  Everything else runs the kernel now.
+        folds_head_norm = wide_sum and ctx.options.get("fold_head_norm", True)
+        if not folds_head_norm:
+            K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
 
         attn = ctx.empty((T, Q))
         aa = K.AttnArgs()
@@ -221,6 +227,11 @@ class AttentionMixer(Mixer):
                     aa.early_len, aa.early_mode = lay.kv_len.data_ptr(), 1
                 elif lay.committed_len is not None:
                     aa.early_len, aa.early_mode = lay.committed_len.data_ptr(), 2
+            if folds_head_norm:
+                aa.fused_qk = ctypes.pointer(qa)
+                if not (fast and K.attn_decode_mma_accepts(aa, q_buf.dtype)):      # the kernel cannot take it in: as a kernel of its own, then
+                    aa.fused_qk = None
+                    K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
             if fast and K.attn_decode_mma_accepts(aa, q_buf.dtype):
                 K.attn_decode_mma(aa, ctx.stream)
             else:
