@@ -652,8 +652,8 @@ extern "C" int tb_attn_decode_mma_check(const AttnArgs* a, int dtype) {
         TB_REQUIRE(q.in && q.in_stride % 4 == 0 && ((uintptr_t)q.in & 15) == 0, "attn_decode_mma: the projection's sums must be 16-byte aligned float32 rows");
         TB_REQUIRE(q.nh == a->nh && q.nkv == a->nkv && q.hd == a->hd, "attn_decode_mma: the folded head norm's heads do not match");
         TB_REQUIRE(!q.rope.inv_freq || q.rope.rot == a->hd, "attn_decode_mma: the folded rotation must span the whole head");
-        TB_REQUIRE(q.cache.storage == a->cache.storage && a->batch.B <= 32, "attn_decode_mma: the folded append writes the cache it reads, for at most 32 sequences");
-        TB_REQUIRE(!q.row_sumsq || (q.row_width > 0 && q.row_parts > 0 && q.row_parts <= 16), "attn_decode_mma: row sums of squares need their width and 1 to 16 parts");
+        TB_REQUIRE(q.cache.storage == a->cache.storage, "attn_decode_mma: the folded append writes the cache it reads");
+        TB_REQUIRE(!q.row_sumsq || (q.row_width > 0 && q.row_parts > 0 && q.row_parts <= 16 && a->batch.B <= 32), "attn_decode_mma: row sums of squares need their width, 1 to 16 parts and at most 32 rows");
         const bool wide = a->nh / a->nkv > 8;
         const int limit = a->hd == 128 ? (wide ? cluster_limit<128, true>() : cluster_limit<128, false>())
                                        : (wide ? cluster_limit<64, true>() : cluster_limit<64, false>());
