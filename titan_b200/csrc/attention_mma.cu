@@ -381,13 +381,25 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
         const int per = (total + n - 1) / n, first = (int)tbtma::cluster_rank() * per, last = min(total, first + per);
         for (int idx = first + (int)threadIdx.x; idx < last; idx += DEC_THREADS) {
             const int row = idx / HD, d = idx % HD;
+            // all loads from the other CTAs' shared memory first (up to 16 splits, unrolled), then the arithmetic:
+            // one trip through the cluster's network instead of one per split
+            float mr[16], lr[16], vr[16];
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                const bool on = r < n;
+                mr[r] = on ? tbtma::ld_cluster_f32(tbtma::cluster_addr(fin + 16 * HD + row, r)) : -1e30f;
+                lr[r] = on ? tbtma::ld_cluster_f32(tbtma::cluster_addr(fin + 16 * HD + 16 + row, r)) : 0.f;
+                vr[r] = on ? tbtma::ld_cluster_f32(tbtma::cluster_addr(fin + row * HD + d, r)) : 0.f;
+            }
             float M = -1e30f;
-            for (int r = 0; r < n; ++r) M = fmaxf(M, tbtma::ld_cluster_f32(tbtma::cluster_addr(fin + 16 * HD + row, r)));
+#pragma unroll
+            for (int r = 0; r < 16; ++r) M = fmaxf(M, mr[r]);
             float acc = 0.f, L = 0.f;
-            for (int r = 0; r < n; ++r) {               // in the order of the splits
-                const float f = exp2f(tbtma::ld_cluster_f32(tbtma::cluster_addr(fin + 16 * HD + row, r)) - M);
-                acc += f * tbtma::ld_cluster_f32(tbtma::cluster_addr(fin + row * HD + d, r));
-                L += f * tbtma::ld_cluster_f32(tbtma::cluster_addr(fin + 16 * HD + 16 + row, r));
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {              // in the order of the splits
+                const float f = r < n ? exp2f(mr[r] - M) : 0.f;
+                acc += f * vr[r];
+                L += f * lr[r];
             }
             a.out[(size_t)b * a.out_stride + (size_t)(kh * group + row) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         }
