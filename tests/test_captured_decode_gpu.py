@@ -191,3 +191,26 @@ def test_head_norm_inside_the_attention_kernel_changes_results_by_rounding_only(
         for s in slots:
             e.free_slot(s)
         e.check_kernels()
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_captured_decode_over_a_ring_cache(hd):
+    """Layers with a window keep a ring of rows: the attention kernel that appends the new key itself writes
+    position p into row p % ring, and the page it patches in shared memory is the ring's.  Sequences that
+    start inside the window and decode far past it (the ring wraps several times), captured steps."""
+    from titan_b200 import Engine
+    from titan_b200.config import config_from_dict
+    cfg = dict(MID64 if hd == 64 else MID, sliding_window=100, layer_types=["sliding_attention", "full_attention"], max_position_embeddings=1024)
+    w = random_weights(cfg, 40 + hd, torch.bfloat16, std=0.03)
+    w32 = {k: v.float() for k, v in w.items()}
+    lens = [60, 130, 1]
+    steps = 300
+    reqs = [random_tokens(n + steps, cfg["vocab_size"], 800 + n) for n in lens]
+    want = [P.forward_logits(cfg, w32, r)[n - 1:] for r, n in zip(reqs, lens)]
+    e = Engine.from_tensors(config_from_dict(cfg), w, dtype="bfloat16", max_tokens=3 * 512, max_context=512, mark_freed_pages=True)
+    assert sorted(g.ring_rows for g in e.cache.groups) == [0, 128]
+    got = teacher_forced(e, reqs, lens, steps)
+    assert e.graph_launches > 0
+    for i in range(3):
+        rows_close(got[i], want[i], "bfloat16", f"head size {hd}, request {i}")
+        rows_close(got[i][-40:], want[i][-40:], "bfloat16", f"head size {hd}, request {i}, the last steps")
