@@ -214,3 +214,22 @@ def test_captured_decode_over_a_ring_cache(hd):
     for i in range(3):
         rows_close(got[i], want[i], "bfloat16", f"head size {hd}, request {i}")
         rows_close(got[i][-40:], want[i][-40:], "bfloat16", f"head size {hd}, request {i}, the last steps")
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd", [(12, 1, 64), (16, 1, 128), (10, 2, 128)])
+def test_captured_decode_with_large_and_odd_groups(heads, kv_heads, hd):
+    """More than eight query heads per kv head (both halves of the tensor-core tile's rows are live), and a group of
+    five: the attention kernel norms and rotates a group's queries with its four warps taking heads in turn."""
+    from titan_b200 import Engine
+    from titan_b200.config import config_from_dict
+    cfg = dict(MID, num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=hd, hidden_size=640, intermediate_size=1280,
+               vocab_size=1500, rms_norm_eps=1e-5)
+    w = random_weights(cfg, heads + hd, torch.bfloat16, std=0.03)
+    w32 = {k: v.float() for k, v in w.items()}
+    lens = [5, 90, 200]
+    reqs = [random_tokens(n + 40, cfg["vocab_size"], 60 + n) for n in lens]
+    want = [P.forward_logits(cfg, w32, r)[n - 1:] for r, n in zip(reqs, lens)]
+    e = Engine.from_tensors(config_from_dict(cfg), w, dtype="bfloat16", max_tokens=3 * 256, max_context=256)
+    got = teacher_forced(e, reqs, lens, 40)
+    for i in range(3):
+        rows_close(got[i], want[i], "bfloat16", f"{heads}/{kv_heads} heads of {hd}, request {i}")
