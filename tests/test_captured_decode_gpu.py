@@ -233,3 +233,28 @@ def test_captured_decode_with_large_and_odd_groups(heads, kv_heads, hd):
     got = teacher_forced(e, reqs, lens, 40)
     for i in range(3):
         rows_close(got[i], want[i], "bfloat16", f"{heads}/{kv_heads} heads of {hd}, request {i}")
+
+
+@pytest.mark.parametrize("B", [1, 3, 8])
+def test_reproducible_mode_gives_the_same_bits_on_every_run(models, B):
+    """``reproducible=True``: the K slices of the decode products add up in a fixed order (and no prompt tile is cut
+    along K), so the same requests in the same batch give bit-identical logits on every run, on another engine, and
+    replayed from a graph or launched kernel by kernel; against the plain implementation they stay as close as the
+    default mode, which is allowed to differ from run to run in the last bits."""
+    from titan_b200 import Engine
+    from titan_b200.config import config_from_dict
+    cfg, w, w32 = models["hd128"]
+    lens = PROMPTS[B]
+    steps = 40
+    reqs = [random_tokens(n + steps, cfg["vocab_size"], 4100 + 3 * n + B) for n in lens]
+    want = [P.forward_logits(cfg, w32, r)[n - 1:] for r, n in zip(reqs, lens)]
+    kw = dict(dtype="bfloat16", max_tokens=B * 768, max_context=768, reproducible=True)
+    first = Engine.from_tensors(config_from_dict(cfg), w, decode_graphs=True, **kw)
+    runs = [teacher_forced(first, reqs, lens, steps), teacher_forced(first, reqs, lens, steps)]
+    assert first.graph_launches > 0
+    runs.append(teacher_forced(Engine.from_tensors(config_from_dict(cfg), w, decode_graphs=True, **kw), reqs, lens, steps))
+    runs.append(teacher_forced(Engine.from_tensors(config_from_dict(cfg), w, decode_graphs=False, **kw), reqs, lens, steps))
+    for i in range(B):
+        rows_close(runs[0][i], want[i], "bfloat16", f"batch {B}, request {i}")
+        for other in runs[1:]:
+            assert torch.equal(other[i], runs[0][i]), (B, i, float((other[i] - runs[0][i]).abs().max()))

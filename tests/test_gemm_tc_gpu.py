@@ -166,3 +166,42 @@ def test_the_norm_before_a_decode_product_folded_into_it(K, M, N, Kd):
     assert not K.gemm_tc_normed_accepts(xd, nd, wd, act, K.EPI_SWIGLU, parts)
     big = torch.zeros(33, Kd, device="cuda")
     assert not K.gemm_tc_normed_accepts(big, nd, wd, torch.zeros(33, N // 2, dtype=torch.bfloat16, device="cuda"), K.EPI_SWIGLU, None)
+
+
+@pytest.mark.parametrize("M,N,Kd", [(1, 4096, 4096), (8, 4096, 12288), (13, 1000, 4104), (17, 384, 2048), (40, 2600, 1096), (64, 4096, 4096),
+                                    (100, 520, 4096), (127, 4096, 2048)])
+def test_k_slices_added_in_a_fixed_order_give_the_same_bits_every_time(K, M, N, Kd):
+    """``ordered``: the K slices of a decode product meet inside a thread-block cluster and are added in slice order, one
+    writer per element.  Six runs from the same residual must agree bit for bit (reductions at L2 do so only by luck),
+    and agree with float64 as closely as the default does."""
+    g = torch.Generator().manual_seed(7 * M + N)
+    x = torch.randn(M, Kd, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, Kd, generator=g) * 0.1).to(torch.bfloat16).cuda()
+    res = torch.randn(M, N, generator=g)
+    want = res + P.linear(x.float().cpu(), w.float().cpu())
+    n4 = -(-N // 4) * 4
+    runs = []
+    for _ in range(6):
+        acc = torch.zeros(M, n4, device="cuda")[:, :N]
+        acc.copy_(res)
+        K.gemm_tc(x, w, acc, K.EPI_ADD, stream(), ordered=True)
+        runs.append(acc.clone())
+    assert K.gemm_tc_error() == 0
+    assert rel_l2(runs[0].cpu(), want) < 1e-5
+    for r in runs[1:]:
+        assert torch.equal(r, runs[0])
+    if M <= 32:                  # and with the norm folded in
+        xf = torch.randn(M, Kd, generator=g).cuda()
+        nw = (1 + 0.2 * torch.randn(Kd, generator=g)).cuda()
+        runs = []
+        for _ in range(6):
+            acc = torch.zeros(M, n4, device="cuda")[:, :N]
+            parts = torch.zeros(16, 32, device="cuda")
+            K.gemm_tc_normed(xf, nw, 1e-6, w, acc, K.EPI_ADD, stream(), sumsq=parts, ordered=True)
+            runs.append((acc.clone(), parts.clone()))
+        assert K.gemm_tc_error() == 0
+        n_parts = K.gemm_tc_normed_slices(w, K.EPI_ADD)
+        scale = 1.0 / torch.sqrt(runs[0][1][:n_parts, :M].sum(0).cpu() / Kd + 1e-6)
+        assert rel_l2(runs[0][0].cpu() * scale[:, None], P.linear(P.rms_norm(xf.cpu(), nw.cpu(), 1e-6), w.float().cpu())) < 6e-3
+        for acc, parts in runs[1:]:
+            assert torch.equal(acc, runs[0][0]) and torch.equal(parts, runs[0][1])

@@ -12,7 +12,7 @@ HTTP request (engine/engine-core/src/sampler.rs:13-24): --prompt-ids, --prompts-
 (default 512, main.rs:515), --top-k (40), --repetition-penalty (1.1), --seed (42), --stop-ids,
 --dtype, --random <config.json> (random weights from a configuration and --weights-seed),
 --max-context (longest sequence; default: the model's position limit or what the cache holds) and
---max-batch (sequences per generation batch, default 64).
+--max-batch (sequences per generation batch, default 64), --reproducible (the same bits on every run, slower).
 Not kept: ``serve``, ``agent``, -e/--engine, -s/--speculative, --system, -p/--port: servers,
 streaming, speculative decoding and text are outside this library.
 """
@@ -52,6 +52,7 @@ def build_parser() -> argparse.ArgumentParser:
         p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
         p.add_argument("--max-context", type=int, default=None, help="longest sequence (prompt + generated); default: the model's limit or the cache's size")
         p.add_argument("--max-batch", type=int, default=64, help="sequences that generate together; more prompts run one batch after another")
+        p.add_argument("--reproducible", action="store_true", help="bfloat16: partial sums add up in a fixed order, the same bits on every run (slower)")
     sub.add_parser("help", help="print this help")
     return ap
 
@@ -60,7 +61,8 @@ def _engine(args):
     from . import Engine
     from .config import config_from_dict
     model = args.model or args.model_pos
-    kw = dict(dtype=args.dtype, max_tokens=args.kv_capacity, max_context=args.max_context, max_batch=args.max_batch)
+    kw = dict(dtype=args.dtype, max_tokens=args.kv_capacity, max_context=args.max_context, max_batch=args.max_batch,
+              reproducible=args.reproducible)
     if args.random:
         with open(args.random) as f:
             return Engine.from_random(config_from_dict(json.load(f)), args.weights_seed, **kw)

@@ -254,10 +254,16 @@ __device__ __forceinline__ void epilogue_rows(const float* val, float* tile, con
     }
 }
 
-template <int BN, int EPI, bool SWAP, bool NORMED = false>
+// ORDERED (swap mode, ADD epilogue): the K slices of a tile are the CTAs of one thread-block cluster.  Each leaves its
+// partial tile in its own shared memory; after a cluster barrier every CTA adds up a share of the tile's elements
+// from all slices, in slice order, through distributed shared memory, and adds the sum to the output.  An element is
+// then written once, by one CTA, from a sum whose order is fixed: the same inputs give the same bits on every run,
+// which float32 reductions that meet at L2 in the order they arrive do not.
+template <int BN, int EPI, bool SWAP, bool NORMED = false, bool ORDERED = false>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs a) {
     static_assert(!NORMED || (SWAP && BN <= 32), "the folded norm is for decode tiles (swap mode, at most 32 rows of activations)");
+    static_assert(!ORDERED || (SWAP && EPI == TB_EPI_ADD), "slices in a fixed order: swap mode with the ADD epilogue");
     constexpr int STAGES = stages_of<BN, EPI, SWAP>();
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     constexpr uint32_t TMEM_COLS = tmem_cols_for<BN>();
@@ -424,7 +430,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] *= norm_sh[4 * BN + c + j];
                     }
-                    epilogue_chunk<EPI, SWAP, 32>(v, a, row, tile_b * BN + c, lane);
+                    if (ORDERED) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) reinterpret_cast<float*>(smem_a)[(c + j) * BM + quarter * 32 + lane] = v[j];
+                    } else {
+                        epilogue_chunk<EPI, SWAP, 32>(v, a, row, tile_b * BN + c, lane);
+                    }
                 }
             } else {
                 float v[16];
@@ -433,7 +444,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] *= norm_sh[4 * BN + j];
                 }
-                epilogue_chunk<EPI, SWAP, 16>(v, a, row, tile_b * BN, lane);
+                if (ORDERED) {      // the ring has drained: its first bytes hold this slice's part, [token][row of the tile]
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) reinterpret_cast<float*>(smem_a)[j * BM + quarter * 32 + lane] = v[j];
+                } else {
+                    epilogue_chunk<EPI, SWAP, 16>(v, a, row, tile_b * BN, lane);
+                }
             }
         }
     }
@@ -443,6 +459,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
+    }
+    if (ORDERED) {
+        // every thread of every CTA of the cluster: parts written -> summed -> may leave
+        __syncwarp();
+        tbtma::cluster_sync();
+        const int n = (int)gridDim.z, total = a.rows_b * BM;          // tokens x rows of the tile (swap mode has one tile of tokens)
+        const int per = (total + n - 1) / n, first = (int)tbtma::cluster_rank() * per, last = min(total, first + per);
+        const float* part = reinterpret_cast<const float*>(smem_a);
+        for (int idx = first + (int)threadIdx.x; idx < last; idx += THREADS) {
+            float v[16];
+#pragma unroll
+            for (int r = 0; r < 16; ++r) v[r] = r < n ? tbtma::ld_cluster_f32(tbtma::cluster_addr(part + idx, r)) : 0.f;     // all loads first
+            float sum = 0.f;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) sum += v[r];                  // in the order of the slices
+            const int m = idx / BM, row = tile_a * BM + idx % BM;
+            if (row < a.rows_a) atomicAdd((float*)a.out + (size_t)m * a.ldo + row, sum);      // the element's only writer in this launch
+        }
+        __syncwarp();
+        tbtma::cluster_sync();
     }
 }
 
@@ -788,6 +824,58 @@ int launch_tc_normed(const CUtensorMap& ma, const TcArgs& a, dim3 grid, cudaStre
     return 0;
 }
 
+// Swap mode, ADD epilogue, the K slices of a tile as one cluster (grid.z CTAs) that adds them up in slice order.
+template <int BN, bool NORMED>
+int launch_tc_ordered(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t stream) {
+    static bool configured = false;
+    constexpr size_t smem = smem_for<BN, true, stages_of<BN, TB_EPI_ADD, true>()>();
+    auto kernel = gemm_tc_kernel<BN, TB_EPI_ADD, true, NORMED, true>;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);      // clusters of up to 16
+        TB_REQUIRE(e == cudaSuccess, "gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    const cudaError_t e = tb_launch_cluster_z(kernel, grid, THREADS, smem, stream, (int)grid.z, ma, mb, a);
+    TB_REQUIRE(e == cudaSuccess, "gemm_tc: the launch of clusters of %d K slices failed: %s", (int)grid.z, cudaGetErrorString(e));
+    return 0;
+}
+// The most K slices that one cluster of this kernel can hold on this device: 16 where the non-portable size is
+// allowed and can be placed, else 8, else 1 (no slices).
+template <int BN, bool NORMED>
+int ordered_limit() {
+    static int limit = -1;
+    if (limit < 0) {
+        limit = 1;
+        constexpr size_t smem = smem_for<BN, true, stages_of<BN, TB_EPI_ADD, true>()>();
+        auto kernel = gemm_tc_kernel<BN, TB_EPI_ADD, true, NORMED, true>;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        for (int size : {16, 8}) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(1, 1, size); cfg.blockDim = dim3(THREADS, 1, 1); cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)size;
+            cfg.attrs = attr; cfg.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters > 0) { limit = size; break; }
+            cudaGetLastError();
+        }
+    }
+    return limit;
+}
+int ordered_limit_for(int bn, bool normed) {
+    if (normed) return bn == 16 ? ordered_limit<16, true>() : ordered_limit<32, true>();
+    switch (bn) {
+        case 16: return ordered_limit<16, false>();
+        case 32: return ordered_limit<32, false>();
+        case 64: return ordered_limit<64, false>();
+    }
+    return ordered_limit<128, false>();
+}
+
 template <int BN, int EPI>
 int launch_persistent_epi(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, dim3 grid, cudaStream_t stream) {
     static bool configured = false;
@@ -950,8 +1038,10 @@ extern "C" int tb_gemm_tc_normed_slices(int N, int K, int epi) { return normed_s
 // 1/sqrt(mean(x^2) + eps) in its epilogue (SWIGLU), or (ADD: K is cut into slices) adds the products of the
 // unscaled rows into ``out`` and leaves the rows' sums of squares, one row of 32 per K slice
 // (tb_gemm_tc_normed_slices of them), at ``sumsq_out`` [slices][32], for the consumer to add up and scale.
+// ordered: the K slices add up in slice order inside a thread-block cluster (the same bits on every run) instead of through
+// float32 reductions that meet at L2 in the order they arrive.
 extern "C" int tb_gemm_tc_normed(const float* xf, int ldxf, const float* norm_w, float eps, const void* W, void* out,
-                                 int M, int N, int K, int ldo, int epi, float* sumsq_out, cudaStream_t stream) {
+                                 int M, int N, int K, int ldo, int epi, float* sumsq_out, int ordered, cudaStream_t stream) {
     if (tb_gemm_tc_normed_check(M, N, K, ldxf, ldo, epi, xf, norm_w, W, out, sumsq_out)) return 1;
     const int kb = (K + BK - 1) / BK;
     const int tiles = (N + BM - 1) / BM;
@@ -966,17 +1056,25 @@ extern "C" int tb_gemm_tc_normed(const float* xf, int ldxf, const float* norm_w,
     if (tb_make_map_bf16(&ma, W, N, K, K, BM)) return 1;
     dim3 grid(1, tiles, s);
     int rc;
-    if (M <= 16) rc = epi == TB_EPI_ADD ? launch_tc_normed<16, TB_EPI_ADD>(ma, a, grid, stream) : launch_tc_normed<16, TB_EPI_SWIGLU>(ma, a, grid, stream);
+    if (ordered && epi == TB_EPI_ADD && s > 1) {
+        TB_REQUIRE(s <= ordered_limit_for(M <= 16 ? 16 : 32, true), "gemm_tc_normed: this device places no cluster of %d K slices", s);
+        a.atomic = 0;
+        rc = M <= 16 ? launch_tc_ordered<16, true>(ma, ma, a, grid, stream) : launch_tc_ordered<32, true>(ma, ma, a, grid, stream);
+    } else if (M <= 16) rc = epi == TB_EPI_ADD ? launch_tc_normed<16, TB_EPI_ADD>(ma, a, grid, stream) : launch_tc_normed<16, TB_EPI_SWIGLU>(ma, a, grid, stream);
     else rc = epi == TB_EPI_ADD ? launch_tc_normed<32, TB_EPI_ADD>(ma, a, grid, stream) : launch_tc_normed<32, TB_EPI_SWIGLU>(ma, a, grid, stream);
     if (rc) return rc;
     TB_CHECK_LAUNCH("gemm_tc_normed");
     return 0;
 }
 
-// splits: K slices (swap mode, ADD epilogue only); 0 = choose.
+// splits: K slices (swap mode, ADD epilogue only); 0 = choose; -1 = choose, and add the parts of a sum in a fixed order
+// (swap mode: the slices of a tile form a thread-block cluster; prompt products: no tile is cut along K), so that
+// the same inputs give the same bits on every run.
 extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N, int K, int ldx, int ldo, int epi,
                           int splits, cudaStream_t stream) {
     if (tb_gemm_tc_check(M, N, K, ldx, ldo, epi, X, W, out)) return 1;
+    const bool ordered = splits < 0;
+    if (ordered) splits = 0;
     const bool swap = M < g_swap_below;
     const int kb = (K + BK - 1) / BK;
     CUtensorMap ma, mb;
@@ -995,7 +1093,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
     auto tail_parts = [&](int total, int workers) {
         const int tail = total % workers;
         int best = 1;
-        if (epi != TB_EPI_ADD || !g_tail_split || !tail) return best;      // total < workers: every tile is in the last round
+        if (epi != TB_EPI_ADD || !g_tail_split || ordered || !tail) return best;      // total < workers: every tile is in the last round
         double best_cost = 1.0;
         for (int p = 2; p <= 8 && kb / p >= 4; ++p) {
             const double cost = (double)((tail * p + workers - 1) / workers) / p + 0.02 * p;
@@ -1011,7 +1109,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
         // outputs) costs 1, a lone 128 x 256 tile 1.1 and a 128 x 128 tile 0.85; what decides is how many
         // rounds of tiles the shape needs and how many rows its padding wastes.  The ADD epilogue cuts a
         // last round into K parts, so its rounds count as fractions.
-        const bool parts = epi == TB_EPI_ADD && g_tail_split;
+        const bool parts = epi == TB_EPI_ADD && g_tail_split && !ordered;
         auto rounds = [&](long long tiles, int workers) {
             const double r = parts ? (double)tiles / workers : (double)((tiles + workers - 1) / workers);
             return r < 0.125 ? 0.125 : r;
@@ -1058,13 +1156,22 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
             s = splits > 0 ? splits : room / tiles;
             const int max_s = kb / 4 > 0 ? kb / 4 : 1;              // at least four 64-wide blocks per slice
             s = s < 1 ? 1 : (s > max_s ? max_s : s);
+            if (ordered) { const int lim = ordered_limit_for(bn, false); s = s > lim ? lim : s; }
         }
         a.k_blocks_per_split = (kb + s - 1) / s;
         s = (kb + a.k_blocks_per_split - 1) / a.k_blocks_per_split;  // no empty slice
-        a.atomic = s > 1;
+        a.atomic = s > 1 && !ordered;
         if (tb_make_map_bf16(&ma, W, N, K, K, BM) || tb_make_map_bf16(&mb, X, M, K, ldx, bn)) return 1;
         dim3 grid(1, tiles, s);
         TB_REQUIRE(tiles <= 65535, "gemm_tc: N=%d is too large for one launch", N);
+        if (ordered && epi == TB_EPI_ADD && s > 1) {
+            switch (bn) {
+                case 16: rc = launch_tc_ordered<16, false>(ma, mb, a, grid, stream); break;
+                case 32: rc = launch_tc_ordered<32, false>(ma, mb, a, grid, stream); break;
+                case 64: rc = launch_tc_ordered<64, false>(ma, mb, a, grid, stream); break;
+                default: rc = launch_tc_ordered<128, false>(ma, mb, a, grid, stream); break;
+            }
+        } else
         switch (bn) {
             case 16: rc = launch_epi<16, true>(epi, ma, mb, a, grid, stream); break;
             case 32: rc = launch_epi<32, true>(epi, ma, mb, a, grid, stream); break;

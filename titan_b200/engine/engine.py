@@ -53,6 +53,7 @@ class EngineOptions:
     fold_norms: bool = True           # decode steps: a norm goes into the product that consumes it where the kernels can take it
     early_pages: bool = True          # decode attention requests pages of older positions before it waits for the kernels before it
     decode_graphs: bool = True        # replay single-token steps as CUDA graphs once a batch size has run eagerly
+    reproducible: bool = False        # bfloat16: partial sums along K add up in a fixed order, so the same requests in the same batches give the same bits on every run (slower)
     device: str = "cuda:0"
 
 
@@ -81,6 +82,7 @@ class Engine:
         self.scratch: Dict[str, torch.Tensor] = {}
         self.step_options = {"gemm": options.gemm, "attention": options.attention, "attn_chunk": options.attn_chunk,
                              "early_pages": options.early_pages, "fold_norms": options.fold_norms, "fold_head_norm": options.fold_head_norm,
+                             "reproducible": options.reproducible,
                              "max_context": self.cache.max_context,
                              "sm_count": torch.cuda.get_device_properties(self.device).multi_processor_count}
         self.h2d_bytes = 0

@@ -120,7 +120,7 @@ def tlib():
         lib()
         l = _build.load("tensor")
         l.tb_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
-        l.tb_gemm_tc_normed.argtypes = [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+        l.tb_gemm_tc_normed.argtypes = [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
         l.tb_gemm_tc_normed_check.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
         l.tb_gemm_tc_check.argtypes = [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
         l.tb_attn_decode_mma.argtypes = [POINTER(AttnArgs), c_void_p]
@@ -219,8 +219,11 @@ def gemm_tc_accepts(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: in
                                   x.data_ptr(), w.data_ptr(), out.data_ptr()) == 0
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, stream: int, splits: int = 0) -> None:
-    """out (epilogue ``epi``) = x[M,K] . w[N,K]^T on the tcgen05 tensor cores (bfloat16 operands)."""
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, stream: int, splits: int = 0, ordered: bool = False) -> None:
+    """out (epilogue ``epi``) = x[M,K] . w[N,K]^T on the tcgen05 tensor cores (bfloat16 operands).  ``ordered``: partial
+    sums along K add up in a fixed order (the K slices of a decode product inside a thread-block cluster, no prompt tile
+    cut along K), so that the same inputs give the same bits on every run; the default lets float32 reductions meet at
+    L2 in the order they arrive, which is faster and differs from run to run in the last bits."""
     _need_cuda(x, w, out)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_tc: operands must be bfloat16")
@@ -232,7 +235,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, strea
     if w.shape[1] != K_ or not w.is_contiguous() or x.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError(f"gemm_tc: shapes do not fit: x {tuple(x.shape)} w {tuple(w.shape)}")
     _check(tlib().tb_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K_, x.stride(0), out.stride(0), epi,
-                            splits, stream))
+                            -1 if ordered and not splits else splits, stream))
 
 
 def gemm_tc_normed_accepts(x: torch.Tensor, norm_w: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int,
@@ -247,18 +250,18 @@ def gemm_tc_normed_accepts(x: torch.Tensor, norm_w: torch.Tensor, w: torch.Tenso
 
 
 def gemm_tc_normed(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Tensor, epi: int, stream: int,
-                   sumsq: Optional[torch.Tensor] = None) -> None:
+                   sumsq: Optional[torch.Tensor] = None, ordered: bool = False) -> None:
     """out (epilogue ``epi``) = rmsnorm(x; norm_w, eps) . w^T for the rows of a decode step, the norm folded into the
     product: x is the float32 residual stream.  EPI_SWIGLU: complete.  EPI_ADD: ``out`` (float32) receives the products
     of the rows times the norm's weight WITHOUT the rows' scales, and ``sumsq`` [slices, 32] (float32; ``gemm_tc_normed_slices``
     rows of it are written) the rows' sums of squares per K slice; the consumer multiplies row m by
-    1/sqrt(sum_z sumsq[z, m] / K + eps)."""
+    1/sqrt(sum_z sumsq[z, m] / K + eps).  ``ordered``: as for ``gemm_tc``."""
     _need_cuda(x, norm_w, w, out, sumsq)
     want = torch.bfloat16 if epi == EPI_SWIGLU else torch.float32
     if out.dtype != want:
         raise KernelError(f"gemm_tc_normed: this epilogue writes {want}, the output is {out.dtype}")
     _check(tlib().tb_gemm_tc_normed(x.data_ptr(), x.stride(0), norm_w.data_ptr(), eps, w.data_ptr(), out.data_ptr(), x.shape[0],
-                                   w.shape[0], x.shape[1], out.stride(0), epi, _ptr(sumsq), stream))
+                                   w.shape[0], x.shape[1], out.stride(0), epi, _ptr(sumsq), int(bool(ordered)), stream))
 
 
 def gemm_tc_normed_slices(w: torch.Tensor, epi: int) -> int:

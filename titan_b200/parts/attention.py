@@ -179,7 +179,8 @@ class AttentionMixer(Mixer):
             if isinstance(h, DeferredNorm) and T <= 32:
                 row_sums = ctx.row_sums()
                 if row_sums is not None and K.gemm_tc_normed_accepts(h.x, h.weight, self.w_qkv, qkv, linear.EPI_ADD, row_sums):
-                    K.gemm_tc_normed(h.x, h.weight, h.eps, self.w_qkv, qkv, linear.EPI_ADD, ctx.stream, sumsq=row_sums)
+                    K.gemm_tc_normed(h.x, h.weight, h.eps, self.w_qkv, qkv, linear.EPI_ADD, ctx.stream, sumsq=row_sums,
+                                     ordered=bool(ctx.options.get("reproducible", False)))
                 else:
                     row_sums = None
             if row_sums is None:

@@ -18,6 +18,6 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epi: int, ctx) -
     if w.dtype == torch.bfloat16 and ctx.options.get("gemm", "fast") != "plain":
         fast = getattr(K, "gemm_tc", None)
         if fast is not None and K.gemm_tc_accepts(x, w, out, epi):
-            fast(x, w, out, epi, ctx.stream)
+            fast(x, w, out, epi, ctx.stream, ordered=bool(ctx.options.get("reproducible", False)))
             return
     K.gemm_simt(x, w, out, epi, ctx.stream)
