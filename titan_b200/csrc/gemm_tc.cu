@@ -348,6 +348,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tc_commit(accum);
             }
         } else {
+            // NORMED: the norm's weight for this warp's first activation tile depends on nothing that the kernel before
+            // makes: it is requested while the wait for that kernel lasts
+            float wv[8];
+            if (NORMED && warp - 2 < n_kb) {
+                const int k0 = (kb0 + warp - 2) * BK + (lane & 7) * 8;
+                if (k0 < a.K) {
+                    const float4 w0 = *reinterpret_cast<const float4*>(a.norm_w + k0), w1 = *reinterpret_cast<const float4*>(a.norm_w + k0 + 4);
+                    wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+                }
+            }
             pdl_wait();
             if (NORMED) {
                 // The four epilogue warps make the activation tiles meanwhile, a stage each in turn (four stages in
@@ -360,10 +370,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int u = 0; u < UNITS; ++u) ss[u] = 0.f;
                 for (int i = w4; i < n_kb; i += 4) {
                     const int s = i % STAGES, round = i / STAGES;
-                    float xv[UNITS][8], wv[8];
+                    float xv[UNITS][8];
                     const int chunk = lane & 7, k0 = (kb0 + i) * BK + chunk * 8;
                     const bool k_ok = k0 < a.K;               // K is a multiple of 8: a chunk is inside or outside
-                    if (k_ok) {
+                    if (k_ok && i != w4) {
                         const float4 w0 = *reinterpret_cast<const float4*>(a.norm_w + k0), w1 = *reinterpret_cast<const float4*>(a.norm_w + k0 + 4);
                         wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
                     }

@@ -95,6 +95,27 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr_) {      /
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr_) : "memory");
     return v;
 }
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr_, float v) {      // into another CTA's shared memory
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr_), "f"(v) : "memory");
+}
+// Split cluster barrier: every thread of the cluster arrives (does not block) and, later, waits.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+// A wait that also sees what other CTAs of the cluster wrote into this CTA's shared memory before they arrived
+// (mbar_arrive_cluster releases at cluster scope; this acquires at cluster scope).  Bounded like mbar_wait.
+__device__ __forceinline__ void mbar_wait_cluster(uint64_t* bar, uint32_t parity, unsigned int* error_word, unsigned code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return;
+        if ((i & 255u) == 255u && *(volatile unsigned int*)error_word) break;
+    }
+    atomicCAS(error_word, 0u, code);
+}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
 }
