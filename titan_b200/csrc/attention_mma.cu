@@ -71,8 +71,8 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk16) { return (uint32_t
 // HD: head size (64 or 128).  WIDE: the group has more than 8 query heads (rows 8..15 of the tile are live).
 // CL: the splits of a (sequence, kv head) are the CTAs of one thread-block cluster (up to 16).  Every CTA merges a
 // share of the output rows: each split SENDS its part of every share (sums, maxima, sums of weights) into the
-// shared memory of the CTA that merges it and arrives on that CTA's barrier; a CTA that has heard from all splits
-// merges from its own memory, writes the result and leaves.  No scratch memory, no merge kernel, and no barrier of
+// shared memory of the CTA that merges it (st.async: every value counts its bytes on that CTA's barrier when it has
+// landed); a CTA whose barrier has counted all splits' bytes merges from its own memory, writes the result and leaves.  No scratch memory, no merge kernel, and no barrier of
 // the whole cluster at the end (one at the start, where nobody waits for it: the barriers must exist before anyone
 // arrives on them).
 // One head of the projection's sums through row scale, head norm and rotation: a lane holds elements lane + 32 i, so an
@@ -147,7 +147,14 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, DEC_WARPS); }
-        if (CL) mbar_init(merge_bar, (uint32_t)a.n_splits);
+        if (CL) {
+            // every split sends this CTA its values for this CTA's share of the output and the rows' maxima and sums
+            const int total = (a.nh / a.nkv) * HD, per = (total + a.n_splits - 1) / a.n_splits;
+            const int mine = min(total, (split + 1) * per) - min(total, split * per);
+            mbar_init(merge_bar, 1);
+            mbar_fence_init();
+            mbar_expect_tx(merge_bar, (uint32_t)(a.n_splits * (mine + 2 * (a.nh / a.nkv)) * sizeof(float)));
+        }
         mbar_fence_init();
     }
     __syncthreads();
@@ -403,10 +410,11 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
         if (CL) {
             // to the CTA that merges this element, into the row of this split; a row's maximum and sum of weights to all
             const int owner = idx / merge_per, e = idx - owner * merge_per;
-            tbtma::st_cluster_f32(tbtma::cluster_addr(recv + split * merge_stride + e, owner), acc);
+            tbtma::st_async_f32(tbtma::cluster_addr(recv + split * merge_stride + e, owner), acc, tbtma::cluster_addr(merge_bar, owner));
             if (d < a.n_splits) {      // the row's first n threads: one CTA of the cluster each
-                tbtma::st_cluster_f32(tbtma::cluster_addr(recv + split * merge_stride + merge_per + row, d), M);
-                tbtma::st_cluster_f32(tbtma::cluster_addr(recv + split * merge_stride + merge_per + 16 + row, d), L);
+                const uint32_t bar = tbtma::cluster_addr(merge_bar, d);
+                tbtma::st_async_f32(tbtma::cluster_addr(recv + split * merge_stride + merge_per + row, d), M, bar);
+                tbtma::st_async_f32(tbtma::cluster_addr(recv + split * merge_stride + merge_per + 16 + row, d), L, bar);
             }
         } else {
             float* part = a.scratch + ((size_t)(b * a.nh + kh * group + row) * a.n_splits + split) * (HD + 2);
@@ -417,14 +425,12 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     }       // compute warps
     if (CL) {
         // The splits of a (sequence, kv head) merge without a barrier of the cluster at the end: every CTA has SENT its
-        // part to the CTAs that merge it (above), tells each of them so on that CTA's barrier, waits until its own
-        // barrier has heard from every split, merges its share from its own shared memory and leaves.  Nobody reads
-        // this CTA's memory, and nobody writes to it after the last of the n arrivals it waits for.
+        // part to the CTAs that merge it (above), waits until its own barrier has counted the bytes of every split,
+        // merges its share from its own shared memory and leaves.  Nobody reads this CTA's memory, and nobody writes
+        // to it after the last of the bytes it waits for.
         tbtma::cluster_wait();                                      // every thread; completed long ago (see the arrival above)
         if (warp < DEC_WARPS) {
-            asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32)); // all of this CTA's parts are on their way
-            if ((int)threadIdx.x < a.n_splits) tbtma::mbar_arrive_cluster(tbtma::cluster_addr(merge_bar, threadIdx.x));
-            tbtma::mbar_wait_cluster(merge_bar, 0, &g_attn_error, 8);
+            tbtma::mbar_wait_cluster(merge_bar, 0, &g_attn_error, 8);      // every split's values have landed here
             if (FUSED && split == 0) {      // every split has sent its part, so it has read the queries' sums: clear them for the next step
                 float* qsum = a.acc + (size_t)b * a.acc_stride + (size_t)(kh * group) * HD;
                 for (int i = threadIdx.x; i < group * HD; i += DEC_WARPS * 32) qsum[i] = 0.f;

@@ -95,14 +95,18 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr_) {      /
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr_) : "memory");
     return v;
 }
-__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr_, float v) {      // into another CTA's shared memory
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr_), "f"(v) : "memory");
+// A value into another CTA's shared memory that counts its four bytes on a barrier of THAT CTA when it has landed:
+// the receiver expects the bytes of all its senders and needs no arrival after them.
+__device__ __forceinline__ void st_async_f32(uint32_t cluster_addr_, float v, uint32_t cluster_bar_addr) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];"
+                 ::"r"(cluster_addr_), "f"(v), "r"(cluster_bar_addr) : "memory");
 }
 // Split cluster barrier: every thread of the cluster arrives (does not block) and, later, waits.
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
-// A wait that also sees what other CTAs of the cluster wrote into this CTA's shared memory before they arrived
-// (mbar_arrive_cluster releases at cluster scope; this acquires at cluster scope).  Bounded like mbar_wait.
+// A wait that also sees what other CTAs of the cluster wrote into this CTA's shared memory (st_async_f32 counts its
+// bytes on the barrier; an arrival by mbar_arrive_cluster releases at cluster scope): it acquires at cluster scope.
+// Bounded like mbar_wait.
 __device__ __forceinline__ void mbar_wait_cluster(uint64_t* bar, uint32_t parity, unsigned int* error_word, unsigned code) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         uint32_t ok;
