@@ -407,7 +407,9 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
             acc += f * mo[(w * 16 + row) * HD + d];
             L += f * ml[w * 16 + row];
         }
-        if (CL) {
+        if (CL && a.n_splits == 1) {      // nothing to merge with: this is the result
+            a.out[(size_t)b * a.out_stride + (size_t)(kh * group + row) * HD + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        } else if (CL) {
             // to the CTA that merges this element, into the row of this split; a row's maximum and sum of weights to all
             const int owner = idx / merge_per, e = idx - owner * merge_per;
             tbtma::st_async_f32(tbtma::cluster_addr(recv + split * merge_stride + e, owner), acc, tbtma::cluster_addr(merge_bar, owner));
@@ -430,13 +432,13 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
         // to it after the last of the bytes it waits for.
         tbtma::cluster_wait();                                      // every thread; completed long ago (see the arrival above)
         if (warp < DEC_WARPS) {
-            tbtma::mbar_wait_cluster(merge_bar, 0, &g_attn_error, 8);      // every split's values have landed here
+            if (a.n_splits > 1) tbtma::mbar_wait_cluster(merge_bar, 0, &g_attn_error, 8);      // every split's values have landed here
             if (FUSED && split == 0) {      // every split has sent its part, so it has read the queries' sums: clear them for the next step
                 float* qsum = a.acc + (size_t)b * a.acc_stride + (size_t)(kh * group) * HD;
                 for (int i = threadIdx.x; i < group * HD; i += DEC_WARPS * 32) qsum[i] = 0.f;
             }
             const int n = a.n_splits, total = group * HD;
-            const int first = split * merge_per, last = min(total, first + merge_per);
+            const int first = split * merge_per, last = n > 1 ? min(total, first + merge_per) : 0;
             for (int idx = first + (int)threadIdx.x; idx < last; idx += DEC_WARPS * 32) {
                 const int row = idx / HD, d = idx % HD, e = idx - first;
                 float mr[16], lr[16], vr[16];
