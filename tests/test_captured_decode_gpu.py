@@ -134,7 +134,8 @@ def test_folded_norms_change_results_by_rounding_only(models, B):
     want = [P.forward_logits(cfg, w32, r)[n - 1:] for r, n in zip(reqs, lens)]
     launches = {}
     for fold in (True, False):
-        e = Engine.from_tensors(config_from_dict(cfg), w, dtype="bfloat16", max_tokens=B * 384, max_context=384, max_batch=B, fold_norms=fold)
+        e = Engine.from_tensors(config_from_dict(cfg), w, dtype="bfloat16", max_tokens=B * 384, max_context=384, max_batch=B, fold_norms=fold,
+                                fold_norms_rows=32)       # 20 rows too: the default folds up to 16
         before = K.launch_count
         got = teacher_forced(e, reqs, lens, 12)
         launches[fold] = K.launch_count - before + e.graph_launches

@@ -51,6 +51,7 @@ class EngineOptions:
     mark_freed_pages: bool = False    # debugging: pages of a freed slot are overwritten with a large finite value, so a stale read shows
     fold_head_norm: bool = True       # decode steps: head norm, rotation and cache append inside the attention kernel where it can take them
     fold_norms: bool = True           # decode steps: a norm goes into the product that consumes it where the kernels can take it
+    fold_norms_rows: int = 16         # ... in steps of up to this many rows (the kernels take up to 32; beyond 16 it was measured slower)
     early_pages: bool = True          # decode attention requests pages of older positions before it waits for the kernels before it
     decode_graphs: bool = True        # replay single-token steps as CUDA graphs once a batch size has run eagerly
     reproducible: bool = False        # bfloat16: partial sums along K add up in a fixed order, so the same requests in the same batches give the same bits on every run (slower)
@@ -82,6 +83,7 @@ class Engine:
         self.scratch: Dict[str, torch.Tensor] = {}
         self.step_options = {"gemm": options.gemm, "attention": options.attention, "attn_chunk": options.attn_chunk,
                              "early_pages": options.early_pages, "fold_norms": options.fold_norms, "fold_head_norm": options.fold_head_norm,
+                             "fold_norms_rows": options.fold_norms_rows,
                              "reproducible": options.reproducible,
                              "max_context": self.cache.max_context,
                              "sm_count": torch.cuda.get_device_properties(self.device).multi_processor_count}

@@ -46,17 +46,20 @@ def decode_split(lay, kv_heads: int, options, fast: bool):
     The any-size kernel takes splits of ``attn_chunk`` keys, as many as the longest sequence needs (an eager
     step) or as the context limit needs (a captured one, whose grid is fixed; the spare ones leave at once):
     the borders are multiples of ``attn_chunk`` either way.  The tensor-core kernel takes the number of splits
-    that fills the machine once at this batch size: two of its CTAs fit an SM, so (sequences x kv heads x
-    splits) stays within 2 x SMs; at most 16 splits merge inside a thread-block cluster (no scratch, no merge
-    kernel), and clusters of more than 8 CTAs only while they fill half of the machine (measured at 2,048 and
-    8,192 keys: 16 / 9 / 8 / 4 / 2 / 1 splits at batch 1 / 2 / 4 / 8 / 16 / 32 with 8 kv heads)."""
+    that fills the machine once at this batch size: two of its CTAs fit an SM, and (sequences x kv heads x splits)
+    stays within 7/8 of those 2 x SMs places, because the splits of a (sequence, kv head) are a thread-block cluster,
+    which is placed as a whole inside one part of the chip: with every place counted, some clusters wait for a
+    second round (measured after 2,048-token prompts: 5 sequences 3.28 -> 3.03 ms per step with 6 splits instead
+    of 7, 6 sequences 3.36 -> 3.09, 9 sequences 3.54 -> 3.29, 12 sequences 3.80 -> 3.50).  At most 16 splits merge
+    inside a cluster (no scratch, no merge kernel), and clusters of more than 8 CTAs only while they fill half of
+    the machine (16 / 9 / 8 / 4 / 2 / 1 splits at batch 1 / 2 / 4 / 8 / 16 / 32 with 8 kv heads)."""
     if not fast:
         chunk = int(options.get("attn_chunk", 256))
         cover = int(options.get("max_context", 0)) if options.get("fixed_splits") else 0
         return chunk, max(1, -(-(cover or lay.max_kv_len) // chunk))
     sms = int(options.get("sm_count", 148))
     pairs = lay.B * kv_heads
-    splits = max(1, min(16, 2 * sms // pairs))
+    splits = max(1, min(16, (2 * sms * 7 // 8) // pairs))
     if splits > 8:
         splits = max(8, min(splits, sms // pairs))
     forced = int(options.get("attn_splits", 0))
