@@ -387,6 +387,66 @@ def profile_case(kv=2048):
     return 0
 
 
+def timeline(batch, kv=2048):
+    """When the CTAs of every kernel of ONE captured decode step start, pass their wait for the kernel before, see
+    their first tile, finish and end (microseconds from the step's first record), for the first layers of the
+    benchmark's model; and the phases of the decode attention's CTAs.  Needs the tensor-core library built with the
+    timeline probe: TITAN_B200_NVCC_FLAGS=-DTB_TIMELINE python bench.py --timeline 1.  Prints text lines."""
+    import numpy as np
+    import torch
+
+    from titan_b200 import Engine, SamplerParams, kernels as K
+    from titan_b200.config import config_from_dict
+    engine = Engine.from_random(config_from_dict(dict(QWEN3_8B)), seed=2, dtype="bfloat16", max_tokens=batch * (kv + 256), max_context=8192,
+                                max_slots=batch, max_batch=batch)
+    records = 200000
+    buf = torch.zeros(1 + 8 * records, dtype=torch.int64, device="cuda")
+    if not K.timeline_attach(buf):
+        print("the kernels were built without the timeline probe: set TITAN_B200_NVCC_FLAGS=-DTB_TIMELINE and run again")
+        return 1
+    slots = [engine.alloc_slot() for _ in range(batch)]
+    engine.sampler.configure(slots, [SamplerParams.greedy()] * batch, list(range(batch)))
+    run_prompts(engine, slots, kv)
+    tokens = [1] * batch
+    for _ in range(6):                                   # the step is captured from the third one on
+        tokens = engine.advance(slots, tokens)
+    torch.cuda.synchronize()
+    buf.zero_()
+    torch.cuda.synchronize()
+    engine.advance(slots, tokens)                       # the one step that is recorded
+    torch.cuda.synchronize()
+    K.timeline_attach(None)
+    engine.check_kernels()
+    host = buf.cpu().numpy()
+    n = int(host[0])
+    rec = host[1:1 + 8 * min(n, records)].reshape(-1, 8)
+    launches = []                                       # a launch = the records of one tag, in the order of their starts, a grid at a time
+    for tag in np.unique(rec[:, 0]):
+        r = rec[rec[:, 0] == tag]
+        r = r[np.argsort(r[:, 2], kind="stable")]
+        per = (tag // 100) * (tag % 100) if tag < 100000 else int((r[:, 1] & 0xffffffff).max()) + 1
+        launches += [(int(tag), r[i:i + per]) for i in range(0, len(r), per)]
+    launches.sort(key=lambda x: x[1][:, 2].min())
+    base = launches[0][1][:, 2].min()
+    us = lambda v: (int(v) - int(base)) / 1e3
+    seen = lambda a: a[a > 0] if (a > 0).any() else np.array([base])
+    print(f"batch {batch}, {kv} cached tokens, {n} CTAs recorded in one captured step; times in us")
+    print("kernel (tiles x K slices | attention splits)  CTAs  start first..last  wait passed min..max  first tile min..max  last tile done min..max  end max")
+    for tag, r in launches:
+        t0, t1, t2, t3, t4 = (r[:, 2 + k] for k in range(5))
+        name = f"attention, {tag - 100000} splits" if tag >= 100000 else f"product {tag // 100} x {tag % 100}"
+        print(f"{name:26s} {len(r):5d}  {us(t0.min()):8.2f} {us(t0.max()):8.2f}   {us(seen(t1).min()):8.2f} {us(seen(t1).max()):8.2f}   "
+              f"{us(seen(t2).min()):8.2f} {us(seen(t2).max()):8.2f}   {us(seen(t3).min()):8.2f} {us(seen(t3).max()):8.2f}   {us(seen(t4).max()):8.2f}")
+        if tag >= 100000:
+            t5 = r[:, 7]
+            med = lambda a, b: float(np.median((a.astype(np.int64) - b.astype(np.int64))[(a > 0) & (b > 0)])) / 1e3 if ((a > 0) & (b > 0)).any() else float("nan")
+            print(f"    a CTA's phases (medians): start -> wait passed {med(t1, t0):.2f}, -> queries ready {med(t2, t1):.2f}, -> pages done {med(t3, t2):.2f}, "
+                  f"-> all parts here {med(t5, t3):.2f}, -> end {med(t4, t5 if (t5 > 0).any() else t3):.2f}")
+        if us(t0.min()) > 320:
+            break
+    return 0
+
+
 def micro():
     """Kernels of the benchmark's layer sizes timed alone with CUDA events (back to back, after warm-up);
     the figures that the summaries under profiles/ quote beside the ncu captures.  Prints text lines."""
@@ -496,11 +556,15 @@ def main():
     ap.add_argument("--config", type=int, default=3, choices=[3, 4, 5], help="3: the benchmark configuration (default); 4, 5: the Qwen3-4B and Qwen3-32B shaped ones")
     ap.add_argument("--profile-case", action="store_true", help="run the small one-layer case used for ncu captures and exit")
     ap.add_argument("--micro", action="store_true", help="time the layer's kernels alone (CUDA events) and exit; text lines, not the JSON line")
+    ap.add_argument("--timeline", type=int, default=0, metavar="BATCH", help="when the CTAs of one captured decode step's kernels start, wait and end "
+                    "(needs TITAN_B200_NVCC_FLAGS=-DTB_TIMELINE); text lines, not the JSON line")
     args = ap.parse_args()
     if args.profile_case:
         return profile_case(args.prompt_tokens)
     if args.micro:
         return micro()
+    if args.timeline:
+        return timeline(args.timeline, args.prompt_tokens)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "berniehans/titan is a Rust workspace (cargo is not installed) "
                           "that needs GGUF Q4_K weights and NVRTC for compute_86; it cannot be installed or run offline here"}))

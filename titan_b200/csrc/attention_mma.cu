@@ -20,6 +20,7 @@
 
 #include "attention_args.h"
 #include "common.cuh"
+#include "timeline.cuh"
 #include "tma.cuh"
 
 namespace {
@@ -128,6 +129,8 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x, kh = blockIdx.y, split = blockIdx.z;
+    TimelineProbe probe;              // stamps: 1 wait for the kernels before passed, 2 queries ready, 3 pages done, 5 all parts here, 4 end
+    probe.begin(100000 + gridDim.z, blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
     // The kernel after this one may start (and request its first weight tiles) while this one runs.  Those requests
     // would queue in front of this kernel's own pages, which at small batches are all that its time depends on, so
     // it lets the next kernel in only once its pages have been requested (the producer) and read (the compute warps).
@@ -161,6 +164,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     // CL: no CTA may send its part before every CTA of the cluster has its barrier; the arrival is here, the wait
     // where the parts are sent, long after the cluster's barrier has completed
     if (CL) tbtma::cluster_arrive();
+    probe.attach();
 
     if (warp == DEC_WARPS) {                            // ---------------- producer
         if (lane == 0) {
@@ -230,6 +234,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
         }
     }
     if (early) pdl_wait();
+    if (threadIdx.x == 0) probe.stamp(1);
     if (FUSED) {
         // every load first (the sums of this warp's first query head, of the new key and value, the row's parts):
         // they do not depend on one another, and at small batches this kernel is all latency
@@ -266,6 +271,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
             for (int i = 0; i < HD / 32; ++i) q_sh[h * HD + lane + 32 * i] = __float2bfloat16_rn(v[i]);
         }
         asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32));      // the group's queries are in shared memory
+        if (threadIdx.x == 0) probe.stamp(2);
         if (appends) {              // after the barrier: the other warps need not wait for the new key and value
             fused_head<HD>(rs, a.k_w != nullptr, kw, a.qk_eps, rotated, sn, cs, kn);
             __nv_bfloat16* kdst = a.storage + ((size_t)(new_page * a.nkv + kh) * PAGE + new_row) * HD;
@@ -377,6 +383,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     if (a.late_trigger) pdl_launch_dependents();
+    if (threadIdx.x == 0) probe.stamp(3);
 
     // ---------------- merge the four warps through shared memory (the stages are drained)
     asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32));      // compute warps only; the producer has left
@@ -433,6 +440,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
         tbtma::cluster_wait();                                      // every thread; completed long ago (see the arrival above)
         if (warp < DEC_WARPS) {
             if (a.n_splits > 1) tbtma::mbar_wait_cluster(merge_bar, 0, &g_attn_error, 8);      // every split's values have landed here
+            if (threadIdx.x == 0) probe.stamp(5);
             if (FUSED && split == 0) {      // every split has sent its part, so it has read the queries' sums: clear them for the next step
                 float* qsum = a.acc + (size_t)b * a.acc_stride + (size_t)(kh * group) * HD;
                 for (int i = threadIdx.x; i < group * HD; i += DEC_WARPS * 32) qsum[i] = 0.f;
@@ -463,6 +471,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
             }
         }
     }
+    if (threadIdx.x == 0) probe.stamp(4);
 }
 
 
@@ -846,3 +855,6 @@ extern "C" int tb_attn_prefill_mma(const AttnArgs* args, int source, cudaStream_
     TB_CHECK_LAUNCH("attn_prefill_mma");
     return 0;
 }
+
+// Names the buffer of the timeline probe (timeline.cuh); 1 if the library was built with it, 0 if not.
+TB_TIMELINE_SETTER(tb_attn_mma_timeline)

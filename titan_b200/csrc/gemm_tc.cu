@@ -40,6 +40,7 @@
 #include "common.cuh"
 #include "gemm.h"
 #include "tcgen05.cuh"
+#include "timeline.cuh"
 #include "tma.cuh"
 
 namespace {
@@ -285,6 +286,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int kb1 = min(kb_total, kb0 + a.k_blocks_per_split);
     const int n_kb = kb1 - kb0;
 
+    TimelineProbe probe;              // stamps: 1 wait for the kernel before passed, 2 first stage full, 3 last MMA done, 4 end, 5 last tile requested
+    probe.begin(gridDim.y * 100 + gridDim.z, blockIdx.y + gridDim.y * blockIdx.z);
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         // NORMED: a stage is full when the weights have landed (TMA) and a warp has written the activations
@@ -302,6 +305,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     constexpr uint32_t TX_BYTES = NORMED ? A_BYTES : A_BYTES + B_BYTES;
+    probe.attach();
 
     if (n_kb > 0) {
         if (warp == 0) {
@@ -316,6 +320,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     else tma_load_2d(smem_b + i * B_BYTES, &map_b, full + i, (kb0 + i) * BK, tile_b * BN);
                 }
                 pdl_wait();
+                probe.stamp(1);
                 for (int i = 0; i < pre; ++i) {
                     if (NORMED) continue;
                     if (SWAP) tma_load_2d(smem_b + i * B_BYTES, &map_b, full + i, (kb0 + i) * BK, tile_b * BN);
@@ -329,6 +334,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     else tma_load_2d(smem_a + s * A_BYTES, &map_a, full + s, (kb0 + i) * BK, tile_a * BM);
                     if (!NORMED) tma_load_2d(smem_b + s * B_BYTES, &map_b, full + s, (kb0 + i) * BK, tile_b * BN);
                 }
+                probe.stamp(5);
             }
         } else if (warp == 1) {
             if (lane == 0) {
@@ -337,6 +343,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int i = 0; i < n_kb; ++i) {
                     const int s = i % STAGES, round = i / STAGES;
                     mbar_wait(full + s, round & 1, 2);
+                    if (i == 0) probe.stamp(2);
                     tc_fence_after();
                     const uint64_t da = smem_desc(smem_u32(smem_a + s * A_BYTES));
                     const uint64_t db = smem_desc(smem_u32(smem_b + s * B_BYTES));
@@ -427,6 +434,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 asm volatile("bar.sync 2, 128;" ::: "memory");
             }
             mbar_wait(accum, 0, 3);
+            if (threadIdx.x == 64) probe.stamp(3);
             tc_fence_after();
             const int quarter = warp & 3;                     // a warp reads TMEM lanes 32 * (warp % 4) ..
             const int row = tile_a * BM + quarter * 32 + lane;
@@ -470,6 +478,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
     }
+    if (threadIdx.x == 0) probe.stamp(4);
     if (ORDERED) {
         // every thread of every CTA of the cluster: parts written -> summed -> may leave
         __syncwarp();
@@ -1193,3 +1202,6 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
     TB_CHECK_LAUNCH("gemm_tc");
     return 0;
 }
+
+// Names the buffer of the timeline probe (timeline.cuh); 1 if the library was built with it, 0 if not.
+TB_TIMELINE_SETTER(tb_gemm_tc_timeline)

@@ -40,6 +40,16 @@ class KernelError(RuntimeError):
     pass
 
 
+def timeline_attach(buffer: Optional[torch.Tensor]) -> bool:
+    """Names the buffer (int64, 1 + 8 * records) in which the decode kernels' timeline probe keeps its records, or
+    takes it away (None).  False if the tensor-core library was built without the probe (csrc/timeline.cuh: it is
+    compiled in with TITAN_B200_NVCC_FLAGS=-DTB_TIMELINE and costs nothing otherwise)."""
+    lib_ = tlib()
+    ptr = None if buffer is None else buffer.data_ptr()
+    on = [int(f(c_void_p(ptr))) for f in (lib_.tb_gemm_tc_timeline, lib_.tb_attn_mma_timeline)]
+    return all(v == 1 for v in on)
+
+
 class KvView(Structure):
     _fields_ = [("storage", c_void_p), ("table", c_void_p), ("table_width", c_int), ("ring_rows", c_int),
                 ("page_size", c_int), ("num_pages", c_int), ("kv_heads", c_int), ("head_dim", c_int)]
