@@ -420,6 +420,8 @@ def timeline(batch, kv=2048):
     host = buf.cpu().numpy()
     n = int(host[0])
     rec = host[1:1 + 8 * min(n, records)].reshape(-1, 8)
+    if os.environ.get("TITAN_B200_TIMELINE_RAW"):        # the records themselves, for a closer look: tag, block | sm << 32, six stamps (ns)
+        np.save(os.environ["TITAN_B200_TIMELINE_RAW"], rec)
     launches = []                                       # a launch = the records of one tag, in the order of their starts, a grid at a time
     for tag in np.unique(rec[:, 0]):
         r = rec[rec[:, 0] == tag]
