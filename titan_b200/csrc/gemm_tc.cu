@@ -255,6 +255,68 @@ __device__ __forceinline__ void epilogue_rows(const float* val, float* tile, con
     }
 }
 
+// Swap mode: the tile as the epilogue warps have left it in shared memory, ``part`` [token][row of the tile = output
+// column], goes out along the output's rows: a thread takes four neighbouring columns of a token (sixteen for SwiGLU:
+// eight outputs), so a warp writes 512 contiguous bytes with one instruction where a thread that holds one column of
+// every token needs an instruction per token (64 rows: 3.2 us of scalar reductions per CTA, 5 us of 2-byte stores).
+template <int BN, int EPI>
+__device__ __forceinline__ void swap_tile_out(const float* part, const TcArgs& a, int tile_a, int t) {
+    if (EPI == TB_EPI_SWIGLU) {
+        for (int item = t; item < BN * 8; item += 128) {
+            const int m = item >> 3, n0 = tile_a * BM + (item & 7) * 16;
+            if (m >= a.rows_b || n0 >= a.rows_a) continue;
+            const float4* p = reinterpret_cast<const float4*>(part + m * BM + (item & 7) * 16);
+            const float4 f0 = p[0], f1 = p[1], f2 = p[2], f3 = p[3];
+            __nv_bfloat16* o = (__nv_bfloat16*)a.out + (size_t)m * a.ldo + n0 / 2;
+            if (n0 + 16 <= a.rows_a) {
+                uint4 pk;
+                pk.x = pack_bf16(silu_mul(f0.x, f0.y), silu_mul(f0.z, f0.w)); pk.y = pack_bf16(silu_mul(f1.x, f1.y), silu_mul(f1.z, f1.w));
+                pk.z = pack_bf16(silu_mul(f2.x, f2.y), silu_mul(f2.z, f2.w)); pk.w = pack_bf16(silu_mul(f3.x, f3.y), silu_mul(f3.z, f3.w));
+                *reinterpret_cast<uint4*>(o) = pk;
+            } else {
+                const float v[16] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w, f2.x, f2.y, f2.z, f2.w, f3.x, f3.y, f3.z, f3.w};
+                for (int j = 0; j < 16; j += 2)
+                    if (n0 + j + 1 < a.rows_a) o[j / 2] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+            }
+        }
+    } else {
+        for (int item = t; item < BN * 32; item += 128) {
+            const int m = item >> 5, n0 = tile_a * BM + (item & 31) * 4;
+            if (m >= a.rows_b || n0 >= a.rows_a) continue;
+            const float4 f = *reinterpret_cast<const float4*>(part + m * BM + (item & 31) * 4);
+            const bool whole = n0 + 4 <= a.rows_a;
+            if (EPI == TB_EPI_STORE) {
+                __nv_bfloat16* o = (__nv_bfloat16*)a.out + (size_t)m * a.ldo + n0;
+                if (whole) {
+                    *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(f.x, f.y), pack_bf16(f.z, f.w));
+                } else {
+                    const float v[4] = {f.x, f.y, f.z, f.w};
+                    for (int j = 0; j < 4; ++j) if (n0 + j < a.rows_a) o[j] = __float2bfloat16_rn(v[j]);
+                }
+            } else {
+                float* o = (float*)a.out + (size_t)m * a.ldo + n0;
+                if (whole && EPI == TB_EPI_F32) {
+                    *reinterpret_cast<float4*>(o) = f;
+                } else if (whole && a.atomic) {
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(f.x), "f"(f.y), "f"(f.z), "f"(f.w) : "memory");
+                } else if (whole) {
+                    float4 old = *reinterpret_cast<const float4*>(o);
+                    old.x += f.x; old.y += f.y; old.z += f.z; old.w += f.w;
+                    *reinterpret_cast<float4*>(o) = old;
+                } else {
+                    const float v[4] = {f.x, f.y, f.z, f.w};
+                    for (int j = 0; j < 4; ++j) {
+                        if (n0 + j >= a.rows_a) continue;
+                        if (EPI == TB_EPI_F32) o[j] = v[j];
+                        else if (a.atomic) atomicAdd(o + j, v[j]);
+                        else o[j] += v[j];
+                    }
+                }
+            }
+        }
+    }
+}
+
 // ORDERED (swap mode, ADD epilogue): the K slices of a tile are the CTAs of one thread-block cluster.  Each leaves its
 // partial tile in its own shared memory; after a cluster barrier every CTA adds up a share of the tile's elements
 // from all slices, in slice order, through distributed shared memory, and adds the sum to the output.  An element is
@@ -448,7 +510,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] *= norm_sh[4 * BN + c + j];
                     }
-                    if (ORDERED) {
+                    if (SWAP) {         // the ring has drained: its first bytes hold the tile, [token][row of the tile]
 #pragma unroll
                         for (int j = 0; j < 32; ++j) reinterpret_cast<float*>(smem_a)[(c + j) * BM + quarter * 32 + lane] = v[j];
                     } else {
@@ -462,12 +524,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] *= norm_sh[4 * BN + j];
                 }
-                if (ORDERED) {      // the ring has drained: its first bytes hold this slice's part, [token][row of the tile]
+                if (SWAP) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) reinterpret_cast<float*>(smem_a)[j * BM + quarter * 32 + lane] = v[j];
                 } else {
                     epilogue_chunk<EPI, SWAP, 16>(v, a, row, tile_b * BN, lane);
                 }
+            }
+            if (SWAP && !ORDERED) {
+                asm volatile("bar.sync 2, 128;" ::: "memory");         // the four epilogue warps: the tile is whole
+                swap_tile_out<BN, EPI>(reinterpret_cast<const float*>(smem_a), a, tile_a, (int)threadIdx.x - 64);
             }
         }
     }
