@@ -46,7 +46,7 @@ def teacher_forced(engine, reqs, prompt_lens, steps):
     return [torch.cat(r).float().cpu() for r in rows]
 
 
-@pytest.mark.parametrize("variant", ["default", "lengths after the wait", "merge through scratch"])
+@pytest.mark.parametrize("variant", ["default", "lengths after the wait", "merge through scratch", "next kernel let in at once"])
 @pytest.mark.parametrize("B", [1, 3, 8])
 @pytest.mark.parametrize("model", ["hd128", "hd64"])
 def test_captured_decode_steps_against_the_plain_implementation(models, model, B, variant):
@@ -60,6 +60,7 @@ def test_captured_decode_steps_against_the_plain_implementation(models, model, B
     if variant == "lengths after the wait":
         kw["early_pages"] = False
     K.set_attn_decode_cluster(variant != "merge through scratch")
+    K.set_attn_decode_late_trigger(variant != "next kernel let in at once")
     try:
         graph = Engine.from_tensors(config_from_dict(cfg), w, decode_graphs=True, **kw)
         got = teacher_forced(graph, reqs, lens, STEPS)
@@ -75,6 +76,7 @@ def test_captured_decode_steps_against_the_plain_implementation(models, model, B
                 rows_close(got[i], plain_steps[i], "bfloat16", f"{model}, batch {B}, request {i} (captured against eager)")
     finally:
         K.set_attn_decode_cluster(True)
+        K.set_attn_decode_late_trigger(True)
 
 
 @pytest.mark.parametrize("model", ["hd128", "hd64"])

@@ -310,9 +310,15 @@ def attn_decode_mma(args: AttnArgs, stream: int) -> None:
 
 
 def set_attn_decode_cluster(on: bool) -> None:
-    """Decode attention with up to 8 splits: merge them inside a thread-block cluster (on by default) or through
+    """Decode attention with up to 16 splits: merge them inside a thread-block cluster (on by default) or through
     scratch memory and the merge kernel."""
     tlib().tb_attn_decode_set_cluster(int(bool(on)))
+
+
+def set_attn_decode_late_trigger(on: bool) -> None:
+    """Decode attention lets the kernel after it start once its own pages have been requested and read (on by
+    default), or at once: the next kernel's first weight requests then queue in front of the pages."""
+    tlib().tb_attn_decode_set_late_trigger(int(bool(on)))
 
 
 # Where the tensor-core prompt kernels take keys and values from: nowhere they can (0), the step's own rows (every
