@@ -73,14 +73,21 @@ template <typename T, bool VEC>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
                                const int* __restrict__ rows, int H, float eps) {
     pdl_launch_dependents();
-    pdl_wait();
     __shared__ float red[33];
     const int r = blockIdx.x;
-    const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
     T* yr = y + (size_t)r * H;
     if (VEC) {
-        float4 v[4];
+        float4 v[4], ww[4];
         const int n4 = H >> 2;
+        // the norm's weight depends on nothing that the kernel before makes: requested while the wait for it lasts
+        // (it used to be a round trip of its own after the row's sum)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            ww[j] = i < n4 ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        pdl_wait();
+        const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
         float ss = 0.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -93,12 +100,12 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int i = threadIdx.x + j * blockDim.x;
-            if (i < n4) {
-                const float4 ww = reinterpret_cast<const float4*>(w)[i];
-                store4<T>(yr + 4 * i, v[j].x * scale * ww.x, v[j].y * scale * ww.y, v[j].z * scale * ww.z, v[j].w * scale * ww.w);
-            }
+            if (i < n4)
+                store4<T>(yr + 4 * i, v[j].x * scale * ww[j].x, v[j].y * scale * ww[j].y, v[j].z * scale * ww[j].z, v[j].w * scale * ww[j].w);
         }
     } else {
+        pdl_wait();
+        const float* xr = x + (size_t)(rows ? rows[r] : r) * H;
         float ss = 0.f;
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
             const float v = xr[i];
