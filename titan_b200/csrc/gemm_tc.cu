@@ -118,11 +118,10 @@ template <int BN, bool SWAP, int STAGES = stages_for<BN>()> constexpr size_t sme
            (SWAP ? 0 : 4 * EPI_TILE_FLOATS * sizeof(float));
 }
 
-// Epilogue of one 32-column chunk held by one thread (row ``r`` of the tile).
-// Plain mode: row = token m, columns = outputs n0 + j.   Swap mode: row = output n, columns = tokens.
-template <int EPI, bool SWAP, int NV>
+// Plain mode: the epilogue of one 32-column chunk held by one thread (row = token m, columns = outputs col0 + j).
+template <int EPI, int NV>
 __device__ __forceinline__ void epilogue_chunk(const float* v, const TcArgs& a, int row, int col0, int lane) {
-    if (!SWAP) {
+    {
         const int m = row;
         if (m >= a.rows_a) return;
         if (EPI == TB_EPI_SWIGLU) {
@@ -179,23 +178,6 @@ __device__ __forceinline__ void epilogue_chunk(const float* v, const TcArgs& a, 
                     else if (a.atomic) atomicAdd(o + j, v[j]);
                     else o[j] += v[j];
                 }
-            }
-        }
-    } else {
-        const int n = row;
-        const bool n_ok = n < a.rows_a;
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const int m = col0 + j;
-            if (EPI == TB_EPI_SWIGLU) {
-                const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);      // the odd lane holds the pair's up value
-                if (m < a.rows_b && n_ok && !(lane & 1))
-                    ((__nv_bfloat16*)a.out)[(size_t)m * a.ldo + n / 2] = __float2bfloat16_rn(silu_mul(v[j], up));
-            } else if (m < a.rows_b && n_ok) {
-                if (EPI == TB_EPI_STORE) ((__nv_bfloat16*)a.out)[(size_t)m * a.ldo + n] = __float2bfloat16_rn(v[j]);
-                else if (EPI == TB_EPI_F32) ((float*)a.out)[(size_t)m * a.ldo + n] = v[j];
-                else if (a.atomic) atomicAdd((float*)a.out + (size_t)m * a.ldo + n, v[j]);
-                else ((float*)a.out)[(size_t)m * a.ldo + n] += v[j];
             }
         }
     }
@@ -326,7 +308,8 @@ template <int BN, int EPI, bool SWAP, bool NORMED = false, bool ORDERED = false>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs a) {
     static_assert(!NORMED || (SWAP && BN <= 32), "the folded norm is for decode tiles (swap mode, at most 32 rows of activations)");
-    static_assert(!ORDERED || (SWAP && EPI == TB_EPI_ADD), "slices in a fixed order: swap mode with the ADD epilogue");
+    static_assert(SWAP, "this kernel takes the decode products (weights on the 128-row side); prompts have the persistent and the pair kernel");
+    static_assert(!ORDERED || EPI == TB_EPI_ADD, "slices in a fixed order: the ADD epilogue");
     constexpr int STAGES = stages_of<BN, EPI, SWAP>();
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     constexpr uint32_t TMEM_COLS = tmem_cols_for<BN>();
@@ -499,7 +482,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (threadIdx.x == 64) probe.stamp(3);
             tc_fence_after();
             const int quarter = warp & 3;                     // a warp reads TMEM lanes 32 * (warp % 4) ..
-            const int row = tile_a * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16);
             if (BN >= 32) {
 #pragma unroll 1
@@ -510,12 +492,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] *= norm_sh[4 * BN + c + j];
                     }
-                    if (SWAP) {         // the ring has drained: its first bytes hold the tile, [token][row of the tile]
+                    // the ring has drained: its first bytes hold the tile, [token][row of the tile]
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) reinterpret_cast<float*>(smem_a)[(c + j) * BM + quarter * 32 + lane] = v[j];
-                    } else {
-                        epilogue_chunk<EPI, SWAP, 32>(v, a, row, tile_b * BN + c, lane);
-                    }
+                    for (int j = 0; j < 32; ++j) reinterpret_cast<float*>(smem_a)[(c + j) * BM + quarter * 32 + lane] = v[j];
                 }
             } else {
                 float v[16];
@@ -524,14 +503,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] *= norm_sh[4 * BN + j];
                 }
-                if (SWAP) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) reinterpret_cast<float*>(smem_a)[j * BM + quarter * 32 + lane] = v[j];
-                } else {
-                    epilogue_chunk<EPI, SWAP, 16>(v, a, row, tile_b * BN, lane);
-                }
+                for (int j = 0; j < 16; ++j) reinterpret_cast<float*>(smem_a)[j * BM + quarter * 32 + lane] = v[j];
             }
-            if (SWAP && !ORDERED) {
+            if (!ORDERED) {
                 asm volatile("bar.sync 2, 128;" ::: "memory");         // the four epilogue warps: the tile is whole
                 swap_tile_out<BN, EPI>(reinterpret_cast<const float*>(smem_a), a, tile_a, (int)threadIdx.x - 64);
             }
@@ -733,7 +708,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                 for (int c = 0; c < BN; c += 32) {
                     float v[32];
                     tmem_ld32(taddr + c, v);
-                    epilogue_chunk<EPI, false, 32>(v, a, row, tile_b * BN + c, lane);
+                    epilogue_chunk<EPI, 32>(v, a, row, tile_b * BN + c, lane);
                 }
             }
             tc_fence_before();
@@ -864,7 +839,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 float v[32];
                 tmem_ld32(taddr + c, v);
                 if (EPI == TB_EPI_ADD) epilogue_rows<EPI>(v, tile, a, row0, tile_b * PAIR_N + c, a.rows_b, lane, true);
-                else epilogue_chunk<EPI, false, 32>(v, a, row0 + lane, tile_b * PAIR_N + c, lane);
+                else epilogue_chunk<EPI, 32>(v, a, row0 + lane, tile_b * PAIR_N + c, lane);
             }
             tc_fence_before();
             __syncwarp();
