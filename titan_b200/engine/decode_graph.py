@@ -44,6 +44,7 @@ class DecodeGraph:
         self.logits: Dict[tuple, torch.Tensor] = {}    # per captured graph: the step's logits [B, vocab], valid until its next replay
         self.host_tokens = torch.zeros(B, dtype=torch.int32).pin_memory()
         self.host_slots = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self.host_out = torch.zeros(B, dtype=torch.int32).pin_memory()      # the step's sampled tokens, read by the host
 
     @property
     def engine(self):

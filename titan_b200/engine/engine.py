@@ -229,9 +229,10 @@ class Engine:
         self._replay(g, False)
         for s in slots:
             self.cache.commit(s, self.cache.length[s] + 1)
-        host = g.out_tokens.cpu()
+        g.host_out.copy_(g.out_tokens, non_blocking=True)       # into pinned memory, then one wait for the stream
+        torch.cuda.current_stream(self.device).synchronize()
         self.d2h_bytes += 4 * B
-        return host.tolist()
+        return g.host_out.tolist()
 
     def decode_on_device(self, slots, steps: int, keep_all: bool = False) -> torch.Tensor:
         """``steps`` decode steps without the host in the loop: every step feeds each sequence the
