@@ -43,6 +43,7 @@ class DecodeGraph:
         self.launches = 0                      # launcher calls inside one replay
         self.logits: Dict[tuple, torch.Tensor] = {}    # per captured graph: the step's logits [B, vocab], valid until its next replay
         self.host_tokens = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self.host_tokens_view = self.host_tokens.numpy()
         self.host_slots = torch.zeros(B, dtype=torch.int32).pin_memory()
         self.host_out = torch.zeros(B, dtype=torch.int32).pin_memory()      # the step's sampled tokens, read by the host
 

@@ -18,6 +18,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from .. import kernels as K
@@ -219,10 +220,11 @@ class Engine:
             return self._step_and_sample([StepEntry(s, [t], [0]) for s, t in zip(slots, tokens)])
         g = self._prepare_graph_step(slots, 1)
         V = self.spec.vocab_size
-        for i, t in enumerate(tokens):
-            if not 0 <= int(t) < V:
-                raise StepError(f"token id {t} lies outside the vocabulary of {V}")
-            g.host_tokens[i] = int(t)
+        ids = np.asarray(tokens, dtype=np.int64)
+        if ids.shape != (B,) or int(ids.min()) < 0 or int(ids.max()) >= V:
+            bad = [int(t) for t in np.ravel(ids) if not 0 <= int(t) < V]
+            raise StepError(f"token id {bad[0]} lies outside the vocabulary of {V}" if bad else f"{ids.size} tokens for {B} sequences")
+        g.host_tokens_view[:] = ids                      # the pinned buffer, as numpy sees it
         g.tokens.copy_(g.host_tokens, non_blocking=True)
         self.h2d_bytes += 4 * B
         self.steps_run += 1
@@ -253,6 +255,16 @@ class Engine:
         return history if keep_all else g.out_tokens
 
     def _prepare_graph_step(self, slots, steps: int) -> "DecodeGraph":
+        g = self._graphs.get(len(slots))
+        if steps == 1 and g is not None and g.slots == list(slots):
+            # The sequences of the step before, which were checked then: a sequence whose length is inside a page needs
+            # no new page for one more token (the host's share of a step at batch 64 is mostly these loops).
+            length, page, limit = self.cache.length, self.cache.page_size, self.cache.max_context
+            try:
+                if all(length[s] % page and length[s] < limit for s in slots):
+                    return g
+            except KeyError:
+                pass                                      # a slot was given back since: the checks below say so
         seen = set()
         for s in slots:
             if not self.cache.is_live(s) or s in seen:
