@@ -205,3 +205,20 @@ def test_k_slices_added_in_a_fixed_order_give_the_same_bits_every_time(K, M, N, 
         assert rel_l2(runs[0][0].cpu() * scale[:, None], P.linear(P.rms_norm(xf.cpu(), nw.cpu(), 1e-6), w.float().cpu())) < 6e-3
         for acc, parts in runs[1:]:
             assert torch.equal(acc, runs[0][0]) and torch.equal(parts, runs[0][1])
+
+
+def test_the_timeline_probe_is_absent_from_the_default_build(K):
+    """The decode kernels' timeline probe costs nothing unless the library is built with -DTB_TIMELINE: the default
+    build says so when a buffer is offered, and runs on as before."""
+    import os
+    buf = torch.zeros(1 + 8 * 16, dtype=torch.int64, device="cuda")
+    built_in = "TB_TIMELINE" in os.environ.get("TITAN_B200_NVCC_FLAGS", "")
+    assert K.timeline_attach(buf) == built_in
+    x = torch.randn(4, 256).to(torch.bfloat16).cuda()
+    w = torch.randn(128, 256).to(torch.bfloat16).cuda()
+    out = torch.zeros(4, 128, device="cuda")
+    K.gemm_tc(x, w, out, K.EPI_F32, stream())
+    torch.cuda.synchronize()
+    assert K.gemm_tc_error() == 0 and rel_l2(out.cpu(), P.linear(x.float().cpu(), w.float().cpu())) < 1e-5
+    assert int(buf[0]) == (1 if built_in else 0)          # one CTA's record, or nothing
+    K.timeline_attach(None)
