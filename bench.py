@@ -6,8 +6,8 @@
 Prints ONE JSON line.  The workload is the benchmark configuration's: sequences that hold 2,048-token
 prompts in a context of 8,192, decoded one token each per step.  ``value`` is decoded tokens per second at
 batch 8 (device time, CUDA events around K replays of the captured decode step that start with 2,048 tokens in
-the cache, each step feeding the token the step before sampled); ``e2e`` is K further steps through the Python
-entry point with host tokens in and out every step (wall clock); ``prefill`` is one
+the cache, each step feeding the token the step before sampled); ``e2e`` is the same K steps, from the same
+prompts run again, through the Python entry point with host tokens in and out every step (wall clock); ``prefill`` is one
 2,048-token prompt; ``roofline`` divides the bytes a decode step has to read (every weight once, the
 live cache) by its time.  ``points`` holds the whole stated run, 256 steps from 2,048 cached tokens, at
 batch 1, 8 and 64 (tokens per second, with ``_ms`` per step and ``_frac`` of the copy bandwidth beside
@@ -127,17 +127,39 @@ def prefill_flops(cfg, layers, T):
 def time_decode(engine, torch, K, batch, kv_timed, steps, warmup, end_to_end=True):
     """``steps`` timed decode steps of ``batch`` sequences whose caches hold ``kv_timed`` tokens when the first
     timed step begins: prompts of ``kv_timed - warmup`` tokens are run, then ``warmup`` untimed steps.  The steps
-    are timed twice: on the device alone (``Engine.decode_on_device``: the captured step replayed ``steps`` times,
-    every step feeding the token that the step before sampled; CUDA events), and then, ``steps`` further steps, end
-    to end through ``Engine.advance`` (host token ids in, sampled host token ids out, every step; wall clock).
+    are timed twice, each time from freshly run prompts: on the device alone (``Engine.decode_on_device``: the
+    captured step replayed ``steps`` times, every step feeding the token that the step before sampled; CUDA events),
+    and end to end through ``Engine.advance`` (host token ids in, sampled host token ids out, every step; wall clock).
     Returns (device ms per step, end-to-end ms per step or None, launcher calls in the device-timed steps, bytes
     copied to and from the device per end-to-end step)."""
     from titan_b200 import SamplerParams
-    slots = [engine.alloc_slot() for _ in range(batch)]
-    try:
+
+    def started():
+        slots = [engine.alloc_slot() for _ in range(batch)]
         engine.sampler.configure(slots, [SamplerParams.greedy()] * batch, list(range(batch)))
         run_prompts(engine, slots, kv_timed - warmup)
         tokens = [(7 * i + 1) % engine.vocab_size for i in range(batch)]
+        return slots, tokens
+
+    wall_ms, h2d, d2h = None, 0, 0
+    if end_to_end:                                       # first: it is the number that a user sees
+        slots, tokens = started()
+        try:
+            for _ in range(warmup):
+                tokens = engine.advance(slots, tokens)
+            h2d0, d2h0 = engine.h2d_bytes, engine.d2h_bytes
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                tokens = engine.advance(slots, tokens)   # host token ids in, sampled host token ids out
+            torch.cuda.synchronize()
+            wall_ms = (time.perf_counter() - t0) * 1e3 / steps
+            h2d, d2h = (engine.h2d_bytes - h2d0) // steps, (engine.d2h_bytes - d2h0) // steps
+        finally:
+            for s in slots:
+                engine.free_slot(s)
+    slots, tokens = started()
+    try:
         for _ in range(max(1, warmup - 2)):
             tokens = engine.advance(slots, tokens)
         engine.decode_on_device(slots, warmup - max(1, warmup - 2))     # the last warm-up steps: the replayed graph itself
@@ -145,22 +167,11 @@ def time_decode(engine, torch, K, batch, kv_timed, steps, warmup, end_to_end=Tru
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches0 = K.launch_count + engine.graph_launches
         start.record()
-        last = engine.decode_on_device(slots, steps)
+        engine.decode_on_device(slots, steps)
         stop.record()
         torch.cuda.synchronize()
         dev_ms = start.elapsed_time(stop) / steps
-        launches = K.launch_count + engine.graph_launches - launches0
-        if not end_to_end:
-            return dev_ms, None, launches, 0, 0
-        tokens = [int(t) for t in last.cpu().tolist()]
-        h2d0, d2h0 = engine.h2d_bytes, engine.d2h_bytes
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(steps):
-            tokens = engine.advance(slots, tokens)       # host token ids in, sampled host token ids out
-        torch.cuda.synchronize()
-        wall_ms = (time.perf_counter() - t0) * 1e3 / steps
-        return dev_ms, wall_ms, launches, (engine.h2d_bytes - h2d0) // steps, (engine.d2h_bytes - d2h0) // steps
+        return dev_ms, wall_ms, K.launch_count + engine.graph_launches - launches0, h2d, d2h
     finally:
         for s in slots:
             engine.free_slot(s)
@@ -199,7 +210,7 @@ def run_ours(args):
     context, B, kv0 = args.context, args.batch, args.prompt_tokens
     point_steps = 0 if args.skip_points else args.point_steps
     biggest = max(B, 1 if args.skip_points else 64)
-    room = max(biggest * (kv0 + 2 * max(args.steps, point_steps) + 64), 8 * context if not args.skip_points else 0)
+    room = max(biggest * (kv0 + max(args.steps, point_steps) + 64), 8 * context if not args.skip_points else 0)
     engine = Engine.from_random(config_from_dict(cfg), seed=2, dtype="bfloat16", max_tokens=room,
                                 max_context=context, max_slots=biggest, max_batch=biggest)
     hbm = pk["hbm_gbs"]
