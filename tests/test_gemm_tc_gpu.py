@@ -200,7 +200,8 @@ def test_k_slices_added_in_a_fixed_order_give_the_same_bits_every_time(K, M, N, 
             K.gemm_tc_normed(xf, nw, 1e-6, w, acc, K.EPI_ADD, stream(), sumsq=parts, ordered=True)
             runs.append((acc.clone(), parts.clone()))
         assert K.gemm_tc_error() == 0
-        n_parts = K.gemm_tc_normed_slices(w, K.EPI_ADD)
+        n_parts = K.gemm_tc_normed_slices(w, K.EPI_ADD, M, ordered=True)
+        assert 1 <= n_parts <= K.gemm_tc_normed_slices(w, K.EPI_ADD, M)
         scale = 1.0 / torch.sqrt(runs[0][1][:n_parts, :M].sum(0).cpu() / Kd + 1e-6)
         assert rel_l2(runs[0][0].cpu() * scale[:, None], P.linear(P.rms_norm(xf.cpu(), nw.cpu(), 1e-6), w.float().cpu())) < 6e-3
         for acc, parts in runs[1:]:

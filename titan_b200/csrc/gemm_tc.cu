@@ -901,39 +901,46 @@ int launch_tc_ordered(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs
     TB_REQUIRE(e == cudaSuccess, "gemm_tc: the launch of clusters of %d K slices failed: %s", (int)grid.z, cudaGetErrorString(e));
     return 0;
 }
-// The most K slices that one cluster of this kernel can hold on this device: 16 where the non-portable size is
-// allowed and can be placed, else 8, else 1 (no slices).
+// How many clusters of ``size`` CTAs of this kernel the device holds at once (0: it places none).  Clusters are placed
+// as wholes inside one part of the chip, so this is less than the CTAs it holds divided by the size.
 template <int BN, bool NORMED>
-int ordered_limit() {
-    static int limit = -1;
-    if (limit < 0) {
-        limit = 1;
+int ordered_clusters(int size) {
+    static int cached[17];
+    static bool known[17] = {false};
+    if (size < 1 || size > 16) return 0;
+    if (!known[size]) {
         constexpr size_t smem = smem_for<BN, true, stages_of<BN, TB_EPI_ADD, true>()>();
         auto kernel = gemm_tc_kernel<BN, TB_EPI_ADD, true, NORMED, true>;
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-        for (int size : {16, 8}) {
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3(1, 1, size); cfg.blockDim = dim3(THREADS, 1, 1); cfg.dynamicSmemBytes = smem;
-            cudaLaunchAttribute attr[1];
-            attr[0].id = cudaLaunchAttributeClusterDimension;
-            attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)size;
-            cfg.attrs = attr; cfg.numAttrs = 1;
-            int clusters = 0;
-            if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) == cudaSuccess && clusters > 0) { limit = size; break; }
-            cudaGetLastError();
-        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, 1, size); cfg.blockDim = dim3(THREADS, 1, 1); cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)size;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess) { clusters = 0; cudaGetLastError(); }
+        cached[size] = clusters; known[size] = true;
     }
-    return limit;
+    return cached[size];
 }
-int ordered_limit_for(int bn, bool normed) {
-    if (normed) return bn == 16 ? ordered_limit<16, true>() : ordered_limit<32, true>();
+int ordered_clusters_for(int bn, bool normed, int size) {
+    if (normed) return bn == 16 ? ordered_clusters<16, true>(size) : ordered_clusters<32, true>(size);
     switch (bn) {
-        case 16: return ordered_limit<16, false>();
-        case 32: return ordered_limit<32, false>();
-        case 64: return ordered_limit<64, false>();
+        case 16: return ordered_clusters<16, false>(size);
+        case 32: return ordered_clusters<32, false>(size);
+        case 64: return ordered_clusters<64, false>(size);
     }
-    return ordered_limit<128, false>();
+    return ordered_clusters<128, false>(size);
+}
+// The most K slices, at most ``wanted``, with which the clusters of all ``tiles`` tiles are held at once (a cluster
+// that waits for a second round costs more than the slices gain); 1: no slices.
+int ordered_fit(int bn, bool normed, int tiles, int wanted) {
+    for (int size = wanted > 16 ? 16 : wanted; size > 1; --size)
+        if (ordered_clusters_for(bn, normed, size) >= tiles) return size;
+    return 1;
 }
 
 template <int BN, int EPI>
@@ -1073,7 +1080,7 @@ extern "C" int tb_gemm_tc_normed_check(int M, int N, int K, int ldxf, int ldo, i
 }
 
 // K slices of tb_gemm_tc_normed with the ADD epilogue for these sizes: as many as fill the machine once, four blocks each at least.
-static int normed_slices(int N, int K, int epi) {
+static int normed_slices(int N, int K, int epi, int M = 1, bool ordered = false) {
     static int sm_count = 0;
     if (!sm_count) {
         int dev = 0;
@@ -1087,11 +1094,13 @@ static int normed_slices(int N, int K, int epi) {
         const int max_s = kb / 4 > 0 ? kb / 4 : 1;
         s = s < 1 ? 1 : (s > max_s ? max_s : s);
         s = s > 16 ? 16 : s;
+        if (ordered) s = ordered_fit(M <= 16 ? 16 : 32, true, tiles, s);
     }
     const int per = (kb + s - 1) / s;
     return (kb + per - 1) / per;
 }
-extern "C" int tb_gemm_tc_normed_slices(int N, int K, int epi) { return normed_slices(N, K, epi); }
+// M, ordered: the rows of the step and whether the slices add up in a fixed order (a cluster per tile: fewer slices fit).
+extern "C" int tb_gemm_tc_normed_slices(int N, int K, int epi, int M, int ordered) { return normed_slices(N, K, epi, M, ordered != 0); }
 
 // out (epilogue) = rmsnorm(xf; norm_w, eps)[M,K] . W[N,K]^T for a decode step's rows, the norm folded into the product:
 // the kernel reads the float32 rows, multiplies by the norm's weight on the way into shared memory and by
@@ -1106,7 +1115,7 @@ extern "C" int tb_gemm_tc_normed(const float* xf, int ldxf, const float* norm_w,
     const int kb = (K + BK - 1) / BK;
     const int tiles = (N + BM - 1) / BM;
     TB_REQUIRE(tiles <= 65535, "gemm_tc_normed: N=%d is too large for one launch", N);
-    const int s = normed_slices(N, K, epi);
+    const int s = normed_slices(N, K, epi, M, ordered != 0);
     TcArgs a;
     a.out = out; a.rows_a = N; a.rows_b = M; a.K = K; a.ldo = ldo; a.tiles_m = a.tiles_n = 0; a.tail_split = 1;
     a.k_blocks_per_split = (kb + s - 1) / s;
@@ -1117,7 +1126,7 @@ extern "C" int tb_gemm_tc_normed(const float* xf, int ldxf, const float* norm_w,
     dim3 grid(1, tiles, s);
     int rc;
     if (ordered && epi == TB_EPI_ADD && s > 1) {
-        TB_REQUIRE(s <= ordered_limit_for(M <= 16 ? 16 : 32, true), "gemm_tc_normed: this device places no cluster of %d K slices", s);
+        TB_REQUIRE(ordered_clusters_for(M <= 16 ? 16 : 32, true, s) > 0, "gemm_tc_normed: this device places no cluster of %d K slices", s);
         a.atomic = 0;
         rc = M <= 16 ? launch_tc_ordered<16, true>(ma, ma, a, grid, stream) : launch_tc_ordered<32, true>(ma, ma, a, grid, stream);
     } else if (M <= 16) rc = epi == TB_EPI_ADD ? launch_tc_normed<16, TB_EPI_ADD>(ma, a, grid, stream) : launch_tc_normed<16, TB_EPI_SWIGLU>(ma, a, grid, stream);
@@ -1216,7 +1225,7 @@ extern "C" int tb_gemm_tc(const void* X, const void* W, void* out, int M, int N,
             s = splits > 0 ? splits : room / tiles;
             const int max_s = kb / 4 > 0 ? kb / 4 : 1;              // at least four 64-wide blocks per slice
             s = s < 1 ? 1 : (s > max_s ? max_s : s);
-            if (ordered) { const int lim = ordered_limit_for(bn, false); s = s > lim ? lim : s; }
+            if (ordered) s = ordered_fit(bn, false, tiles, s);
         }
         a.k_blocks_per_split = (kb + s - 1) / s;
         s = (kb + a.k_blocks_per_split - 1) / a.k_blocks_per_split;  // no empty slice

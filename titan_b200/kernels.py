@@ -274,9 +274,10 @@ def gemm_tc_normed(x: torch.Tensor, norm_w: torch.Tensor, eps: float, w: torch.T
                                    w.shape[0], x.shape[1], out.stride(0), epi, _ptr(sumsq), int(bool(ordered)), stream))
 
 
-def gemm_tc_normed_slices(w: torch.Tensor, epi: int) -> int:
-    """K slices that gemm_tc_normed cuts this product into (one row of partial sums of squares each)."""
-    return int(tlib().tb_gemm_tc_normed_slices(w.shape[0], w.shape[1], epi))
+def gemm_tc_normed_slices(w: torch.Tensor, epi: int, rows: int = 1, ordered: bool = False) -> int:
+    """K slices that gemm_tc_normed cuts this product into (one row of partial sums of squares each) for a step of
+    ``rows`` rows; ``ordered``: as it cuts when the slices add up in a fixed order (a cluster per tile: fewer fit)."""
+    return int(tlib().tb_gemm_tc_normed_slices(w.shape[0], w.shape[1], epi, int(rows), int(bool(ordered))))
 
 
 def gemm_tc_error() -> int:

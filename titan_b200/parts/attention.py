@@ -201,7 +201,8 @@ class AttentionMixer(Mixer):
         if not (self.shared or wide_sum):
             qa.k_out, qa.k_stride = qkv.data_ptr() + Q * qkv.element_size(), width
         if row_sums is not None:
-            qa.row_sumsq, qa.row_parts = row_sums.data_ptr(), K.gemm_tc_normed_slices(self.w_qkv, linear.EPI_ADD)
+            qa.row_sumsq = row_sums.data_ptr()
+            qa.row_parts = K.gemm_tc_normed_slices(self.w_qkv, linear.EPI_ADD, T, bool(ctx.options.get("reproducible", False)))
             qa.row_width, qa.row_eps = s.hidden_size, h.eps
         # A decode step whose Q | K | V are float32 sums may leave head norm, rotation and append to the attention
         # kernel itself (one kernel less between the projection and the attention); decided below, where the
