@@ -149,6 +149,24 @@ def toy_parts():
                 state[slot] = s
     MIXERS.register("toy_decay", DecayMixer)
 
+    class DecayMixerOnDevice(DecayMixer):
+        """The same mixer with its single-token steps written without the host: the layout's arrays index the state on
+        the device, so the engine may capture decode steps with it as CUDA graphs (the default: ``capturable``)."""
+
+        capturable = True
+
+        def forward(self, h, ctx, cache, out):
+            lay = ctx.layout
+            if not lay.all_single:
+                return super().forward(h, ctx, cache, out)         # prompts: the scan over a sequence's tokens, on the host
+            group, index = cache
+            state = group.layer_storage(index)
+            slots = lay.slot_of_seq.long()
+            new = self.decay * state[slots] + h.float() @ self.w.float().t()
+            state[slots] = new
+            out += new
+    MIXERS.register("toy_decay_on_device", DecayMixerOnDevice)
+
 
 class ToyConfig:
     """Layers alternate between the toy mixer and attention; layer 2 runs twice."""
@@ -170,7 +188,7 @@ class ToyConfig:
         layers = []
         for i in range(d["depth"]):
             if i % 2 == 0:
-                mixer = MixerSpec("toy_decay", H, prefix="mix.", extra=(("decay", d["decay"]),))
+                mixer = MixerSpec(d.get("mixer", "toy_decay"), H, prefix="mix.", extra=(("decay", d["decay"]),))
             else:
                 mixer = MixerSpec("attention", H, 4, 2, 16, position=PositionSpec("rope", 16, 100.0), prefix="attn.")
             layers.append(LayerSpec(i, "pre_norm", mixer, FeedForwardSpec("gated_mlp", H, d["ff"], prefix="ff."),
@@ -242,6 +260,38 @@ def test_a_toy_mixer_with_state_registers_builds_and_steps(dtype):
     for j, tok in enumerate(made):
         row = logits[len(prompt) - 1 + j]
         assert tok == int(row.argmax()) or float(row.max() - row[tok]) < 0.05 * float(row.abs().max())
+
+
+def test_a_toy_mixer_with_state_in_captured_decode_steps():
+    """The toy mixer with its decode step written for the device: the engine captures its steps as graphs (state of fixed
+    size per sequence, read and written inside the graph through the step's slot indices), two requests of unequal
+    length generate greedily, one leaves earlier, and every token is the plain implementation's choice."""
+    from titan_b200 import Engine, SamplerParams, register_architecture
+    from titan_b200.parts import declare_weights
+    toy_parts()
+    register_architecture("ToyForCausalLM", ToyConfig)
+    d = {"architectures": ["ToyForCausalLM"], "width": 64, "depth": 2, "ff": 96, "vocab": 150, "decay": 0.7, "order": [0, 1, 0],
+         "mixer": "toy_decay_on_device"}
+    cfg = ToyConfig(d)
+    g = torch.Generator().manual_seed(9)
+    w = {}
+    for s in declare_weights(cfg.to_model_spec()):
+        t = torch.randn(s.shape, generator=g) * (0.1 if s.role == "vector" else 0.12) + (1.0 if s.role == "vector" else 0.0)
+        w[s.name] = t.to(torch.bfloat16)
+    w32 = {k: v.float() for k, v in w.items()}
+    e = Engine.from_tensors(cfg, w, dtype="float32", max_tokens=512, max_slots=3)
+    prompts = [random_tokens(17, 150, 5), random_tokens(4, 150, 6)]
+    from titan_b200 import GenerationRequest
+    from titan_b200.engine import generate
+    outs = generate(e, [GenerationRequest(list(p), n, SamplerParams.greedy(), (), False) for p, n in zip(prompts, (20, 9))])
+    assert e.graph_launches > 0                                          # the steps were replayed from graphs
+    for prompt, o, n in zip(prompts, outs, (20, 9)):
+        assert len(o.tokens) == n
+        logits = toy_plain(d, w32, list(prompt) + o.tokens)
+        for j, tok in enumerate(o.tokens):
+            row = logits[len(prompt) - 1 + j]
+            assert tok == int(row.argmax()) or float(row.max() - row[tok]) < 1e-3 * float(row.abs().max()), (j, tok)
+    e.cache.check()
 
 
 # --------------------------------------------------------------------------- #
